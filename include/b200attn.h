@@ -1,0 +1,160 @@
+/*
+ * b200attn — C ABI of the B200 (sm_100a) attention hot path.
+ *
+ * Plain pointers and sizes only; no torch types.  Every entry point is
+ * asynchronous on the stream it is given, never synchronises the device,
+ * never allocates or frees device memory, and returns 0 on success or a
+ * negative B200ATTN_E_* code (text via b200attn_last_error()).
+ *
+ * The functions replace the Triton launches behind these reference entry
+ * points (paths are relative to the reference project):
+ *
+ *   b200attn_prefill  <- kernels/attention.py:749-927  flash_attention_v2
+ *                        (partial kernel :430-656 + merge kernel :659-746),
+ *                        and flash_attention_v1 :249-364 (same semantics)
+ *   b200attn_decode   <- kernels/decode.py:203-331  decode_attention
+ *                        (split kernel :22-168 + merge :171-200) and
+ *                        kernels/speculative_decode.py:228-366
+ *                        speculative_decode_attention (split :22-186 +
+ *                        merge :189-226); decode is the M == 1 case
+ *   b200attn_*_workspace_bytes <- the torch.empty fp32 workspaces at
+ *                        kernels/attention.py:852-864, kernels/decode.py:280-292,
+ *                        kernels/speculative_decode.py:311-323
+ *   b200attn_device_info <- torch.cuda.get_device_properties(...).multi_processor_count
+ *                        at kernels/attention.py:836, kernels/decode.py:273
+ */
+#ifndef B200ATTN_H_
+#define B200ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200ATTN_ABI_VERSION 1
+
+/* element type of q/k/v/out */
+enum { B200ATTN_F16 = 0, B200ATTN_BF16 = 1, B200ATTN_F32 = 2 };
+/* K/V layout (reference "TYPE" 0/1/2: kernels/attention.py:785,810,832) */
+enum { B200ATTN_DENSE = 0, B200ATTN_RAGGED = 1, B200ATTN_PAGED = 2 };
+
+/* status codes */
+enum {
+  B200ATTN_OK = 0,
+  B200ATTN_E_INVALID = -1,      /* bad argument (null pointer, bad shape, misalignment) */
+  B200ATTN_E_UNSUPPORTED = -2,  /* head_dim / dtype / page size outside the built kernels */
+  B200ATTN_E_ARCH = -3,         /* device is not compute capability 10.x */
+  B200ATTN_E_WORKSPACE = -4,    /* workspace too small or misaligned */
+  B200ATTN_E_CUDA = -5,         /* CUDA runtime / driver call failed */
+  B200ATTN_E_DEVICE = -6        /* a kernel reported a bounded-wait expiry or bounds violation */
+};
+
+typedef struct b200attn_device_info_t {
+  int32_t sm_count;
+  int32_t cc_major;
+  int32_t cc_minor;
+  int32_t max_smem_optin;  /* bytes */
+} b200attn_device_info_t;
+
+/*
+ * Prefill (many query rows per sequence).
+ *
+ *  DENSE : q [B,QH,M,D]  k,v [B,KVH,N,D]                       out [B,QH,M,D]
+ *  RAGGED: q [total_q,QH,D]  k,v [total_kv,KVH,D]  q_indptr,kv_indptr [B+1] prefix sums
+ *          out [total_q,QH,D]
+ *  PAGED : q [B,QH,M,D]  k,v cache [cache_tokens,KVH,D]  kv_indptr [B] = lengths,
+ *          k_table,v_table [B,table_stride] int32 physical page numbers
+ *
+ * All tensors contiguous, 16-byte aligned.  Causal masking is top-left aligned
+ * on per-sequence indices (key j visible to query i iff j <= i).  scale = sm_scale.
+ */
+typedef struct b200attn_prefill_args_t {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  const void* q_indptr;   /* RAGGED only */
+  const void* kv_indptr;  /* RAGGED: prefix sums [B+1]; PAGED: lengths [B] */
+  const int32_t* k_table; /* PAGED only */
+  const int32_t* v_table; /* PAGED only */
+  void* workspace;        /* >= b200attn_prefill_workspace_bytes(), 256-byte aligned */
+  size_t workspace_bytes;
+  int64_t total_q;        /* RAGGED: rows of q */
+  int64_t total_kv;       /* RAGGED: rows of k/v; PAGED: rows of the cache */
+  int64_t table_stride;   /* PAGED: entries per table row */
+  int32_t dtype;
+  int32_t layout;
+  int32_t indptr_is_i64;  /* width of q_indptr / kv_indptr entries */
+  int32_t batch;
+  int32_t q_heads;
+  int32_t kv_heads;
+  int32_t max_q;          /* DENSE/PAGED: M */
+  int32_t max_kv;         /* DENSE: N */
+  int32_t head_dim;       /* 64 or 128 */
+  int32_t page_size;      /* PAGED */
+  int32_t is_causal;
+  int32_t device;         /* CUDA ordinal that owns the pointers */
+  float sm_scale;
+} b200attn_prefill_args_t;
+
+/*
+ * Decode / speculative decode (q_len = M <= 16 query tokens per sequence).
+ *
+ *  q, out [B,QH,M,D] (decode_attention's [B,QH,D] is M == 1)
+ *  DENSE : k,v [B,KVH,N,D]
+ *  RAGGED: k,v [total_kv,KVH,D], kv_indptr [B+1] prefix sums
+ *  PAGED : k,v cache [cache_tokens,KVH,D], kv_indptr [B] lengths, tables as above
+ *
+ * causal_drafts != 0: the last M keys of each sequence are the draft tokens'
+ * own keys and draft row i does not see draft keys i+1..M-1.
+ */
+typedef struct b200attn_decode_args_t {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  const void* kv_indptr;
+  const int32_t* k_table;
+  const int32_t* v_table;
+  void* workspace;        /* >= b200attn_decode_workspace_bytes(), 256-byte aligned */
+  size_t workspace_bytes;
+  int64_t total_kv;       /* RAGGED: rows of k/v; PAGED: rows of the cache */
+  int64_t table_stride;
+  int32_t dtype;
+  int32_t layout;
+  int32_t indptr_is_i64;
+  int32_t batch;
+  int32_t q_heads;
+  int32_t kv_heads;
+  int32_t q_len;          /* M, 1..16 */
+  int32_t max_kv;         /* DENSE: N; PAGED: table_stride * page_size */
+  int32_t head_dim;
+  int32_t page_size;
+  int32_t causal_drafts;
+  int32_t device;
+  float sm_scale;
+} b200attn_decode_args_t;
+
+int b200attn_abi_version(void);
+const char* b200attn_last_error(void);
+int b200attn_device_info(int device, b200attn_device_info_t* info);
+
+size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args_t* args);
+size_t b200attn_decode_workspace_bytes(const b200attn_decode_args_t* args);
+
+int b200attn_prefill(const b200attn_prefill_args_t* args, void* cuda_stream);
+int b200attn_decode(const b200attn_decode_args_t* args, void* cuda_stream);
+
+/*
+ * Reads (and clears) the error word a kernel of an earlier call may have set in
+ * `workspace` (bounded wait expired, page index out of range).  Synchronises
+ * `cuda_stream`.  Returns 0, or B200ATTN_E_DEVICE with the code in *code.
+ */
+int b200attn_check_workspace(void* workspace, void* cuda_stream, int32_t* code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ATTN_H_ */

@@ -1,0 +1,110 @@
+"""GPU parity tests for speculative_decode_attention.  Mirrors the reference's
+tests/test_speculative_decode.py:169-332 (causal x M x layout x topology x dtype, B=4, D=64) with
+seeded inputs; in causal mode the M draft K/V rows are appended to each sequence and the length
+passed to the kernel includes them (:202-224, :242-251, :280-289)."""
+import pytest
+import torch
+
+from helpers import DTYPE_IDS, DTYPES, TOPOLOGIES, assert_close_both, decode_sequences, make_rngs
+from oracle import sdpa_ref
+
+pytestmark = pytest.mark.gpu
+DEVICE = "cuda"
+PAGE_SIZE = 16
+M_VALUES = [2, 3, 4, 6, 8, 10, 12, 16]
+
+
+def run_spec(layout, qs, ks, vs, causal, *, index_dtype=torch.int32, permute=None, poison=None, pad=0):
+    from kernels.speculative_decode import speculative_decode_attention
+
+    B = len(qs)
+    q = torch.stack(qs)
+    lens = [int(k.shape[0]) for k in ks]
+    if layout == "dense":
+        KVH, D = ks[0].shape[1], ks[0].shape[2]
+        n = max(lens)
+        k = torch.zeros((B, KVH, n, D), device=DEVICE, dtype=q.dtype)
+        v = torch.zeros_like(k)
+        for b in range(B):
+            k[b, :, : lens[b]] = ks[b].transpose(0, 1)
+            v[b, :, : lens[b]] = vs[b].transpose(0, 1)
+        return speculative_decode_attention(q, k, v, causal=causal)
+    if layout == "ragged":
+        k, indptr = sdpa_ref.pack_ragged(ks, index_dtype)
+        v, _ = sdpa_ref.pack_ragged(vs, index_dtype)
+        return speculative_decode_attention(q, k, v, kv_indptr=indptr, causal=causal)
+    kc, kt, lens_t = sdpa_ref.pack_paged(ks, PAGE_SIZE, permute_seed=permute, extra_pages=2 if permute is not None else 0,
+                                         pad_value=pad, poison=poison)
+    vc, vt, _ = sdpa_ref.pack_paged(vs, PAGE_SIZE, permute_seed=None if permute is None else permute + 1,
+                                    extra_pages=4 if permute is not None else 0, pad_value=pad, poison=poison)
+    return speculative_decode_attention(q, kc, vc, kv_indptr=lens_t.to(index_dtype), k_block_table=kt, v_block_table=vt,
+                                        kv_page_size=PAGE_SIZE, causal=causal)
+
+
+def with_drafts(rng, gen, B, QH, KVH, M, D, dtype, layout, causal):
+    qs, ks, vs, kv_lens = decode_sequences(rng, gen, B, QH, KVH, D, dtype, layout, DEVICE, M=M)
+    if causal:
+        ks = [torch.cat([k, torch.randn((M, KVH, D), generator=gen).to(dtype).to(DEVICE)]) for k in ks]
+        vs = [torch.cat([v, torch.randn((M, KVH, D), generator=gen).to(dtype).to(DEVICE)]) for v in vs]
+    return qs, ks, vs
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("M", M_VALUES)
+@pytest.mark.parametrize("layout", ["dense", "ragged", "paged"])
+@pytest.mark.parametrize("topology", list(TOPOLOGIES))
+@pytest.mark.parametrize("dtype", DTYPES, ids=DTYPE_IDS)
+def test_speculative_decode_reference_grid(M, layout, topology, dtype, causal):
+    QH, KVH = TOPOLOGIES[topology]
+    rng, gen = make_rngs("spec", M, layout, topology, dtype, causal)
+    qs, ks, vs = with_drafts(rng, gen, 4, QH, KVH, M, 64, dtype, layout, causal)
+    if layout == "dense" and causal:
+        # the dense kernel takes one N for the batch: the drafts must sit at the tail of every row
+        pass
+    refs = sdpa_ref.spec_decode_reference(qs, ks, vs, QH, KVH, causal)
+    out = run_spec(layout, qs, ks, vs, causal)
+    n = max(int(k.shape[0]) for k in ks)
+    for b in range(4):
+        assert_close_both(out[b], refs[b], dtype, n, f"seq {b}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=DTYPE_IDS)
+@pytest.mark.parametrize("M", [1, 5, 16])
+def test_spec_paged_hostile_cache_d128(dtype, M):
+    """The benchmark's shape family: 64/8 heads, D=128, random tables, poisoned tails, long contexts."""
+    QH, KVH, B = 64, 8, 2
+    rng, gen = make_rngs("spec-hostile", dtype, M)
+    lens = [2500 + M, 77 + M]
+    qs = [torch.randn((QH, M, 128), generator=gen).to(dtype).to(DEVICE) for _ in range(B)]
+    ks = [torch.randn((n, KVH, 128), generator=gen).to(dtype).to(DEVICE) for n in lens]
+    vs = [torch.randn((n, KVH, 128), generator=gen).to(dtype).to(DEVICE) for n in lens]
+    refs = sdpa_ref.spec_decode_reference(qs, ks, vs, QH, KVH, True)
+    out = run_spec("paged", qs, ks, vs, True, permute=9, poison=float("nan"), pad=-1, index_dtype=torch.int64)
+    assert torch.isfinite(out.float()).all()
+    for b in range(B):
+        assert_close_both(out[b], refs[b], dtype, max(lens), f"seq {b}")
+
+
+def test_spec_draft_only_context():
+    """Sequences that consist of the drafts alone (context length 0): row i sees keys 0..i."""
+    M, QH, KVH = 4, 8, 2
+    gen = torch.Generator().manual_seed(12)
+    qs = [torch.randn((QH, M, 64), generator=gen).to(torch.float16).to(DEVICE) for _ in range(2)]
+    ks = [torch.randn((M, KVH, 64), generator=gen).to(torch.float16).to(DEVICE) for _ in range(2)]
+    vs = [torch.randn((M, KVH, 64), generator=gen).to(torch.float16).to(DEVICE) for _ in range(2)]
+    refs = sdpa_ref.spec_decode_reference(qs, ks, vs, QH, KVH, True)
+    for layout in ("dense", "ragged", "paged"):
+        out = run_spec(layout, qs, ks, vs, True)
+        for b in range(2):
+            assert_close_both(out[b], refs[b], torch.float16, M, layout)
+        # row 0 of every head sees exactly key 0
+        assert torch.equal(out[0][:, 0, :], vs[0][0].repeat_interleave(QH // KVH, dim=0))
+
+
+def test_spec_m_too_large_rejected():
+    from kernels.speculative_decode import speculative_decode_attention
+
+    q = torch.zeros((1, 8, 17, 64), device=DEVICE, dtype=torch.float16)
+    k = torch.zeros((1, 2, 32, 64), device=DEVICE, dtype=torch.float16)
+    with pytest.raises(AssertionError):
+        speculative_decode_attention(q, k, k)

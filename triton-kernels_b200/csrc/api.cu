@@ -1,0 +1,172 @@
+// C ABI of the attention hot path: argument checks, device bookkeeping, dispatch.
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "common.cuh"
+#include "decode_launch.h"
+#include "prefill_launch.h"
+
+namespace b200attn {
+
+namespace {
+thread_local char g_error[512] = "";
+
+struct DeviceCache {
+  bool valid = false;
+  b200attn_device_info_t info{};
+};
+constexpr int kMaxDevices = 64;
+DeviceCache g_devices[kMaxDevices];
+std::mutex g_device_mutex;
+}  // namespace
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+  return B200ATTN_E_CUDA;
+}
+
+static int query_device(int device, b200attn_device_info_t* out) {
+  if (device < 0 || device >= kMaxDevices) { set_error("device ordinal %d out of range", device); return B200ATTN_E_INVALID; }
+  std::lock_guard<std::mutex> lock(g_device_mutex);
+  DeviceCache& c = g_devices[device];
+  if (!c.valid) {
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceProperties");
+    c.info.sm_count = prop.multiProcessorCount;
+    c.info.cc_major = prop.major;
+    c.info.cc_minor = prop.minor;
+    c.info.max_smem_optin = static_cast<int32_t>(prop.sharedMemPerBlockOptin);
+    c.valid = true;
+  }
+  *out = c.info;
+  return B200ATTN_OK;
+}
+
+// makes `device` current for the duration of a call
+struct DeviceGuard {
+  int prev = -1;
+  bool changed = false;
+  int enter(int device) {
+    cudaError_t e = cudaGetDevice(&prev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+    if (prev != device) {
+      e = cudaSetDevice(device);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaSetDevice");
+      changed = true;
+    }
+    return 0;
+  }
+  ~DeviceGuard() { if (changed) cudaSetDevice(prev); }
+};
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+static int check_common(int dtype, int layout, int batch, int q_heads, int kv_heads, int head_dim) {
+  if (dtype != B200ATTN_F16 && dtype != B200ATTN_BF16 && dtype != B200ATTN_F32) { set_error("unknown dtype %d", dtype); return B200ATTN_E_INVALID; }
+  if (layout != B200ATTN_DENSE && layout != B200ATTN_RAGGED && layout != B200ATTN_PAGED) { set_error("unknown layout %d", layout); return B200ATTN_E_INVALID; }
+  if (batch < 0 || q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0) { set_error("bad batch/head counts (B=%d QH=%d KVH=%d)", batch, q_heads, kv_heads); return B200ATTN_E_INVALID; }
+  if (head_dim != 64 && head_dim != 128) { set_error("head_dim %d is not built (64 or 128)", head_dim); return B200ATTN_E_UNSUPPORTED; }
+  return 0;
+}
+
+static int check_arch(int device, b200attn_device_info_t* info) {
+  int rc = query_device(device, info);
+  if (rc) return rc;
+  if (info->cc_major != 10) {
+    set_error("device %d is sm_%d%d; this library contains sm_100a code only", device, info->cc_major, info->cc_minor);
+    return B200ATTN_E_ARCH;
+  }
+  return 0;
+}
+
+}  // namespace b200attn
+
+using namespace b200attn;
+
+extern "C" {
+
+int b200attn_abi_version(void) { return B200ATTN_ABI_VERSION; }
+
+const char* b200attn_last_error(void) { return g_error; }
+
+int b200attn_device_info(int device, b200attn_device_info_t* info) {
+  if (!info) { set_error("info is null"); return B200ATTN_E_INVALID; }
+  return query_device(device, info);
+}
+
+size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args_t* a) {
+  if (!a) return 0;
+  return prefill_workspace_bytes(*a);
+}
+
+size_t b200attn_decode_workspace_bytes(const b200attn_decode_args_t* a) {
+  if (!a || a->kv_heads <= 0 || a->batch < 0) return 0;
+  b200attn_device_info_t info;
+  if (query_device(a->device, &info)) return 0;
+  return decode_ws_layout(*a, info.sm_count).total;
+}
+
+int b200attn_prefill(const b200attn_prefill_args_t* a, void* cuda_stream) {
+  if (!a) { set_error("args is null"); return B200ATTN_E_INVALID; }
+  int rc = check_common(a->dtype, a->layout, a->batch, a->q_heads, a->kv_heads, a->head_dim);
+  if (rc) return rc;
+  if (!a->q || !a->k || !a->v || !a->out) { set_error("prefill: null tensor pointer"); return B200ATTN_E_INVALID; }
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out)) { set_error("prefill: tensors must be 16-byte aligned"); return B200ATTN_E_INVALID; }
+  if (a->layout == B200ATTN_RAGGED && (!a->q_indptr || !a->kv_indptr || a->total_q < 0 || a->total_kv < 0)) { set_error("prefill: ragged layout needs q_indptr, kv_indptr and totals"); return B200ATTN_E_INVALID; }
+  if (a->layout == B200ATTN_PAGED && (!a->kv_indptr || !a->k_table || !a->v_table || a->page_size <= 0 || a->table_stride < 0)) { set_error("prefill: paged layout needs lengths, both block tables and a page size"); return B200ATTN_E_INVALID; }
+  if (a->layout != B200ATTN_RAGGED && (a->max_q < 0 || (a->layout == B200ATTN_DENSE && a->max_kv < 0))) { set_error("prefill: negative extent"); return B200ATTN_E_INVALID; }
+  b200attn_device_info_t info;
+  if ((rc = check_arch(a->device, &info))) return rc;
+  if (a->batch == 0) return B200ATTN_OK;
+  DeviceGuard guard;
+  if ((rc = guard.enter(a->device))) return rc;
+  return launch_prefill(*a, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int b200attn_decode(const b200attn_decode_args_t* a, void* cuda_stream) {
+  if (!a) { set_error("args is null"); return B200ATTN_E_INVALID; }
+  int rc = check_common(a->dtype, a->layout, a->batch, a->q_heads, a->kv_heads, a->head_dim);
+  if (rc) return rc;
+  if (!a->q || !a->k || !a->v || !a->out) { set_error("decode: null tensor pointer"); return B200ATTN_E_INVALID; }
+  if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out)) { set_error("decode: tensors must be 16-byte aligned"); return B200ATTN_E_INVALID; }
+  if (a->q_len < 1 || a->q_len > 16) { set_error("decode: q_len %d outside 1..16", a->q_len); return B200ATTN_E_INVALID; }
+  if ((a->q_heads / a->kv_heads) * a->q_len > 128) { set_error("decode: group*q_len = %d rows exceed 128", (a->q_heads / a->kv_heads) * a->q_len); return B200ATTN_E_UNSUPPORTED; }
+  if (a->layout == B200ATTN_RAGGED && (!a->kv_indptr || a->total_kv < 0)) { set_error("decode: ragged layout needs kv_indptr and total_kv"); return B200ATTN_E_INVALID; }
+  if (a->layout == B200ATTN_PAGED && (!a->kv_indptr || !a->k_table || !a->v_table || a->page_size <= 0 || a->table_stride < 0)) { set_error("decode: paged layout needs lengths, both block tables and a page size"); return B200ATTN_E_INVALID; }
+  if (a->layout == B200ATTN_DENSE && a->max_kv < 0) { set_error("decode: negative extent"); return B200ATTN_E_INVALID; }
+  b200attn_device_info_t info;
+  if ((rc = check_arch(a->device, &info))) return rc;
+  if (a->batch == 0) return B200ATTN_OK;
+  DeviceGuard guard;
+  if ((rc = guard.enter(a->device))) return rc;
+  return launch_decode(*a, info.sm_count, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int b200attn_check_workspace(void* workspace, void* cuda_stream, int32_t* code) {
+  if (!workspace) { set_error("workspace is null"); return B200ATTN_E_INVALID; }
+  cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+  int32_t word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, workspace, sizeof(word), cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the workspace error word");
+  if (code) *code = word;
+  if (word != 0) {
+    e = cudaMemsetAsync(workspace, 0, sizeof(word), st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return cuda_fail(e, "clearing the workspace error word");
+    set_error("a kernel reported device error code %d (1 = bounded wait expired, 2 = block-table entry out of range, 3 = planner overflow)", word);
+    return B200ATTN_E_DEVICE;
+  }
+  return B200ATTN_OK;
+}
+
+}  // extern "C"

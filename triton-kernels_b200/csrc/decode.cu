@@ -1,0 +1,663 @@
+// Decode and speculative-decode attention for sm_100a (HBM-bound path).
+//
+// One launch family replaces the reference's split kernel + merge kernel pairs
+// (kernels/decode.py:22-200, kernels/speculative_decode.py:22-226):
+//
+//   decode_plan_kernel : 1 CTA.  Reads the sequence lengths on the device (no
+//       host sync), picks the KV chunk size so that the whole batch becomes about
+//       `target_items` equally sized work items, and writes the per-sequence item
+//       prefix.  A work item is (sequence, KV chunk); the grid's y axis is the KV head.
+//   decode_mma_kernel  : one CTA per (item, kv_head).  All q rows that share the
+//       KV head (group size G x draft tokens M, <= 128 rows) are packed into
+//       16-row MMA tiles, so every K/V byte is read from HBM once per KV head
+//       (the reference re-reads it once per q head).  K/V tiles of 64 tokens
+//       stream through a 3-stage cp.async ring with 16-byte loads; paged
+//       layouts resolve the block table per row; rows past the sequence end
+//       are zero-filled, never dereferenced.  QK^T and PV run on bf16/fp16
+//       mma.sync with fp32 accumulation and an online softmax in the exp2 domain.
+//   decode_simt_kernel : the fp32-input variant, fp32 FMA arithmetic like the
+//       reference's decode kernel.
+//   Both end in emit_and_merge(): a CTA whose sequence has a single chunk writes
+//       the output directly; otherwise it writes an (m, l, acc) partial and takes
+//       a ticket, and the CTA that draws the last ticket of its (sequence, kv head)
+//       performs the log-sum-exp merge.  No CTA ever waits for another.
+#include <algorithm>
+
+#include "common.cuh"
+#include "decode_launch.h"
+
+namespace b200attn {
+
+namespace {
+
+constexpr int kTileN = 64;
+constexpr int kStages = 3;
+constexpr int kPlanThreads = 1024;
+
+struct SeqInfo {
+  long long start;  // ragged: first row of the sequence
+  int len;
+};
+
+__device__ __forceinline__ SeqInfo seq_info(const DecodeParams& p, int b) {
+  SeqInfo s;
+  s.start = 0;
+  if (p.layout == B200ATTN_DENSE) {
+    s.len = p.max_kv;
+  } else if (p.layout == B200ATTN_RAGGED) {
+    long long a = load_index(p.kv_indptr, p.indptr_is_i64, b);
+    long long e = load_index(p.kv_indptr, p.indptr_is_i64, b + 1);
+    a = a < 0 ? 0 : (a > p.total_kv ? p.total_kv : a);
+    e = e < a ? a : (e > p.total_kv ? p.total_kv : e);
+    s.start = a;
+    s.len = static_cast<int>(e - a);
+  } else {
+    long long n = load_index(p.kv_indptr, p.indptr_is_i64, b);
+    long long cap = p.table_stride * static_cast<long long>(p.page_size);
+    n = n < 0 ? 0 : (n > cap ? cap : n);
+    s.len = static_cast<int>(n);
+  }
+  return s;
+}
+
+// element offset of row `t` of sequence `b`, head `h`; -1 when the block table entry is out of range
+__device__ __forceinline__ long long row_offset(const DecodeParams& p, const int* table, int b, int h,
+                                                long long seq_start, int t, int D) {
+  if (p.layout == B200ATTN_DENSE) {
+    return ((static_cast<long long>(b) * p.kv_heads + h) * p.max_kv + t) * D;
+  } else if (p.layout == B200ATTN_RAGGED) {
+    return ((seq_start + t) * p.kv_heads + h) * D;
+  } else {
+    int lp, off;
+    if (p.page_shift >= 0) {
+      lp = t >> p.page_shift;
+      off = t & (p.page_size - 1);
+    } else {
+      lp = t / p.page_size;
+      off = t - lp * p.page_size;
+    }
+    const int page = __ldg(table + static_cast<long long>(b) * p.table_stride + lp);
+    if (page < 0 || page >= p.num_pages) return -1;
+    return ((static_cast<long long>(page) * p.page_size + off) * p.kv_heads + h) * D;
+  }
+}
+
+__device__ __forceinline__ int find_sequence(const int* item_start, int batch, int item) {
+  int lo = 0, hi = batch;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (item_start[mid] <= item) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// ---------------------------------------------------------------------------
+// Emit the CTA's combined (m, l, acc) rows, then merge if this CTA is the last
+// of its (sequence, kv head).  `comb_o` is smem [KS][rows_pad][D] fp32,
+// `comb_ml` is smem [KS][rows_pad][2] = (m in log2 units, l).
+// ---------------------------------------------------------------------------
+template <typename T, int D>
+__device__ __forceinline__ void emit_and_merge(const DecodeParams& p, int b, int h, int c, int n_chunks,
+                                               int item0, const float* comb_o, const float* comb_ml,
+                                               int KS, int rows_pad, int* s_ticket) {
+  constexpr int D4 = D / 4;
+  const int R = p.rows;
+  T* out = static_cast<T*>(p.out) +
+           ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.group) * p.q_len) * D;
+  const long long slot = (static_cast<long long>(item0) + c) * p.kv_heads + h;
+  for (int idx = threadIdx.x; idx < R * D4; idx += blockDim.x) {
+    const int r = idx / D4, d4 = idx - r * D4;
+    float mg = -INFINITY;
+    for (int k = 0; k < KS; ++k) mg = fmaxf(mg, comb_ml[(k * rows_pad + r) * 2]);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.f;
+    for (int k = 0; k < KS; ++k) {
+      const float mk = comb_ml[(k * rows_pad + r) * 2];
+      const float w = (mk == -INFINITY) ? 0.f : fast_exp2(mk - mg);
+      const float4 o = *reinterpret_cast<const float4*>(comb_o + (static_cast<size_t>(k) * rows_pad + r) * D + d4 * 4);
+      acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+      l += w * comb_ml[(k * rows_pad + r) * 2 + 1];
+    }
+    if (n_chunks == 1) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      T* dst = out + static_cast<long long>(r) * D + d4 * 4;
+      if constexpr (sizeof(T) == 2) {
+        uint2 u;
+        u.x = ElemTraits<T>::pack2(acc.x * inv, acc.y * inv);
+        u.y = ElemTraits<T>::pack2(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(dst) = u;
+      } else {
+        *reinterpret_cast<float4*>(dst) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+      }
+    } else {
+      *reinterpret_cast<float4*>(p.part_o + (slot * R + r) * D + d4 * 4) = acc;
+      if (d4 == 0) {
+        p.part_ml[(slot * R + r) * 2] = mg;
+        p.part_ml[(slot * R + r) * 2 + 1] = l;
+      }
+    }
+  }
+  if (n_chunks == 1) return;
+
+  // publish the partial, draw a ticket; the last arrival merges (nobody waits)
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) *s_ticket = atomicAdd(p.counters + b * p.kv_heads + h, 1);
+  __syncthreads();
+  if (*s_ticket != n_chunks - 1) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < R * D4; idx += blockDim.x) {
+    const int r = idx / D4, d4 = idx - r * D4;
+    float mg = -INFINITY;
+    for (int k = 0; k < n_chunks; ++k) {
+      const long long s = (static_cast<long long>(item0) + k) * p.kv_heads + h;
+      mg = fmaxf(mg, __ldcg(p.part_ml + (s * R + r) * 2));
+    }
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float l = 0.f;
+    for (int k = 0; k < n_chunks; ++k) {
+      const long long s = (static_cast<long long>(item0) + k) * p.kv_heads + h;
+      const float mk = __ldcg(p.part_ml + (s * R + r) * 2);
+      const float w = (mk == -INFINITY) ? 0.f : fast_exp2(mk - mg);
+      const float4 o = __ldcg(reinterpret_cast<const float4*>(p.part_o + (s * R + r) * D + d4 * 4));
+      acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
+      l += w * __ldcg(p.part_ml + (s * R + r) * 2 + 1);
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    T* dst = out + static_cast<long long>(r) * D + d4 * 4;
+    if constexpr (sizeof(T) == 2) {
+      uint2 u;
+      u.x = ElemTraits<T>::pack2(acc.x * inv, acc.y * inv);
+      u.y = ElemTraits<T>::pack2(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(dst) = u;
+    } else {
+      *reinterpret_cast<float4*>(dst) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    }
+  }
+  if (threadIdx.x == 0) p.counters[b * p.kv_heads + h] = 0;  // leave the counter ready for the next call
+}
+
+// ---------------------------------------------------------------------------
+// Planner
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeParams p) {
+  __shared__ long long s_tot[32];
+  __shared__ int s_warp[32];
+  __shared__ int s_carry;
+  __shared__ int s_chunk;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  long long tot = 0;
+  for (int b = tid; b < p.batch; b += kPlanThreads) tot += seq_info(p, b).len;
+  for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
+  if (lane == 0) s_tot[warp] = tot;
+  __syncthreads();
+  if (tid == 0) {
+    long long t = 0;
+    for (int w = 0; w < kPlanThreads / 32; ++w) t += s_tot[w];
+    long long per = (t + p.target_items - 1) / p.target_items;
+    per = ((per + kTileN - 1) / kTileN) * kTileN;
+    if (per < p.min_chunk) per = p.min_chunk;
+    if (per > (1 << 30)) per = 1 << 30;
+    s_chunk = static_cast<int>(per);
+    s_carry = 0;
+  }
+  for (int i = tid; i < p.batch * p.kv_heads; i += kPlanThreads) p.counters[i] = 0;
+  __syncthreads();
+  const int chunk = s_chunk;
+
+  for (int base = 0; base < p.batch; base += kPlanThreads) {
+    const int b = base + tid;
+    int v = 0;
+    if (b < p.batch) {
+      const int len = seq_info(p, b).len;
+      v = (len + chunk - 1) / chunk;
+      if (v < 1) v = 1;
+    }
+    int incl = v;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+      int w = s_warp[lane];
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += n;
+      }
+      s_warp[lane] = w;  // inclusive over warps
+    }
+    __syncthreads();
+    const int carry = s_carry;
+    const int before = warp > 0 ? s_warp[warp - 1] : 0;
+    if (b < p.batch) p.item_start[b + 1] = carry + before + incl;
+    __syncthreads();
+    if (tid == 0) s_carry = carry + s_warp[31];
+    __syncthreads();
+  }
+  if (tid == 0) {
+    p.item_start[0] = 0;
+    int n_items = s_carry;
+    if (n_items > p.max_items) {
+      p.header[0] = DEV_ERR_PLAN;
+      n_items = 0;
+    }
+    p.header[1] = chunk;
+    p.header[2] = n_items;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// bf16 / fp16 tensor-core kernel
+// ---------------------------------------------------------------------------
+template <typename T, int D>
+__global__ void __launch_bounds__(256) decode_mma_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int s_ticket;
+  constexpr int CPR = D * 2 / 16;          // 16-byte chunks per row
+  constexpr int ROW_BYTES = D * 2;
+  constexpr int TILE_BYTES = kTileN * ROW_BYTES;
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  constexpr int KSTEPS = D / 16;
+
+  const int n_items = p.header[2];
+  const int item = blockIdx.x;
+  if (item >= n_items) return;
+  const int h = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nthreads = blockDim.x;
+  const int NMT = p.n_mtiles;
+  const int KS = (nthreads >> 5) / NMT;
+  const int mt = warp % NMT, ks = warp / NMT;
+  const int rows_pad = NMT * 16;
+
+  const int b = find_sequence(p.item_start, p.batch, item);
+  const int item0 = p.item_start[b];
+  const int c = item - item0;
+  const int n_chunks = p.item_start[b + 1] - item0;
+  const int chunk = p.header[1];
+  const SeqInfo si = seq_info(p, b);
+  const int len = si.len;
+  const int t_begin = c * chunk;
+  const int t_end = min(len, t_begin + chunk);
+  const int ntiles = t_end > t_begin ? (t_end - t_begin + kTileN - 1) / kTileN : 0;
+
+  unsigned char* q_smem = smem;
+  unsigned char* stage_base = smem + rows_pad * ROW_BYTES;
+  const uint32_t q_s = smem_u32(q_smem);
+  const uint32_t stage_s = smem_u32(stage_base);
+
+  const T* kg = static_cast<const T*>(p.k);
+  const T* vg = static_cast<const T*>(p.v);
+
+  auto load_tile = [&](int tile, int stage) {
+    const int t0 = t_begin + tile * kTileN;
+    const uint32_t kdst = stage_s + stage * STAGE_BYTES;
+    const uint32_t vdst = kdst + TILE_BYTES;
+    for (int idx = tid; idx < kTileN * CPR; idx += nthreads) {
+      const int row = idx / CPR, ch = idx % CPR;
+      const int t = t0 + row;
+      const T* ksrc = kg;
+      const T* vsrc = vg;
+      int kbytes = 0, vbytes = 0;
+      if (t < t_end) {
+        const long long ko = row_offset(p, p.k_table, b, h, si.start, t, D);
+        const long long vo = (p.layout == B200ATTN_PAGED) ? row_offset(p, p.v_table, b, h, si.start, t, D) : ko;
+        if (ko >= 0) { ksrc = kg + ko + ch * 8; kbytes = 16; }
+        if (vo >= 0) { vsrc = vg + vo + ch * 8; vbytes = 16; }
+        if ((ko < 0 || vo < 0) && ch == 0) p.header[0] = DEV_ERR_PAGE_RANGE;
+      }
+      const uint32_t off = row * ROW_BYTES + ((ch ^ (row & 7)) << 4);
+      cp_async16(kdst + off, ksrc, kbytes);
+      cp_async16(vdst + off, vsrc, vbytes);
+    }
+  };
+
+  // prologue loads first, so the Q staging below overlaps with them
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (s < ntiles) load_tile(s, s);
+    cp_async_commit();
+  }
+
+  // Q rows (group x drafts, contiguous in memory) -> smem, zero padded to 16-row tiles
+  {
+    const T* qg = static_cast<const T*>(p.q) +
+                  ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.group) * p.q_len) * D;
+    for (int idx = tid; idx < rows_pad * CPR; idx += nthreads) {
+      const int row = idx / CPR, ch = idx % CPR;
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (row < p.rows) val = __ldg(reinterpret_cast<const uint4*>(qg + static_cast<long long>(row) * D + ch * 8));
+      *reinterpret_cast<uint4*>(q_smem + row * ROW_BYTES + ((ch ^ (row & 7)) << 4)) = val;
+    }
+  }
+  __syncthreads();
+  uint32_t qf[KSTEPS][4];
+  {
+    const int mat = lane >> 3;
+    const int row = mt * 16 + (mat & 1) * 8 + (lane & 7);
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      const int ch = kk * 2 + (mat >> 1);
+      ldmatrix_x4(qf[kk], q_s + row * ROW_BYTES + ((ch ^ (row & 7)) << 4));
+    }
+  }
+
+  // per-lane rows: r0 = mt*16 + lane/4, r1 = r0 + 8
+  const int r0 = mt * 16 + (lane >> 2);
+  const int r1 = r0 + 8;
+  int lim0 = len - 1, lim1 = len - 1;  // last visible key index for each row
+  if (p.causal) {
+    lim0 = len - p.q_len + (r0 % p.q_len);
+    lim1 = len - p.q_len + (r1 % p.q_len);
+  }
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+  float o[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { o[i][0] = 0.f; o[i][1] = 0.f; o[i][2] = 0.f; o[i][3] = 0.f; }
+  const float sl2 = p.scale_log2;
+
+  for (int it = 0; it < ntiles; ++it) {
+    cp_async_wait<kStages - 2>();
+    __syncthreads();
+    {
+      const int nt = it + kStages - 1;
+      if (nt < ntiles) load_tile(nt, nt % kStages);
+      cp_async_commit();
+    }
+    const int stage = it % kStages;
+    const uint32_t ks_base = stage_s + stage * STAGE_BYTES;
+    const uint32_t vs_base = ks_base + TILE_BYTES;
+    const int tile_t0 = t_begin + it * kTileN;
+
+    for (int sb = ks; sb < kTileN / 16; sb += KS) {
+      const int tok0 = sb * 16;             // within tile
+      const int abs0 = tile_t0 + tok0;      // within sequence
+      if (abs0 >= t_end) break;
+      float s[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
+      {
+        const int mat = lane >> 3;
+        const int trow = tok0 + (mat >> 1) * 8 + (lane & 7);
+        const uint32_t rbase = ks_base + trow * ROW_BYTES;
+        const int sw = trow & 7;
+#pragma unroll
+        for (int kk = 0; kk < KSTEPS; ++kk) {
+          uint32_t kb[4];
+          const int ch = kk * 2 + (mat & 1);
+          ldmatrix_x4(kb, rbase + ((ch ^ sw) << 4));
+          mma_m16n8k16<T>(s[0], qf[kk], kb[0], kb[1]);
+          mma_m16n8k16<T>(s[1], qf[kk], kb[2], kb[3]);
+        }
+      }
+      // scale, mask, online softmax (exp2 domain)
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const int col = abs0 + nt * 8 + 2 * (lane & 3);
+        s[nt][0] = (col <= lim0) ? s[nt][0] * sl2 : -INFINITY;
+        s[nt][1] = (col + 1 <= lim0) ? s[nt][1] * sl2 : -INFINITY;
+        s[nt][2] = (col <= lim1) ? s[nt][2] * sl2 : -INFINITY;
+        s[nt][3] = (col + 1 <= lim1) ? s[nt][3] * sl2 : -INFINITY;
+        mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+      const float ms0 = (mn0 == -INFINITY) ? 0.f : mn0;
+      const float ms1 = (mn1 == -INFINITY) ? 0.f : mn1;
+      const float a0 = fast_exp2(m_run[0] - ms0), a1 = fast_exp2(m_run[1] - ms1);
+      m_run[0] = mn0; m_run[1] = mn1;
+      float rs0 = 0.f, rs1 = 0.f;
+      uint32_t pa[4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const float p0 = fast_exp2(s[nt][0] - ms0), p1 = fast_exp2(s[nt][1] - ms0);
+        const float p2 = fast_exp2(s[nt][2] - ms1), p3 = fast_exp2(s[nt][3] - ms1);
+        rs0 += p0 + p1; rs1 += p2 + p3;
+        pa[nt * 2 + 0] = ElemTraits<T>::pack2(p0, p1);
+        pa[nt * 2 + 1] = ElemTraits<T>::pack2(p2, p3);
+      }
+      l_run[0] = l_run[0] * a0 + rs0;   // per-lane partial row sums; reduced over the quad at the end
+      l_run[1] = l_run[1] * a1 + rs1;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+      {
+        const int mat = lane >> 3;
+        const int trow = tok0 + (mat & 1) * 8 + (lane & 7);
+        const uint32_t rbase = vs_base + trow * ROW_BYTES;
+        const int sw = trow & 7;
+#pragma unroll
+        for (int n0 = 0; n0 < D / 16; ++n0) {
+          uint32_t vb[4];
+          const int ch = n0 * 2 + (mat >> 1);
+          ldmatrix_x4_trans(vb, rbase + ((ch ^ sw) << 4));
+          mma_m16n8k16<T>(o[2 * n0], pa, vb[0], vb[1]);
+          mma_m16n8k16<T>(o[2 * n0 + 1], pa, vb[2], vb[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // all tiles consumed: the stage ring is free for the cross-warp combine
+
+  l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+  l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+  l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
+  l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+
+  float* comb_o = reinterpret_cast<float*>(stage_base);
+  float* comb_ml = comb_o + static_cast<size_t>(KS) * rows_pad * D;
+  {
+    float* o0 = comb_o + (static_cast<size_t>(ks) * rows_pad + r0) * D;
+    float* o1 = comb_o + (static_cast<size_t>(ks) * rows_pad + r1) * D;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+      const int col = i * 8 + 2 * (lane & 3);
+      *reinterpret_cast<float2*>(o0 + col) = make_float2(o[i][0], o[i][1]);
+      *reinterpret_cast<float2*>(o1 + col) = make_float2(o[i][2], o[i][3]);
+    }
+    if ((lane & 3) == 0) {
+      comb_ml[(ks * rows_pad + r0) * 2] = m_run[0];
+      comb_ml[(ks * rows_pad + r0) * 2 + 1] = l_run[0];
+      comb_ml[(ks * rows_pad + r1) * 2] = m_run[1];
+      comb_ml[(ks * rows_pad + r1) * 2 + 1] = l_run[1];
+    }
+  }
+  __syncthreads();
+  emit_and_merge<T, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, KS, rows_pad, &s_ticket);
+}
+
+// ---------------------------------------------------------------------------
+// fp32 kernel: fp32 FMA dot products, one warp per q row, lanes split head_dim
+// ---------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128) decode_simt_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int s_ticket;
+  constexpr int VEC = D / 32;  // floats per lane
+  const int n_items = p.header[2];
+  const int item = blockIdx.x;
+  if (item >= n_items) return;
+  const int h = blockIdx.y;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int R = p.rows;
+
+  const int b = find_sequence(p.item_start, p.batch, item);
+  const int item0 = p.item_start[b];
+  const int c = item - item0;
+  const int n_chunks = p.item_start[b + 1] - item0;
+  const int chunk = p.header[1];
+  const SeqInfo si = seq_info(p, b);
+  const int len = si.len;
+  const int t_begin = c * chunk;
+  const int t_end = min(len, t_begin + chunk);
+
+  float* comb_o = reinterpret_cast<float*>(smem);          // [R][D]
+  float* comb_ml = comb_o + static_cast<size_t>(R) * D;    // [R][2]
+  const float* kg = static_cast<const float*>(p.k);
+  const float* vg = static_cast<const float*>(p.v);
+  const float* qg = static_cast<const float*>(p.q) +
+                    ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.group) * p.q_len) * D;
+  const float sl2 = p.scale_log2;
+
+  for (int r = warp; r < R; r += nwarps) {
+    float qv[VEC], acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) { qv[i] = qg[static_cast<long long>(r) * D + lane * VEC + i]; acc[i] = 0.f; }
+    const int lim = p.causal ? (len - p.q_len + (r % p.q_len)) : (len - 1);
+    const int stop = min(t_end, lim + 1);
+    float m = -INFINITY, l = 0.f;
+    for (int t = t_begin; t < stop; ++t) {
+      const long long ko = row_offset(p, p.k_table, b, h, si.start, t, D);
+      const long long vo = (p.layout == B200ATTN_PAGED) ? row_offset(p, p.v_table, b, h, si.start, t, D) : ko;
+      if (ko < 0 || vo < 0) {
+        if (lane == 0) p.header[0] = DEV_ERR_PAGE_RANGE;
+        continue;
+      }
+      float kv[VEC], vv[VEC];
+      if constexpr (VEC == 4) {
+        const float4 k4 = __ldg(reinterpret_cast<const float4*>(kg + ko) + lane);
+        const float4 v4 = __ldg(reinterpret_cast<const float4*>(vg + vo) + lane);
+        kv[0] = k4.x; kv[1] = k4.y; kv[2] = k4.z; kv[3] = k4.w;
+        vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
+      } else {
+        const float2 k2 = __ldg(reinterpret_cast<const float2*>(kg + ko) + lane);
+        const float2 v2 = __ldg(reinterpret_cast<const float2*>(vg + vo) + lane);
+        kv[0] = k2.x; kv[1] = k2.y;
+        vv[0] = v2.x; vv[1] = v2.y;
+      }
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) dot = fmaf(qv[i], kv[i], dot);
+      for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+      const float sc = dot * sl2;
+      const float mn = fmaxf(m, sc);
+      const float a = fast_exp2(m - mn);
+      const float pw = fast_exp2(sc - mn);
+      l = l * a + pw;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = fmaf(pw, vv[i], acc[i] * a);
+      m = mn;
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) comb_o[static_cast<size_t>(r) * D + lane * VEC + i] = acc[i];
+    if (lane == 0) { comb_ml[r * 2] = m; comb_ml[r * 2 + 1] = l; }
+  }
+  __syncthreads();
+  emit_and_merge<float, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, 1, R, &s_ticket);
+}
+
+template <typename K>
+int set_smem(K kernel, size_t bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(decode)");
+  return 0;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count) {
+  DecodeWsLayout w;
+  const int group = a.kv_heads > 0 ? a.q_heads / a.kv_heads : 1;
+  const int rows = group * a.q_len;
+  // about 6 resident-CTA waves of (item, kv head) pairs at 2 CTAs per SM
+  long long target = (static_cast<long long>(sm_count) * 2 * 6) / std::max(1, a.kv_heads);
+  if (target < 1) target = 1;
+  w.target_items = static_cast<int>(target);
+  // keep the partial write (rows x D fp32) small next to the chunk's K/V bytes
+  int min_chunk = 128;
+  const int by_rows = ((rows * 8 + kTileN - 1) / kTileN) * kTileN;
+  if (by_rows > min_chunk) min_chunk = by_rows;
+  w.min_chunk = min_chunk;
+  w.max_items = w.target_items + a.batch;
+  auto up = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
+  size_t off = kHeaderBytes;
+  w.item_start_off = off; off = up(off + sizeof(int) * (static_cast<size_t>(a.batch) + 1));
+  w.counters_off = off;   off = up(off + sizeof(int) * static_cast<size_t>(a.batch) * a.kv_heads);
+  const size_t slots = static_cast<size_t>(w.max_items) * a.kv_heads;
+  w.ml_off = off;         off = up(off + sizeof(float) * slots * rows * 2);
+  w.o_off = off;          off = up(off + sizeof(float) * slots * rows * a.head_dim);
+  w.total = off;
+  return w;
+}
+
+int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream) {
+  const DecodeWsLayout w = decode_ws_layout(a, sm_count);
+  if (a.workspace == nullptr || a.workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(a.workspace) & 255)) {
+    set_error("decode: workspace needs %zu bytes, 256-byte aligned (got %zu)", w.total, a.workspace_bytes);
+    return B200ATTN_E_WORKSPACE;
+  }
+  DecodeParams p;
+  p.q = a.q; p.k = a.k; p.v = a.v; p.out = a.out;
+  p.kv_indptr = a.kv_indptr; p.k_table = a.k_table; p.v_table = a.v_table;
+  unsigned char* ws = static_cast<unsigned char*>(a.workspace);
+  p.header = reinterpret_cast<int*>(ws);
+  p.item_start = reinterpret_cast<int*>(ws + w.item_start_off);
+  p.counters = reinterpret_cast<int*>(ws + w.counters_off);
+  p.part_ml = reinterpret_cast<float*>(ws + w.ml_off);
+  p.part_o = reinterpret_cast<float*>(ws + w.o_off);
+  p.total_kv = a.total_kv; p.table_stride = a.table_stride;
+  p.layout = a.layout; p.indptr_is_i64 = a.indptr_is_i64;
+  p.batch = a.batch; p.q_heads = a.q_heads; p.kv_heads = a.kv_heads;
+  p.group = a.q_heads / a.kv_heads; p.q_len = a.q_len; p.rows = p.group * a.q_len;
+  p.n_mtiles = (p.rows + 15) / 16;
+  p.max_kv = a.max_kv; p.page_size = a.layout == B200ATTN_PAGED ? a.page_size : 1;
+  p.page_shift = -1;
+  if (p.page_size > 0 && (p.page_size & (p.page_size - 1)) == 0) {
+    int s = 0; while ((1 << s) < p.page_size) ++s;
+    p.page_shift = s;
+  }
+  p.num_pages = a.layout == B200ATTN_PAGED ? static_cast<int>(std::min<long long>(a.total_kv / p.page_size, 0x7fffffff)) : 0;
+  p.causal = a.causal_drafts ? 1 : 0;
+  p.target_items = w.target_items; p.min_chunk = w.min_chunk; p.max_items = w.max_items;
+  p.scale_log2 = a.sm_scale * 1.4426950408889634f;
+
+  decode_plan_kernel<<<1, kPlanThreads, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "decode_plan_kernel launch");
+
+  const dim3 grid(w.max_items, a.kv_heads);
+  const int D = a.head_dim;
+  if (a.dtype == B200ATTN_F32) {
+    const size_t smem = sizeof(float) * static_cast<size_t>(p.rows) * (D + 2);
+    int rc = 0;
+    if (D == 128) { rc = set_smem(decode_simt_kernel<128>, smem); if (rc) return rc; decode_simt_kernel<128><<<grid, 128, smem, stream>>>(p); }
+    else          { rc = set_smem(decode_simt_kernel<64>, smem);  if (rc) return rc; decode_simt_kernel<64><<<grid, 128, smem, stream>>>(p); }
+  } else {
+    const int nmt = p.n_mtiles;
+    const int ksl = nmt == 1 ? 4 : (nmt <= 4 ? 2 : 1);
+    const int threads = 32 * nmt * ksl;
+    const size_t stage_bytes = static_cast<size_t>(kStages) * 2 * kTileN * D * 2;
+    const size_t comb_bytes = sizeof(float) * static_cast<size_t>(ksl) * nmt * 16 * (D + 2);
+    const size_t smem = static_cast<size_t>(nmt) * 16 * D * 2 + std::max(stage_bytes, comb_bytes);
+    int rc = 0;
+#define B200ATTN_LAUNCH_DECODE(TYPE, DIM)                                         \
+    do {                                                                          \
+      rc = set_smem(decode_mma_kernel<TYPE, DIM>, smem);                          \
+      if (rc) return rc;                                                          \
+      decode_mma_kernel<TYPE, DIM><<<grid, threads, smem, stream>>>(p);           \
+    } while (0)
+    if (a.dtype == B200ATTN_BF16) {
+      if (D == 128) B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 128); else B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 64);
+    } else {
+      if (D == 128) B200ATTN_LAUNCH_DECODE(__half, 128); else B200ATTN_LAUNCH_DECODE(__half, 64);
+    }
+#undef B200ATTN_LAUNCH_DECODE
+  }
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "decode kernel launch");
+  return B200ATTN_OK;
+}
+
+}  // namespace b200attn

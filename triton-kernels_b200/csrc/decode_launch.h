@@ -1,0 +1,61 @@
+// Host/device shared declarations for the decode path.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include "../../include/b200attn.h"
+
+namespace b200attn {
+
+// Kernel parameter block (passed by value).
+struct DecodeParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  const void* kv_indptr;
+  const int* k_table;
+  const int* v_table;
+  int* header;       // [0] error code, [1] chunk tokens, [2] number of work items
+  int* item_start;   // [batch + 1] prefix of per-sequence chunk counts
+  int* counters;     // [batch * kv_heads] merge tickets
+  float* part_ml;    // [slot][rows][2]  (running max in log2 units, running sum)
+  float* part_o;     // [slot][rows][D]  un-normalised accumulators
+  long long total_kv;
+  long long table_stride;
+  int layout;
+  int indptr_is_i64;
+  int batch;
+  int q_heads;
+  int kv_heads;
+  int group;         // q heads per kv head
+  int q_len;         // M
+  int rows;          // group * M: q rows that share one kv head
+  int n_mtiles;      // ceil(rows / 16)
+  int max_kv;
+  int page_size;
+  int page_shift;    // log2(page_size) or -1
+  int num_pages;
+  int causal;
+  int target_items;
+  int min_chunk;
+  int max_items;
+  float scale_log2;  // sm_scale * log2(e)
+};
+
+struct DecodeWsLayout {
+  size_t item_start_off;
+  size_t counters_off;
+  size_t ml_off;
+  size_t o_off;
+  size_t total;
+  int target_items;
+  int min_chunk;
+  int max_items;
+};
+
+DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count);
+int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream);
+
+}  // namespace b200attn

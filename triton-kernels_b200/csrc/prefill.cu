@@ -1,0 +1,724 @@
+// Prefill attention forward for sm_100a: tcgen05 tensor cores, TMEM accumulators,
+// TMA-staged K/V ring, online softmax in registers.
+//
+// Replaces the reference's partial + merge launch pair (kernels/attention.py:430-746).
+//
+// One CTA owns two 128-row query tiles of one (sequence, q head) ("slots").
+// Warp roles (384 threads):
+//   warps 0-3  : softmax warpgroup of slot 0 (thread i owns query row i)
+//   warps 4-7  : softmax warpgroup of slot 1
+//   warp  8    : TMA producer (Q once, then K_j / V_j tiles of 128 keys through a 4-buffer ring;
+//                paged caches are fetched one page-sized box at a time from the block table)
+//   warp  9    : tcgen05.mma issuer (lane 0) and TMEM owner
+// TMEM (512 columns): S0 | S1 | O0 | O1.  Per KV tile j and slot s:
+//   S_s = Q_s K_j^T   (SS MMA, 128x128xD)            -> commit s_full[s]
+//   softmax WG s reads S_s (one row per thread), masks, keeps a running max / sum in the exp2
+//   domain, rescales O_s in TMEM only when the max moved by more than 2^8, writes P_s as
+//   packed 16-bit into the first 64 columns of S_s                -> arrive p_ready[s]
+//   O_s += P_s V_j    (TS MMA, A from TMEM, V is the MN-major B operand) -> commit o_done[s]
+// The two slots are interleaved so that one slot's softmax overlaps the other's MMAs.
+// The epilogue normalises O by the row sum, stages it in the (now dead) Q buffer and
+// writes rows < seq_len_q with coalesced 16-byte stores.
+//
+// Every mbarrier wait is bounded; on expiry the role records DEV_ERR_WAIT_EXPIRED
+// in the workspace header and falls through to the common teardown (TMEM is freed).
+#include <algorithm>
+#include <mutex>
+#include <type_traits>
+
+#include "common.cuh"
+#include "prefill_launch.h"
+#include "sm100_ptx.cuh"
+
+namespace b200attn {
+
+namespace {
+
+using namespace ptx;
+
+constexpr int kBM = 128;           // query rows per slot
+constexpr int kBN = 128;           // keys per tile
+constexpr int kSlots = 2;
+constexpr int kRing = 4;           // K/V ring buffers (K_j, V_j alternate)
+constexpr int kThreads = 384;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct CtaWork {
+  int b;
+  int pair;          // index of the 256-row query block inside the sequence
+  int len_q;
+  int len_k;
+  long long q_row0;  // first q row of the sequence in the q tensor map's token axis
+  long long kv_row0; // first kv row of the sequence (dense / ragged)
+  int q_head_coord;  // head coordinate in the q tensor map
+  int kv_head_coord;
+};
+
+// shared-memory control block placed after the tiles
+struct __align__(8) Control {
+  uint64_t q_full;
+  uint64_t kv_full[kRing];
+  uint64_t kv_empty[kRing];
+  uint64_t s_full[kSlots];
+  uint64_t p_ready[kSlots];
+  uint64_t o_done[kSlots];
+  uint32_t tmem_base;
+  int work_b;
+  int work_pair;
+  int abort_flag;
+};
+
+template <int D>
+struct SmemPlan {
+  static constexpr int kChunks = D / 64;                   // 128-byte column blocks per row
+  static constexpr int kChunkBytes = kBN * 128;            // one column block of a 128-row tile
+  static constexpr int kTileBytes = kChunks * kChunkBytes; // 128 x D 16-bit tile
+  static constexpr int kQOff = 0;
+  static constexpr int kRingOff = kSlots * kTileBytes;
+  static constexpr int kCtrlOff = kRingOff + kRing * kTileBytes;
+  static constexpr int kTotal = kCtrlOff + static_cast<int>(sizeof(Control));
+};
+
+// bounded mbarrier wait whose verdict is uniform over the (converged) warp
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
+  const bool ok = mbar_wait(bar, parity);
+  return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ int pairs_of(int len_q) { return (len_q + 2 * kBM - 1) / (2 * kBM); }
+
+// Ragged layout: warp-cooperative search of the (sequence, pair) that owns flat pair index x.
+__device__ __forceinline__ bool find_ragged_work(const PrefillParams& p, int x, int lane, int* out_b, int* out_pair) {
+  int base = 0;
+  for (int b0 = 0; b0 < p.batch; b0 += 32) {
+    const int b = b0 + lane;
+    int cnt = 0;
+    if (b < p.batch) {
+      const long long a = load_index(p.q_indptr, p.indptr_is_i64, b);
+      const long long e = load_index(p.q_indptr, p.indptr_is_i64, b + 1);
+      const long long n = e > a ? e - a : 0;
+      cnt = pairs_of(static_cast<int>(n));
+    }
+    int incl = cnt;
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    const int excl = incl - cnt;
+    const bool hit = (x >= base + excl) && (x < base + incl);
+    const unsigned mask = __ballot_sync(0xffffffffu, hit);
+    if (mask) {
+      const int src = __ffs(mask) - 1;
+      *out_b = b0 + src;
+      *out_pair = x - (base + __shfl_sync(0xffffffffu, excl, src));
+      return true;
+    }
+    base += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  return false;
+}
+
+// fp32 inputs: q, k and v are first rounded to fp16 into the workspace (the reference's kernel does the
+// same cast in registers, kernels/attention.py:547,572,594,614) and the result is written back as fp32.
+__global__ void __launch_bounds__(256) cast_f32_to_f16_kernel(const float4* __restrict__ src, uint2* __restrict__ dst,
+                                                              long long n4) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float4 f = __ldg(src + i);
+    uint2 u;
+    u.x = ElemTraits<__half>::pack2(f.x, f.y);
+    u.y = ElemTraits<__half>::pack2(f.z, f.w);
+    dst[i] = u;
+  }
+}
+
+template <typename T, int D, typename OutT>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
+  using Plan = SmemPlan<D>;
+  extern __shared__ unsigned char smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte alignment
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  Control* ctrl = reinterpret_cast<Control*>(smem + Plan::kCtrlOff);
+  const uint32_t smem_base = smem_u32(smem);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  // ---------------- which (sequence, q head, 256-row block) is this CTA? ----------------
+  if (warp == 0) {
+    int wb = -1, wpair = 0;
+    if (p.layout == B200ATTN_RAGGED) {
+      if (!find_ragged_work(p, blockIdx.x, lane, &wb, &wpair)) wb = -1;
+    } else {
+      wb = blockIdx.z;
+      const int npairs = pairs_of(p.max_q);
+      // causal: heaviest (last) blocks are scheduled first
+      wpair = p.is_causal ? (npairs - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
+    }
+    if (lane == 0) { ctrl->work_b = wb; ctrl->work_pair = wpair; ctrl->abort_flag = 0; }
+  }
+  if (tid == 0) {
+    mbar_init(smem_u32(&ctrl->q_full), 1);
+    for (int i = 0; i < kRing; ++i) { mbar_init(smem_u32(&ctrl->kv_full[i]), 1); mbar_init(smem_u32(&ctrl->kv_empty[i]), 1); }
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(smem_u32(&ctrl->s_full[s]), 1);
+      mbar_init(smem_u32(&ctrl->p_ready[s]), kBM);
+      mbar_init(smem_u32(&ctrl->o_done[s]), 1);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  CtaWork w;
+  w.b = ctrl->work_b;
+  w.pair = ctrl->work_pair;
+  if (w.b < 0) return;  // whole CTA: nothing allocated yet
+
+  const int q_head = blockIdx.y;
+  const int kv_head = q_head / p.group;
+  if (p.layout == B200ATTN_RAGGED) {
+    const long long qa = load_index(p.q_indptr, p.indptr_is_i64, w.b);
+    const long long qe = load_index(p.q_indptr, p.indptr_is_i64, w.b + 1);
+    const long long ka = load_index(p.kv_indptr, p.indptr_is_i64, w.b);
+    const long long ke = load_index(p.kv_indptr, p.indptr_is_i64, w.b + 1);
+    w.len_q = static_cast<int>(qe > qa ? qe - qa : 0);
+    w.len_k = static_cast<int>(ke > ka ? ke - ka : 0);
+    w.q_row0 = qa;
+    w.kv_row0 = ka;
+    w.q_head_coord = q_head;
+    w.kv_head_coord = kv_head;
+  } else {
+    w.len_q = p.max_q;
+    w.q_row0 = (static_cast<long long>(w.b) * p.q_heads + q_head) * p.max_q;
+    w.q_head_coord = 0;
+    if (p.layout == B200ATTN_DENSE) {
+      w.len_k = p.max_kv;
+      w.kv_row0 = (static_cast<long long>(w.b) * p.kv_heads + kv_head) * p.max_kv;
+      w.kv_head_coord = 0;
+    } else {
+      long long n = load_index(p.kv_indptr, p.indptr_is_i64, w.b);
+      const long long cap = p.table_stride * static_cast<long long>(p.page_size);
+      n = n < 0 ? 0 : (n > cap ? cap : n);
+      w.len_k = static_cast<int>(n);
+      w.kv_row0 = 0;
+      w.kv_head_coord = kv_head;
+    }
+  }
+
+  // per-slot extents
+  int m0[kSlots], nkv[kSlots];
+  int nkv_max = 0;
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+    m0[s] = (w.pair * kSlots + s) * kBM;
+    int n = 0;
+    if (m0[s] < w.len_q) {
+      int kv_hi = w.len_k;
+      if (p.is_causal) kv_hi = min(kv_hi, min(m0[s] + kBM, w.len_q));
+      n = (kv_hi + kBN - 1) / kBN;
+    }
+    nkv[s] = n;
+    nkv_max = max(nkv_max, n);
+  }
+
+  // ---------------- TMEM allocation (MMA warp owns it) ----------------
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctrl->tmem_base;
+  const uint32_t tmem_S[kSlots] = {tmem, tmem + kBN};
+  const uint32_t tmem_O[kSlots] = {tmem + 2 * kBN, tmem + 2 * kBN + D};
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  if (warp == kProducerWarp) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) { prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); }
+    bool ok = true;
+    if (lane == 0) {
+      uint32_t bytes = 0;
+      for (int s = 0; s < kSlots; ++s) if (nkv[s] > 0) bytes += Plan::kTileBytes;
+      if (bytes > 0) {
+        mbar_arrive_expect_tx(smem_u32(&ctrl->q_full), bytes);
+        for (int s = 0; s < kSlots; ++s) {
+          if (nkv[s] == 0) continue;
+          for (int c = 0; c < Plan::kChunks; ++c)
+            tma_load_3d(smem_base + Plan::kQOff + s * Plan::kTileBytes + c * Plan::kChunkBytes, &tm_q,
+                        smem_u32(&ctrl->q_full), c * 64, w.q_head_coord, static_cast<int>(w.q_row0 + m0[s]));
+        }
+      }
+    }
+    int issued = 0;
+    for (int e = 0; e < 2 * nkv_max && ok; ++e) {
+      const int j = e >> 1;
+      const bool is_v = e & 1;
+      const int buf = e % kRing;
+      const int use = e / kRing;
+      if (use > 0) {
+        ok = warp_wait(smem_u32(&ctrl->kv_empty[buf]), (use - 1) & 1);
+        if (!ok || *abort_flag) { ok = false; break; }
+      }
+      const uint32_t dst = smem_base + Plan::kRingOff + buf * Plan::kTileBytes;
+      const uint32_t bar = smem_u32(&ctrl->kv_full[buf]);
+      const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+      if (p.layout != B200ATTN_PAGED) {
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar, Plan::kTileBytes);
+          for (int c = 0; c < Plan::kChunks; ++c)
+            tma_load_3d(dst + c * Plan::kChunkBytes, tm, bar, c * 64, w.kv_head_coord,
+                        static_cast<int>(w.kv_row0 + static_cast<long long>(j) * kBN));
+        }
+      } else {
+        // one box of `box_rows` tokens per lane per round; only pages that exist are fetched
+        const int* table = (is_v ? p.v_table : p.k_table) + static_cast<long long>(w.b) * p.table_stride;
+        const int boxes = kBN / p.box_rows;
+        int my_rows[4];
+        int nmine = 0;
+        int count = 0;
+        for (int i = lane; i < boxes; i += 32) {
+          const int t = j * kBN + i * p.box_rows;
+          int row = -1;
+          if (t < w.len_k) {
+            const int lp = t / p.page_size;
+            const int page = __ldg(table + lp);
+            if (page >= 0 && page < p.num_pages) row = page * p.page_size + (t - lp * p.page_size);
+            else p.header[0] = DEV_ERR_PAGE_RANGE;
+          }
+          my_rows[nmine++] = row;
+          if (row >= 0) ++count;
+        }
+        for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
+        if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * p.box_rows * 128 * Plan::kChunks);
+        __syncwarp();
+        int k = 0;
+        for (int i = lane; i < boxes; i += 32, ++k) {
+          const int row = my_rows[k];
+          if (row < 0) continue;
+          for (int c = 0; c < Plan::kChunks; ++c)
+            tma_load_3d(dst + c * Plan::kChunkBytes + i * p.box_rows * 128, tm, bar, c * 64, w.kv_head_coord, row);
+        }
+      }
+      issued = e + 1;
+    }
+    if (!ok) {
+      if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
+      // drain: wait (bounded) for the copies still in flight before the CTA may exit
+      for (int e = max(0, issued - kRing); e < issued; ++e) mbar_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
+    }
+  } else if (warp == kMmaWarp) {
+    // =========================== MMA issuer ===========================
+    constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+    constexpr uint32_t idesc_s = make_idesc_f16(kBM, kBN, kFmt, 0);
+    constexpr uint32_t idesc_o = make_idesc_f16(kBM, D, kFmt, 1);
+    bool ok = true;
+    auto ring_full_wait = [&](int e) -> bool {
+      return warp_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
+    };
+    auto issue_s = [&](int s, int j) {
+      // S_s = Q_s K_j^T : K-major A and B, D/16 k-steps
+      if (lane == 0) {
+        const uint32_t qa = smem_base + Plan::kQOff + s * Plan::kTileBytes;
+        const uint32_t kb = smem_base + Plan::kRingOff + ((2 * j) % kRing) * Plan::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = (kk >> 2) * Plan::kChunkBytes + (kk & 3) * 32;
+          mma_ss(tmem_S[s], make_smem_desc_sw128(qa + off, 16), make_smem_desc_sw128(kb + off, 16), idesc_s, kk > 0);
+        }
+        mma_commit(smem_u32(&ctrl->s_full[s]));
+      }
+      __syncwarp();
+    };
+    auto issue_pv = [&](int s, int j) {
+      // O_s (+)= P_s V_j : A = packed 16-bit P in TMEM (8 columns per k-step), B = V, MN-major
+      if (lane == 0) {
+        const uint32_t vb = smem_base + Plan::kRingOff + ((2 * j + 1) % kRing) * Plan::kTileBytes;
+#pragma unroll
+        for (int kk = 0; kk < kBN / 16; ++kk) {
+          mma_ts(tmem_O[s], tmem_S[s] + kk * 8, make_smem_desc_sw128(vb + kk * 16 * 128, Plan::kChunkBytes), idesc_o,
+                 (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(smem_u32(&ctrl->o_done[s]));
+      }
+      __syncwarp();
+    };
+
+    if (nkv_max > 0) {
+      ok = warp_wait(smem_u32(&ctrl->q_full), 0) && ring_full_wait(0);
+      if (ok) {
+        tc_fence_after();
+        for (int s = 0; s < kSlots; ++s) if (nkv[s] > 0) issue_s(s, 0);
+        if (lane == 0) mma_commit(smem_u32(&ctrl->kv_empty[0]));
+      }
+    }
+    for (int j = 0; j < nkv_max && ok; ++j) {
+      bool v_ready = false;
+      for (int s = 0; s < kSlots && ok; ++s) {
+        if (j >= nkv[s]) continue;
+        ok = warp_wait(smem_u32(&ctrl->p_ready[s]), j & 1);
+        if (!ok) break;
+        if (!v_ready) {
+          ok = ring_full_wait(2 * j + 1);
+          if (!ok) break;
+          v_ready = true;
+          const int valid = w.len_k - j * kBN;
+          if (valid < kBN) {
+            // keys past the sequence end carry P == 0 but their V rows may hold anything (stale
+            // shared memory, the next sequence, poisoned page tails): zero them so 0 * x stays 0
+            unsigned char* vbuf = smem + Plan::kRingOff + ((2 * j + 1) % kRing) * Plan::kTileBytes;
+            const int first = valid > 0 ? valid : 0;
+            const int n16 = (kBN - first) * 8;  // 16-byte pieces per column block
+            for (int c = 0; c < Plan::kChunks; ++c) {
+              uint4* dst = reinterpret_cast<uint4*>(vbuf + c * Plan::kChunkBytes + first * 128);
+              for (int i = lane; i < n16; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+        }
+        tc_fence_after();
+        issue_pv(s, j);
+        if (j + 1 < nkv[s]) {
+          ok = ring_full_wait(2 * (j + 1));
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(s, j + 1);
+        }
+      }
+      if (!ok) break;
+      if (lane == 0) {
+        mma_commit(smem_u32(&ctrl->kv_empty[(2 * j + 1) % kRing]));
+        if (j + 1 < nkv_max) mma_commit(smem_u32(&ctrl->kv_empty[(2 * j + 2) % kRing]));
+      }
+      __syncwarp();
+    }
+    if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
+  } else if (warp < kSlots * 4) {
+    // =========================== softmax warpgroups ===========================
+    const int s = warp >> 2;
+    const int row = tid - s * kBM;                      // 0..127 inside the slot
+    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem_S[s] + lane_off;
+    const uint32_t tO = tmem_O[s] + lane_off;
+    const int row_abs = m0[s] + row;                    // query index inside the sequence
+    const int n = nkv[s];
+    const float sl2 = p.scale_log2;
+    float m_used = -INFINITY;   // exponent reference currently baked into O and l
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      ok = warp_wait(smem_u32(&ctrl->s_full[s]), j & 1);
+      if (!ok || *abort_flag) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[kBN];
+#pragma unroll
+      for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
+      tmem_wait_ld();
+      // masking is needed only on the tile that holds the sequence end or the causal diagonal
+      int limit = w.len_k - 1 - j * kBN;
+      if (p.is_causal) limit = min(limit, row_abs - j * kBN);
+      float mx = -INFINITY;
+      if (limit < kBN - 1) {
+#pragma unroll
+        for (int c = 0; c < kBN; ++c) {
+          const float x = (c <= limit) ? __uint_as_float(sv[c]) : -INFINITY;
+          sv[c] = __float_as_uint(x);
+          mx = fmaxf(mx, x);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < kBN; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+      }
+      const float m_new = fmaxf(m_used, mx * sl2);
+      const bool need = (m_new - m_used) > kRescaleThreshold;   // false for NaN / (-inf)-(-inf)
+      float alpha = 1.f;
+      if (need) { alpha = fast_exp2(m_used - m_new); m_used = m_new; l *= alpha; }
+      if (j > 0) {
+        // PV(j-1) must have landed in O before it is touched (always true once S(j) is visible,
+        // the wait keeps the barrier phase in step)
+        ok = warp_wait(smem_u32(&ctrl->o_done[s]), (j - 1) & 1);
+        if (!ok) break;
+        if (__any_sync(0xffffffffu, need)) {
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t ov[32];
+            tmem_ld32(tO + c * 32, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st32(tO + c * 32, ov);
+          }
+        }
+      }
+      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+      const float neg_m = -m_eff;
+      float rs = 0.f;
+#pragma unroll
+      for (int c = 0; c < kBN / 64; ++c) {
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c * 64 + 2 * i]), sl2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c * 64 + 2 * i + 1]), sl2, neg_m));
+          rs += p0 + p1;
+          pk[i] = ElemTraits<T>::pack2(p0, p1);
+        }
+        tmem_st32(tS + c * 32, pk);
+      }
+      l += rs;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctrl->p_ready[s]));
+    }
+    // ---------------- epilogue ----------------
+    if (ok && n > 0) ok = warp_wait(smem_u32(&ctrl->o_done[s]), (n - 1) & 1);
+    if (!ok) {
+      if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
+    } else if (m0[s] < w.len_q) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int rows_valid = min(kBM, w.len_q - m0[s]);
+      if constexpr (std::is_same<OutT, float>::value) {
+        // fp32 output: every thread stores its own row, 128 contiguous bytes per TMEM chunk
+        float* out = static_cast<float*>(p.out);
+        long long off;
+        if (p.layout == B200ATTN_RAGGED) off = ((w.q_row0 + m0[s] + row) * p.q_heads + q_head) * D;
+        else off = (w.q_row0 + m0[s] + row) * D;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t ov[32];
+          if (n > 0) {
+            tmem_ld32(tO + c * 32, ov);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = 0u;
+          }
+          if (row < rows_valid) {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              *reinterpret_cast<float4*>(out + off + c * 32 + q4 * 4) =
+                  make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
+                              __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
+          }
+        }
+      } else {
+        unsigned char* stage = smem + Plan::kQOff + s * Plan::kTileBytes;  // [128][D] 16-bit, 16-byte pieces XOR-swizzled
+        constexpr int kPieces = D * 2 / 16;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t ov[32];
+          if (n > 0) {
+            tmem_ld32(tO + c * 32, ov);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = 0u;
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 u;
+            u.x = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
+            u.y = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
+            u.z = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
+            u.w = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
+            const int piece = c * 4 + q4;
+            *reinterpret_cast<uint4*>(stage + row * (D * 2) + ((piece ^ (row & 7)) << 4)) = u;
+          }
+        }
+        __syncwarp();
+        // coalesced write-out of this warp's own 32 rows: kPieces lanes cover one row
+        T* out = static_cast<T*>(p.out);
+        constexpr int kRowsPerPass = 32 / kPieces;
+        const int piece = lane % kPieces;
+        const int wrow0 = (warp & 3) * 32;
+        for (int rr = lane / kPieces; rr < 32; rr += kRowsPerPass) {
+          const int r = wrow0 + rr;
+          if (r >= rows_valid) break;
+          const uint4 u = *reinterpret_cast<const uint4*>(stage + r * (D * 2) + ((piece ^ (r & 7)) << 4));
+          long long off;
+          if (p.layout == B200ATTN_RAGGED) off = ((w.q_row0 + m0[s] + r) * p.q_heads + q_head) * D;
+          else off = (w.q_row0 + m0[s] + r) * D;
+          *reinterpret_cast<uint4*>(out + off + piece * 8) = u;
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side: tensor maps
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// 3-D map over a [tokens][heads][D] (heads == 1 for per-head-contiguous dense tensors) 16-bit tensor,
+// box = 64 elements x 1 head x box_rows tokens, 128-byte swizzle, zero fill out of bounds.
+int make_map(CUtensorMap* m, int dtype, const void* base, long long tokens, int heads, int D, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return B200ATTN_E_CUDA; }
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(tokens)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(D) * 2 * heads};
+  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt = dtype == B200ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (tokens=%lld heads=%d D=%d box_rows=%d)", static_cast<int>(r),
+              tokens, heads, D, box_rows);
+    return B200ATTN_E_CUDA;
+  }
+  return 0;
+}
+
+}  // namespace
+
+namespace {
+struct CastPlan {
+  size_t q_elems, kv_elems, q_off, k_off, v_off, total;
+};
+CastPlan cast_plan(const b200attn_prefill_args_t& a) {
+  CastPlan c{};
+  auto up = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
+  const size_t D = static_cast<size_t>(a.head_dim);
+  if (a.layout == B200ATTN_RAGGED) {
+    c.q_elems = static_cast<size_t>(a.total_q) * a.q_heads * D;
+    c.kv_elems = static_cast<size_t>(a.total_kv) * a.kv_heads * D;
+  } else {
+    c.q_elems = static_cast<size_t>(a.batch) * a.q_heads * a.max_q * D;
+    c.kv_elems = a.layout == B200ATTN_DENSE ? static_cast<size_t>(a.batch) * a.kv_heads * a.max_kv * D
+                                            : static_cast<size_t>(a.total_kv) * a.kv_heads * D;
+  }
+  c.q_off = kHeaderBytes;
+  c.k_off = up(c.q_off + c.q_elems * 2);
+  c.v_off = up(c.k_off + c.kv_elems * 2);
+  c.total = up(c.v_off + c.kv_elems * 2);
+  return c;
+}
+}  // namespace
+
+size_t prefill_workspace_bytes(const b200attn_prefill_args_t& a) {
+  if (a.dtype == B200ATTN_F32) return cast_plan(a).total;
+  return kHeaderBytes;
+}
+
+int launch_prefill(const b200attn_prefill_args_t& a_in, cudaStream_t stream) {
+  const size_t need = prefill_workspace_bytes(a_in);
+  if (a_in.workspace == nullptr || a_in.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a_in.workspace) & 255)) {
+    set_error("prefill: workspace needs %zu bytes, 256-byte aligned (got %zu)", need, a_in.workspace_bytes);
+    return B200ATTN_E_WORKSPACE;
+  }
+  b200attn_prefill_args_t a = a_in;
+  const bool f32 = a_in.dtype == B200ATTN_F32;
+  if (f32) {
+    const CastPlan c = cast_plan(a_in);
+    unsigned char* ws = static_cast<unsigned char*>(a_in.workspace);
+    const void* src[3] = {a_in.q, a_in.k, a_in.v};
+    const size_t off[3] = {c.q_off, c.k_off, c.v_off};
+    const size_t cnt[3] = {c.q_elems, c.kv_elems, c.kv_elems};
+    for (int i = 0; i < 3; ++i) {
+      const long long n4 = static_cast<long long>(cnt[i] / 4);  // head_dim is a multiple of 4
+      if (n4 == 0) continue;
+      const int blocks = static_cast<int>(std::min<long long>((n4 + 255) / 256, 148 * 16));
+      cast_f32_to_f16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4*>(src[i]),
+                                                         reinterpret_cast<uint2*>(ws + off[i]), n4);
+    }
+    cudaError_t ce = cudaGetLastError();
+    if (ce != cudaSuccess) return cuda_fail(ce, "cast kernel launch");
+    a.q = ws + c.q_off; a.k = ws + c.k_off; a.v = ws + c.v_off;
+    a.dtype = B200ATTN_F16;
+  }
+  const int D = a.head_dim;
+  PrefillParams p;
+  p.out = a.out; p.q_indptr = a.q_indptr; p.kv_indptr = a.kv_indptr;
+  p.k_table = a.k_table; p.v_table = a.v_table;
+  p.header = static_cast<int*>(a.workspace);
+  p.table_stride = a.table_stride;
+  p.layout = a.layout; p.indptr_is_i64 = a.indptr_is_i64;
+  p.batch = a.batch; p.q_heads = a.q_heads; p.kv_heads = a.kv_heads; p.group = a.q_heads / a.kv_heads;
+  p.max_q = a.max_q; p.max_kv = a.max_kv;
+  p.page_size = a.layout == B200ATTN_PAGED ? a.page_size : 1;
+  p.box_rows = kBN;
+  p.num_pages = 0;
+  p.is_causal = a.is_causal ? 1 : 0;
+  p.scale_log2 = a.sm_scale * 1.4426950408889634f;
+
+  CUtensorMap tq, tk, tv;
+  int rc;
+  dim3 grid;
+  if (a.layout == B200ATTN_RAGGED) {
+    if ((rc = make_map(&tq, a.dtype, a.q, a.total_q, a.q_heads, D, kBM))) return rc;
+    if ((rc = make_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, kBN))) return rc;
+    if ((rc = make_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, kBN))) return rc;
+    const long long pairs = a.total_q / (2 * kBM) + a.batch;
+    grid = dim3(static_cast<unsigned>(pairs), a.q_heads, 1);
+  } else {
+    const long long q_rows = static_cast<long long>(a.batch) * a.q_heads * a.max_q;
+    if ((rc = make_map(&tq, a.dtype, a.q, q_rows, 1, D, kBM))) return rc;
+    if (a.layout == B200ATTN_DENSE) {
+      const long long kv_rows = static_cast<long long>(a.batch) * a.kv_heads * a.max_kv;
+      if ((rc = make_map(&tk, a.dtype, a.k, kv_rows, 1, D, kBN))) return rc;
+      if ((rc = make_map(&tv, a.dtype, a.v, kv_rows, 1, D, kBN))) return rc;
+    } else {
+      // largest power of two that divides the page size, capped at the tile: every box stays inside one page
+      int box = 1;
+      while (box < kBN && (a.page_size % (box * 2)) == 0) box *= 2;
+      p.box_rows = box;
+      p.num_pages = static_cast<int>(std::min<long long>(a.total_kv / a.page_size, 0x7fffffff));
+      if ((rc = make_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box))) return rc;
+      if ((rc = make_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box))) return rc;
+    }
+    grid = dim3((a.max_q + 2 * kBM - 1) / (2 * kBM), a.q_heads, a.batch);
+  }
+  if (grid.x == 0 || grid.y == 0 || grid.z == 0) return B200ATTN_OK;
+
+  cudaError_t e;
+#define B200ATTN_LAUNCH_PREFILL(TYPE, DIM, OUT)                                                          \
+  do {                                                                                                   \
+    const size_t smem = std::max<size_t>(SmemPlan<DIM>::kTotal + 1024, 120 * 1024);                      \
+    e = cudaFuncSetAttribute(prefill_kernel<TYPE, DIM, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,\
+                             static_cast<int>(smem));                                                    \
+    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(prefill)");                          \
+    prefill_kernel<TYPE, DIM, OUT><<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);                     \
+  } while (0)
+  if (f32) {
+    if (D == 128) B200ATTN_LAUNCH_PREFILL(__half, 128, float); else B200ATTN_LAUNCH_PREFILL(__half, 64, float);
+  } else if (a.dtype == B200ATTN_BF16) {
+    if (D == 128) B200ATTN_LAUNCH_PREFILL(__nv_bfloat16, 128, __nv_bfloat16); else B200ATTN_LAUNCH_PREFILL(__nv_bfloat16, 64, __nv_bfloat16);
+  } else {
+    if (D == 128) B200ATTN_LAUNCH_PREFILL(__half, 128, __half); else B200ATTN_LAUNCH_PREFILL(__half, 64, __half);
+  }
+#undef B200ATTN_LAUNCH_PREFILL
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "prefill kernel launch");
+  return B200ATTN_OK;
+}
+
+}  // namespace b200attn

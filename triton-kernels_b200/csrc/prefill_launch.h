@@ -1,0 +1,37 @@
+// Host/device shared declarations for the prefill path.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include "../../include/b200attn.h"
+
+namespace b200attn {
+
+struct PrefillParams {
+  void* out;
+  const void* q_indptr;
+  const void* kv_indptr;
+  const int* k_table;
+  const int* v_table;
+  int* header;          // workspace header, word 0 = device error code
+  long long table_stride;
+  int layout;
+  int indptr_is_i64;
+  int batch;
+  int q_heads;
+  int kv_heads;
+  int group;
+  int max_q;
+  int max_kv;
+  int page_size;
+  int box_rows;         // tokens per TMA box of a paged cache
+  int num_pages;
+  int is_causal;
+  float scale_log2;
+};
+
+size_t prefill_workspace_bytes(const b200attn_prefill_args_t& a);
+int launch_prefill(const b200attn_prefill_args_t& a, cudaStream_t stream);
+
+}  // namespace b200attn

@@ -1,0 +1,17 @@
+"""B200-native attention kernels behind the reference's public names
+(kernels/__init__.py:1-51 of the reference; only the attention hot path is provided)."""
+from .attention import (
+    flash_attention_v1,
+    flash_attention_v2,
+)
+from .decode import decode_attention
+from .speculative_decode import (
+    speculative_decode_attention,
+)
+
+__all__ = [
+    "flash_attention_v1",
+    "flash_attention_v2",
+    "speculative_decode_attention",
+    "decode_attention",
+]

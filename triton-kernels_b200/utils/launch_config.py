@@ -1,0 +1,69 @@
+"""Launch planning for the attention path.
+
+Pure-Python mirrors of the planning rules compiled into ``libb200attn.so``
+(csrc/decode.cu ``decode_ws_layout`` / ``decode_plan_kernel`` and the prefill
+grid in csrc/prefill.cu).  They replace the reference's split heuristics
+(kernels/attention.py:836-841, kernels/decode.py:271-278,
+kernels/speculative_decode.py:301-309) and let the planning be unit-tested
+without a GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence
+
+DECODE_TILE_TOKENS = 64       # keys per cp.async stage
+PREFILL_BLOCK_M = 128         # query rows per tensor-core tile
+PREFILL_SLOTS = 2             # query tiles per CTA
+PREFILL_BLOCK_N = 128         # keys per tile
+
+
+@dataclass
+class DecodePlan:
+    target_items: int
+    min_chunk: int
+    max_items: int
+    mma_tiles: int     # 16-row MMA tiles that hold group x q_len rows
+    key_slices: int    # warps that split the keys of one stage
+    threads: int
+
+
+def decode_plan(sm_count: int, batch: int, q_heads: int, kv_heads: int, q_len: int) -> DecodePlan:
+    group = q_heads // kv_heads
+    rows = group * q_len
+    target = max(1, (sm_count * 2 * 6) // max(1, kv_heads))
+    by_rows = -(-(rows * 8) // DECODE_TILE_TOKENS) * DECODE_TILE_TOKENS
+    min_chunk = max(128, by_rows)
+    tiles = -(-rows // 16)
+    slices = 4 if tiles == 1 else (2 if tiles <= 4 else 1)
+    return DecodePlan(target, min_chunk, target + batch, tiles, slices, 32 * tiles * slices)
+
+
+def decode_chunk_tokens(plan: DecodePlan, lengths: Sequence[int]) -> int:
+    """Chunk size the device planner picks for these lengths."""
+    total = sum(max(0, int(n)) for n in lengths)
+    per = -(-total // plan.target_items)
+    per = -(-per // DECODE_TILE_TOKENS) * DECODE_TILE_TOKENS
+    return max(per, plan.min_chunk)
+
+
+def decode_items(plan: DecodePlan, lengths: Sequence[int]) -> List[int]:
+    """Work items (KV chunks) per sequence; their sum never exceeds plan.max_items."""
+    chunk = decode_chunk_tokens(plan, lengths)
+    return [max(1, -(-max(0, int(n)) // chunk)) for n in lengths]
+
+
+def prefill_ctas(layout: str, batch: int, q_heads: int, max_q: int = 0, total_q: int = 0) -> int:
+    """CTAs launched by the prefill kernel (each owns PREFILL_SLOTS x PREFILL_BLOCK_M query rows)."""
+    rows = PREFILL_BLOCK_M * PREFILL_SLOTS
+    if layout == "ragged":
+        return (total_q // rows + batch) * q_heads
+    return -(-max_q // rows) * q_heads * batch
+
+
+def paged_box_rows(page_size: int) -> int:
+    """Tokens per TMA box for a paged cache: the largest power of two dividing the page size, at most one tile."""
+    box = 1
+    while box < PREFILL_BLOCK_N and page_size % (box * 2) == 0:
+        box *= 2
+    return box
