@@ -61,12 +61,20 @@ def make_rngs(*parts):
     return random.Random(s), torch.Generator().manual_seed(s)
 
 
-def assert_close_both(out, ref, dtype, n_kv, what=""):
-    """The reference tolerance (atol = base*sqrt(N)+eps, rtol) and the stricter un-scaled max-abs bar."""
+# fp32 prefill multiplies in fp16 on the tensor cores, exactly as the reference kernel does (it casts
+# q, k, v and p to fp16 whatever the input dtype: kernels/attention.py:547,572,594,607,614), so its
+# un-scaled bar is the 16-bit class one; fp32 decode uses fp32 FMAs and keeps the 1e-3 bar.
+PREFILL_F32_STRICT = 4e-3
+
+
+def assert_close_both(out, ref, dtype, n_kv, what="", strict=None):
+    """The reference tolerance (atol = base*sqrt(N)+eps, rtol) and the stricter un-scaled max-abs bar
+    (bf16 2e-2, fp16 1e-2, fp32 1e-3 unless `strict` overrides it)."""
     from oracle.sdpa_ref import attn_tolerances, strict_max_abs
 
     out = out.float().cpu()
     ref = ref.float().cpu()
     torch.testing.assert_close(out, ref, **attn_tolerances(dtype, n_kv), msg=lambda m: f"{what}: {m}")
     err = (out - ref).abs().max().item() if out.numel() else 0.0
-    assert err <= strict_max_abs(dtype), f"{what}: max-abs {err:.3e} exceeds strict bar {strict_max_abs(dtype):.1e}"
+    bar = strict if strict is not None else strict_max_abs(dtype)
+    assert err <= bar, f"{what}: max-abs {err:.3e} exceeds strict bar {bar:.1e}"

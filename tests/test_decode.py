@@ -35,7 +35,7 @@ def run_decode(layout, qs, ks, vs, kv_lens, *, index_dtype=torch.int32, permute=
     kc, kt, lens = sdpa_ref.pack_paged(ks, page_size, permute_seed=permute, extra_pages=3 if permute is not None else 0,
                                        pad_value=pad, poison=poison)
     vc, vt, _ = sdpa_ref.pack_paged(vs, page_size, permute_seed=None if permute is None else permute + 1,
-                                    extra_pages=5 if permute is not None else 0, pad_value=pad, poison=poison)
+                                    extra_pages=3 if permute is not None else 0, pad_value=pad, poison=poison)
     return decode_attention(q, kc, vc, kv_indptr=lens.to(index_dtype), k_block_table=kt, v_block_table=vt,
                             kv_page_size=page_size)
 
