@@ -148,6 +148,29 @@ int b200attn_prefill(const b200attn_prefill_args_t* args, void* cuda_stream);
 int b200attn_decode(const b200attn_decode_args_t* args, void* cuda_stream);
 
 /*
+ * Decode / speculative decode for callers that cannot hand over device memory for scratch and
+ * must not trigger an allocation: a server that gave all of its HBM to the KV cache at start-up,
+ * a plug-in living inside another framework's memory pool, code that runs while that framework
+ * has frozen its allocator.  Same arguments, kernels and results as b200attn_decode, except that
+ * `workspace` / `workspace_bytes` are ignored: the planner tables, merge tickets and split-KV
+ * partials live in an 8 MiB array built into the library (each GPU that loads the library holds
+ * those 8 MiB until the process exits).  Calls cudaMalloc / cudaFree or any allocating routine: never.
+ *
+ *  - Problems whose scratch need (b200attn_decode_workspace_bytes) exceeds 8 MiB are refused with
+ *    B200ATTN_E_WORKSPACE; use b200attn_decode for those.
+ *  - The first call on each device looks up the array's device address (one driver query, no
+ *    allocation); make that first call before starting any stream capture.
+ *  - All calls on a device share the one array.  Calls must not overlap on the GPU (two streams,
+ *    two threads): they would overwrite each other's partials.  Back-to-back calls on one stream
+ *    are fine; nothing needs clearing in between.
+ *  - Device-side error codes (block-table entry out of range) are not reported through this entry
+ *    point; such entries are still skipped, never dereferenced.
+ *
+ * This function has no counterpart in the reference.
+ */
+int b200attn_decode_static(const b200attn_decode_args_t* args, void* cuda_stream);
+
+/*
  * Reads (and clears) the error word a kernel of an earlier call may have set in
  * `workspace` (bounded wait expired, page index out of range).  Synchronises
  * `cuda_stream`.  Returns 0, or B200ATTN_E_DEVICE with the code in *code.

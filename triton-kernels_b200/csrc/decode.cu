@@ -22,6 +22,7 @@
 //       a ticket, and the CTA that draws the last ticket of its (sequence, kv head)
 //       performs the log-sum-exp merge.  No CTA ever waits for another.
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 #include "decode_launch.h"
@@ -658,6 +659,59 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "decode kernel launch");
   return B200ATTN_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Decode without any caller-provided or allocated scratch memory.
+//
+// Some hosts of this library are not allowed to allocate device memory at the moment they need
+// attention: an inference server that hands its whole HBM budget to the KV cache at start-up and
+// forbids allocations afterwards, a plug-in running inside another framework's memory pool, or
+// code running while that framework is recording its work and must not disturb its allocator.
+// For them the planner tables, merge tickets and split-KV partials live in this fixed array,
+// which is part of the loaded module: every GPU that loads the library holds kStaticScratchBytes
+// of it until the process exits.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kScratchMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_ptr[kScratchMaxDevices] = {};
+}  // namespace
+
+// `a.device` must be the current device.  The first call on a device resolves the device address of
+// the array (in host code `g_decode_scratch` itself is only a handle, not something a kernel may be
+// given); later calls reuse the cached address.
+int launch_decode_static(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream) {
+  if (a.device < 0 || a.device >= kScratchMaxDevices) {
+    set_error("decode_static: device ordinal %d out of range", a.device);
+    return B200ATTN_E_INVALID;
+  }
+  const DecodeWsLayout w = decode_ws_layout(a, sm_count);
+  if (w.total > kStaticScratchBytes) {
+    set_error("decode_static: this problem needs %zu bytes of scratch but the built-in array holds %zu; "
+              "use b200attn_decode with a caller-provided workspace", w.total, kStaticScratchBytes);
+    return B200ATTN_E_WORKSPACE;
+  }
+  void* ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_ptr[a.device] == nullptr) {
+      void* resolved = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&resolved, g_decode_scratch);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(decode scratch)");
+      g_scratch_ptr[a.device] = resolved;
+    }
+    ptr = g_scratch_ptr[a.device];
+  }
+  b200attn_decode_args_t b = a;
+  b.workspace = ptr;
+  b.workspace_bytes = kStaticScratchBytes;
+  // The planner kernel rewrites the item prefix and zeroes the merge tickets at the start of every
+  // call, and partial slots are always written before they are read, so stale contents are harmless.
+  return launch_decode(b, sm_count, stream);
 }
 
 }  // namespace b200attn

@@ -31,6 +31,7 @@ EXPORTS = (
     "b200attn_decode_workspace_bytes",
     "b200attn_prefill",
     "b200attn_decode",
+    "b200attn_decode_static",
     "b200attn_check_workspace",
 )
 
@@ -139,6 +140,8 @@ def lib() -> C.CDLL:
         handle.b200attn_prefill.restype = C.c_int
         handle.b200attn_decode.argtypes = [C.POINTER(DecodeArgs), C.c_void_p]
         handle.b200attn_decode.restype = C.c_int
+        handle.b200attn_decode_static.argtypes = [C.POINTER(DecodeArgs), C.c_void_p]
+        handle.b200attn_decode_static.restype = C.c_int
         handle.b200attn_check_workspace.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
         handle.b200attn_check_workspace.restype = C.c_int
         got = handle.b200attn_abi_version()
