@@ -26,6 +26,8 @@
 
 #include "common.cuh"
 #include "decode_launch.h"
+#include "sm100_ptx.cuh"
+#include "tensor_map.h"
 
 namespace b200attn {
 
@@ -251,15 +253,35 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
 }
 
 // ---------------------------------------------------------------------------
-// bf16 / fp16 tensor-core kernel
+// bf16 / fp16 tensor-core kernel.
+// Warps 0 .. n_mtiles*key_slices-1 consume; the last warp is the TMA producer.
+// A stage holds 64 keys: K as D/64 column blocks of [64 rows][128 B] (128-byte swizzle, as
+// written by the TMA), then V in the same form.
 // ---------------------------------------------------------------------------
-template <typename T, int D>
-__global__ void __launch_bounds__(256) decode_mma_kernel(const DecodeParams p) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ int s_ticket;
-  constexpr int CPR = D * 2 / 16;          // 16-byte chunks per row
+struct __align__(8) DecodeCtrl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  int ticket;
+  int abort_flag;
+};
+
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
+  const bool ok = ptx::mbar_wait(bar, parity);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// kQRegs: keep the Q fragments in registers (one 16-row tile per warp, 4*D/16 registers); otherwise they are
+// re-read from shared memory at every k-step, which frees registers so that two CTAs fit on an SM.
+template <typename T, int D, bool kQRegs, int kMaxThreads, int kMinBlocks>
+__global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
+                                                         const __grid_constant__ CUtensorMap tm_v,
+                                                         const DecodeParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  constexpr int CPR = D * 2 / 16;            // 16-byte pieces per row
   constexpr int ROW_BYTES = D * 2;
-  constexpr int TILE_BYTES = kTileN * ROW_BYTES;
+  constexpr int CHUNKS = D / 64;             // 128-byte column blocks
+  constexpr int CHUNK_BYTES = kTileN * 128;  // one column block of a 64-key tile
+  constexpr int TILE_BYTES = CHUNKS * CHUNK_BYTES;
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   constexpr int KSTEPS = D / 16;
 
@@ -268,11 +290,12 @@ __global__ void __launch_bounds__(256) decode_mma_kernel(const DecodeParams p) {
   if (item >= n_items) return;
   const int h = blockIdx.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int nthreads = blockDim.x;
   const int NMT = p.n_mtiles;
-  const int KS = (nthreads >> 5) / NMT;
-  const int mt = warp % NMT, ks = warp / NMT;
+  const int n_cwarps = (blockDim.x >> 5) - 1;   // consumer warps
+  const int KS = n_cwarps / NMT;
+  const int mt = warp % NMT, ks = warp / NMT;   // meaningful for consumer warps only
   const int rows_pad = NMT * 16;
+  const bool is_producer = warp == n_cwarps;
 
   const int b = find_sequence(p.item_start, p.batch, item);
   const int item0 = p.item_start[b];
@@ -285,48 +308,27 @@ __global__ void __launch_bounds__(256) decode_mma_kernel(const DecodeParams p) {
   const int t_end = min(len, t_begin + chunk);
   const int ntiles = t_end > t_begin ? (t_end - t_begin + kTileN - 1) / kTileN : 0;
 
-  unsigned char* q_smem = smem;
-  unsigned char* stage_base = smem + rows_pad * ROW_BYTES;
-  const uint32_t q_s = smem_u32(q_smem);
+  // smem: [stages (1024-byte aligned)] [Q rows] [control]
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* stage_base = smem;
+  unsigned char* q_smem = smem + kStages * STAGE_BYTES;
+  DecodeCtrl* ctrl = reinterpret_cast<DecodeCtrl*>(q_smem + rows_pad * ROW_BYTES);
   const uint32_t stage_s = smem_u32(stage_base);
+  const uint32_t q_s = smem_u32(q_smem);
 
-  const T* kg = static_cast<const T*>(p.k);
-  const T* vg = static_cast<const T*>(p.v);
-
-  auto load_tile = [&](int tile, int stage) {
-    const int t0 = t_begin + tile * kTileN;
-    const uint32_t kdst = stage_s + stage * STAGE_BYTES;
-    const uint32_t vdst = kdst + TILE_BYTES;
-    for (int idx = tid; idx < kTileN * CPR; idx += nthreads) {
-      const int row = idx / CPR, ch = idx % CPR;
-      const int t = t0 + row;
-      const T* ksrc = kg;
-      const T* vsrc = vg;
-      int kbytes = 0, vbytes = 0;
-      if (t < t_end) {
-        const long long ko = row_offset(p, p.k_table, b, h, si.start, t, D);
-        const long long vo = (p.layout == B200ATTN_PAGED) ? row_offset(p, p.v_table, b, h, si.start, t, D) : ko;
-        if (ko >= 0) { ksrc = kg + ko + ch * 8; kbytes = 16; }
-        if (vo >= 0) { vsrc = vg + vo + ch * 8; vbytes = 16; }
-        if ((ko < 0 || vo < 0) && ch == 0) p.header[0] = DEV_ERR_PAGE_RANGE;
-      }
-      const uint32_t off = row * ROW_BYTES + ((ch ^ (row & 7)) << 4);
-      cp_async16(kdst + off, ksrc, kbytes);
-      cp_async16(vdst + off, vsrc, vbytes);
+  if (tid == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(smem_u32(&ctrl->full[i]), 1);
+      ptx::mbar_init(smem_u32(&ctrl->empty[i]), n_cwarps);
     }
-  };
-
-  // prologue loads first, so the Q staging below overlaps with them
-  for (int s = 0; s < kStages - 1; ++s) {
-    if (s < ntiles) load_tile(s, s);
-    cp_async_commit();
+    ctrl->abort_flag = 0;
+    ptx::mbar_fence_init();
   }
-
   // Q rows (group x drafts, contiguous in memory) -> smem, zero padded to 16-row tiles
   {
     const T* qg = static_cast<const T*>(p.q) +
                   ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.group) * p.q_len) * D;
-    for (int idx = tid; idx < rows_pad * CPR; idx += nthreads) {
+    for (int idx = tid; idx < rows_pad * CPR; idx += blockDim.x) {
       const int row = idx / CPR, ch = idx % CPR;
       uint4 val = make_uint4(0u, 0u, 0u, 0u);
       if (row < p.rows) val = __ldg(reinterpret_cast<const uint4*>(qg + static_cast<long long>(row) * D + ch * 8));
@@ -334,128 +336,238 @@ __global__ void __launch_bounds__(256) decode_mma_kernel(const DecodeParams p) {
     }
   }
   __syncthreads();
-  uint32_t qf[KSTEPS][4];
-  {
-    const int mat = lane >> 3;
-    const int row = mt * 16 + (mat & 1) * 8 + (lane & 7);
-#pragma unroll
-    for (int kk = 0; kk < KSTEPS; ++kk) {
-      const int ch = kk * 2 + (mat >> 1);
-      ldmatrix_x4(qf[kk], q_s + row * ROW_BYTES + ((ch ^ (row & 7)) << 4));
-    }
-  }
 
-  // per-lane rows: r0 = mt*16 + lane/4, r1 = r0 + 8
-  const int r0 = mt * 16 + (lane >> 2);
-  const int r1 = r0 + 8;
-  int lim0 = len - 1, lim1 = len - 1;  // last visible key index for each row
-  if (p.causal) {
-    lim0 = len - p.q_len + (r0 % p.q_len);
-    lim1 = len - p.q_len + (r1 % p.q_len);
-  }
-  float m_run[2] = {-INFINITY, -INFINITY};
+  float m_used[2] = {-INFINITY, -INFINITY};  // exponent reference baked into o[] and l_run[]
   float l_run[2] = {0.f, 0.f};
   float o[D / 8][4];
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) { o[i][0] = 0.f; o[i][1] = 0.f; o[i][2] = 0.f; o[i][3] = 0.f; }
-  const float sl2 = p.scale_log2;
+  const int r0 = mt * 16 + (lane >> 2);
+  const int r1 = r0 + 8;
 
-  for (int it = 0; it < ntiles; ++it) {
-    cp_async_wait<kStages - 2>();
-    __syncthreads();
-    {
-      const int nt = it + kStages - 1;
-      if (nt < ntiles) load_tile(nt, nt % kStages);
-      cp_async_commit();
-    }
-    const int stage = it % kStages;
-    const uint32_t ks_base = stage_s + stage * STAGE_BYTES;
-    const uint32_t vs_base = ks_base + TILE_BYTES;
-    const int tile_t0 = t_begin + it * kTileN;
-
-    for (int sb = ks; sb < kTileN / 16; sb += KS) {
-      const int tok0 = sb * 16;             // within tile
-      const int abs0 = tile_t0 + tok0;      // within sequence
-      if (abs0 >= t_end) break;
-      float s[2][4];
+  if (is_producer) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) { ptx::prefetch_tensormap(&tm_k); ptx::prefetch_tensormap(&tm_v); }
+    int h_coord = h;
+    long long row0 = si.start;               // ragged
+    if (p.layout == B200ATTN_DENSE) { h_coord = 0; row0 = (static_cast<long long>(b) * p.kv_heads + h) * p.max_kv; }
+    bool ok = true;
+    int issued = 0;
+    for (int tile = 0; tile < ntiles; ++tile) {
+      const int stage = tile % kStages, use = tile / kStages;
+      if (use > 0) {
+        ok = warp_wait(smem_u32(&ctrl->empty[stage]), (use - 1) & 1);
+        if (!ok) break;
+      }
+      const int t0 = t_begin + tile * kTileN;
+      const uint32_t kdst = stage_s + stage * STAGE_BYTES;
+      const uint32_t vdst = kdst + TILE_BYTES;
+      const uint32_t bar = smem_u32(&ctrl->full[stage]);
+      if (p.layout != B200ATTN_PAGED) {
+        if (lane == 0) {
+          ptx::mbar_arrive_expect_tx(bar, STAGE_BYTES);
+          const int row = static_cast<int>(row0 + t0);
 #pragma unroll
-      for (int i = 0; i < 2; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
-      {
-        const int mat = lane >> 3;
-        const int trow = tok0 + (mat >> 1) * 8 + (lane & 7);
-        const uint32_t rbase = ks_base + trow * ROW_BYTES;
-        const int sw = trow & 7;
+          for (int cc = 0; cc < CHUNKS; ++cc) {
+            ptx::tma_load_3d(kdst + cc * CHUNK_BYTES, &tm_k, bar, cc * 64, h_coord, row);
+            ptx::tma_load_3d(vdst + cc * CHUNK_BYTES, &tm_v, bar, cc * 64, h_coord, row);
+          }
+        }
+      } else {
+        // one box of box_rows keys per (lane, round); only pages that hold keys of this chunk are fetched
+        const int boxes = kTileN / p.box_rows;
+        const int* ktab = p.k_table + static_cast<long long>(b) * p.table_stride;
+        const int* vtab = p.v_table + static_cast<long long>(b) * p.table_stride;
+        int krow[2], vrow[2];
+        int count = 0, n = 0;
+        for (int i = lane; i < boxes; i += 32, ++n) {
+          const int t = t0 + i * p.box_rows;
+          int kr = -1, vr = -1;
+          if (t < t_end) {
+            int lp, off;
+            if (p.page_shift >= 0) { lp = t >> p.page_shift; off = t & (p.page_size - 1); }
+            else { lp = t / p.page_size; off = t - lp * p.page_size; }
+            const int kp = __ldg(ktab + lp), vp = __ldg(vtab + lp);
+            // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
+            const bool kbad = kp < 0 || kp >= p.num_pages, vbad = vp < 0 || vp >= p.num_pages;
+            if (kbad || vbad) p.header[0] = DEV_ERR_PAGE_RANGE;
+            if (p.num_pages > 0) {
+              kr = (kbad ? 0 : kp) * p.page_size + off;
+              vr = (vbad ? 0 : vp) * p.page_size + off;
+            }
+          }
+          krow[n] = kr; vrow[n] = vr;
+          count += (kr >= 0) + (vr >= 0);
+        }
+        for (int off = 16; off > 0; off >>= 1) count += __shfl_xor_sync(0xffffffffu, count, off);
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * p.box_rows * 128 * CHUNKS);
+        __syncwarp();
+        n = 0;
+        for (int i = lane; i < boxes; i += 32, ++n) {
+          const uint32_t roff = i * p.box_rows * 128;
 #pragma unroll
-        for (int kk = 0; kk < KSTEPS; ++kk) {
-          uint32_t kb[4];
-          const int ch = kk * 2 + (mat & 1);
-          ldmatrix_x4(kb, rbase + ((ch ^ sw) << 4));
-          mma_m16n8k16<T>(s[0], qf[kk], kb[0], kb[1]);
-          mma_m16n8k16<T>(s[1], qf[kk], kb[2], kb[3]);
+          for (int cc = 0; cc < CHUNKS; ++cc) {
+            if (krow[n] >= 0) ptx::tma_load_3d(kdst + cc * CHUNK_BYTES + roff, &tm_k, bar, cc * 64, h_coord, krow[n]);
+            if (vrow[n] >= 0) ptx::tma_load_3d(vdst + cc * CHUNK_BYTES + roff, &tm_v, bar, cc * 64, h_coord, vrow[n]);
+          }
         }
       }
-      // scale, mask, online softmax (exp2 domain)
-      float mx0 = -INFINITY, mx1 = -INFINITY;
+      issued = tile + 1;
+    }
+    if (!ok) {
+      if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; ctrl->abort_flag = 1; }
+      // bounded drain of the copies still in flight before the CTA may exit
+      for (int t = max(0, issued - kStages); t < issued; ++t)
+        ptx::mbar_wait(smem_u32(&ctrl->full[t % kStages]), (t / kStages) & 1);
+    }
+  } else {
+    // =========================== consumers ===========================
+    uint32_t qf[kQRegs ? KSTEPS : 1][4];
+    const int q_row = mt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+    const uint32_t q_rbase = q_s + q_row * ROW_BYTES;
+    if constexpr (kQRegs) {
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const int col = abs0 + nt * 8 + 2 * (lane & 3);
-        s[nt][0] = (col <= lim0) ? s[nt][0] * sl2 : -INFINITY;
-        s[nt][1] = (col + 1 <= lim0) ? s[nt][1] * sl2 : -INFINITY;
-        s[nt][2] = (col <= lim1) ? s[nt][2] * sl2 : -INFINITY;
-        s[nt][3] = (col + 1 <= lim1) ? s[nt][3] * sl2 : -INFINITY;
-        mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
-        mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
-      }
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-      const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-      const float ms0 = (mn0 == -INFINITY) ? 0.f : mn0;
-      const float ms1 = (mn1 == -INFINITY) ? 0.f : mn1;
-      const float a0 = fast_exp2(m_run[0] - ms0), a1 = fast_exp2(m_run[1] - ms1);
-      m_run[0] = mn0; m_run[1] = mn1;
-      float rs0 = 0.f, rs1 = 0.f;
-      uint32_t pa[4];
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const float p0 = fast_exp2(s[nt][0] - ms0), p1 = fast_exp2(s[nt][1] - ms0);
-        const float p2 = fast_exp2(s[nt][2] - ms1), p3 = fast_exp2(s[nt][3] - ms1);
-        rs0 += p0 + p1; rs1 += p2 + p3;
-        pa[nt * 2 + 0] = ElemTraits<T>::pack2(p0, p1);
-        pa[nt * 2 + 1] = ElemTraits<T>::pack2(p2, p3);
-      }
-      l_run[0] = l_run[0] * a0 + rs0;   // per-lane partial row sums; reduced over the quad at the end
-      l_run[1] = l_run[1] * a1 + rs1;
-#pragma unroll
-      for (int i = 0; i < D / 8; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
-      {
-        const int mat = lane >> 3;
-        const int trow = tok0 + (mat & 1) * 8 + (lane & 7);
-        const uint32_t rbase = vs_base + trow * ROW_BYTES;
-        const int sw = trow & 7;
-#pragma unroll
-        for (int n0 = 0; n0 < D / 16; ++n0) {
-          uint32_t vb[4];
-          const int ch = n0 * 2 + (mat >> 1);
-          ldmatrix_x4_trans(vb, rbase + ((ch ^ sw) << 4));
-          mma_m16n8k16<T>(o[2 * n0], pa, vb[0], vb[1]);
-          mma_m16n8k16<T>(o[2 * n0 + 1], pa, vb[2], vb[3]);
-        }
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        const int ch = kk * 2 + (lane >> 4);
+        ldmatrix_x4(qf[kk], q_rbase + ((ch ^ (q_row & 7)) << 4));
       }
     }
+    int lim0 = len - 1, lim1 = len - 1;  // last visible key index for each of this lane's two rows
+    if (p.causal) {
+      lim0 = len - p.q_len + (r0 % p.q_len);
+      lim1 = len - p.q_len + (r1 % p.q_len);
+    }
+    const int lim_min = min(lim0, lim1);
+    const float sl2 = p.scale_log2;
+    bool ok = true;
+
+    for (int tile = 0; tile < ntiles; ++tile) {
+      const int stage = tile % kStages, use = tile / kStages;
+      ok = warp_wait(smem_u32(&ctrl->full[stage]), use & 1);
+      if (!ok) break;
+      const uint32_t ks_base = stage_s + stage * STAGE_BYTES;
+      const uint32_t vs_base = ks_base + TILE_BYTES;
+      const int tile_t0 = t_begin + tile * kTileN;
+      const int valid = len - tile_t0;  // keys of this tile that belong to the sequence
+
+      for (int sb = ks; sb < kTileN / 16; sb += KS) {
+        const int tok0 = sb * 16;             // within tile
+        const int abs0 = tile_t0 + tok0;      // within sequence
+        if (abs0 >= t_end) break;
+        if (valid < tok0 + 16) {
+          // keys past the sequence end get P == 0, but their V rows may hold anything (page tails,
+          // the next sequence, stale shared memory): zero them so that 0 * x stays 0
+          unsigned char* vtile = stage_base + stage * STAGE_BYTES + TILE_BYTES;
+          const int first = max(valid, tok0);
+          const int npieces = (tok0 + 16 - first) * 8;
+          for (int cc = 0; cc < CHUNKS; ++cc) {
+            uint4* dst = reinterpret_cast<uint4*>(vtile + cc * CHUNK_BYTES + first * 128);
+            for (int i = lane; i < npieces; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+          __syncwarp();
+        }
+        float s[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
+        {
+          const int mat = lane >> 3;
+          const int trow = tok0 + (mat >> 1) * 8 + (lane & 7);
+          const uint32_t rbase = ks_base + trow * 128;
+          const int sw = trow & 7;
+#pragma unroll
+          for (int kk = 0; kk < KSTEPS; ++kk) {
+            uint32_t kb[4];
+            const int ch = kk * 2 + (mat & 1);   // 16-byte piece index along D
+            ldmatrix_x4(kb, rbase + (ch >> 3) * CHUNK_BYTES + (((ch & 7) ^ sw) << 4));
+            if constexpr (kQRegs) {
+              mma_m16n8k16<T>(s[0], qf[kk], kb[0], kb[1]);
+              mma_m16n8k16<T>(s[1], qf[kk], kb[2], kb[3]);
+            } else {
+              const int qch = kk * 2 + (lane >> 4);
+              ldmatrix_x4(qf[0], q_rbase + ((qch ^ (q_row & 7)) << 4));
+              mma_m16n8k16<T>(s[0], qf[0], kb[0], kb[1]);
+              mma_m16n8k16<T>(s[1], qf[0], kb[2], kb[3]);
+            }
+          }
+        }
+        // scale, mask (only where the tile reaches a row's last visible key), online softmax in the exp2 domain
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+        const bool all_visible = __all_sync(0xffffffffu, abs0 + 15 <= lim_min);
+        if (all_visible) {
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            s[nt][0] *= sl2; s[nt][1] *= sl2; s[nt][2] *= sl2; s[nt][3] *= sl2;
+            mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+          }
+        } else {
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt) {
+            const int col = abs0 + nt * 8 + 2 * (lane & 3);
+            s[nt][0] = (col <= lim0) ? s[nt][0] * sl2 : -INFINITY;
+            s[nt][1] = (col + 1 <= lim0) ? s[nt][1] * sl2 : -INFINITY;
+            s[nt][2] = (col <= lim1) ? s[nt][2] * sl2 : -INFINITY;
+            s[nt][3] = (col + 1 <= lim1) ? s[nt][3] * sl2 : -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+          }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        // the accumulators are rescaled only when a row's max grew by more than 2^8; until then the
+        // older reference keeps being used (exact: the same reference normalises the row at the end)
+        const bool need0 = (mx0 - m_used[0]) > 8.f, need1 = (mx1 - m_used[1]) > 8.f;
+        if (__any_sync(0xffffffffu, need0 || need1)) {
+          float a0 = 1.f, a1 = 1.f;
+          if (need0) { a0 = fast_exp2(m_used[0] - mx0); m_used[0] = mx0; }
+          if (need1) { a1 = fast_exp2(m_used[1] - mx1); m_used[1] = mx1; }
+          l_run[0] *= a0; l_run[1] *= a1;
+#pragma unroll
+          for (int i = 0; i < D / 8; ++i) { o[i][0] *= a0; o[i][1] *= a0; o[i][2] *= a1; o[i][3] *= a1; }
+        }
+        const float ms0 = (m_used[0] == -INFINITY) ? 0.f : m_used[0];
+        const float ms1 = (m_used[1] == -INFINITY) ? 0.f : m_used[1];
+        uint32_t pa[4];
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const float p0 = fast_exp2(s[nt][0] - ms0), p1 = fast_exp2(s[nt][1] - ms0);
+          const float p2 = fast_exp2(s[nt][2] - ms1), p3 = fast_exp2(s[nt][3] - ms1);
+          l_run[0] += p0 + p1;   // per-lane partial row sums; reduced over the quad at the end
+          l_run[1] += p2 + p3;
+          pa[nt * 2 + 0] = ElemTraits<T>::pack2(p0, p1);
+          pa[nt * 2 + 1] = ElemTraits<T>::pack2(p2, p3);
+        }
+        {
+          const int mat = lane >> 3;
+          const int trow = tok0 + (mat & 1) * 8 + (lane & 7);
+          const uint32_t rbase = vs_base + trow * 128;
+          const int sw = trow & 7;
+#pragma unroll
+          for (int n0 = 0; n0 < D / 16; ++n0) {
+            uint32_t vb[4];
+            const int ch = n0 * 2 + (mat >> 1);
+            ldmatrix_x4_trans(vb, rbase + (ch >> 3) * CHUNK_BYTES + (((ch & 7) ^ sw) << 4));
+            mma_m16n8k16<T>(o[2 * n0], pa, vb[0], vb[1]);
+            mma_m16n8k16<T>(o[2 * n0 + 1], pa, vb[2], vb[3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(smem_u32(&ctrl->empty[stage]));
+    }
+    if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; ctrl->abort_flag = 1; }
   }
-  cp_async_wait<0>();
-  __syncthreads();  // all tiles consumed: the stage ring is free for the cross-warp combine
-
-  l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
-  l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
-  l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
-  l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
+  __syncthreads();  // every tile consumed (or the CTA gave up): the stage ring is free for the cross-warp combine
 
   float* comb_o = reinterpret_cast<float*>(stage_base);
   float* comb_ml = comb_o + static_cast<size_t>(KS) * rows_pad * D;
-  {
+  if (!is_producer) {
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 1);
+    l_run[0] += __shfl_xor_sync(0xffffffffu, l_run[0], 2);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 1);
+    l_run[1] += __shfl_xor_sync(0xffffffffu, l_run[1], 2);
     float* o0 = comb_o + (static_cast<size_t>(ks) * rows_pad + r0) * D;
     float* o1 = comb_o + (static_cast<size_t>(ks) * rows_pad + r1) * D;
 #pragma unroll
@@ -465,14 +577,15 @@ __global__ void __launch_bounds__(256) decode_mma_kernel(const DecodeParams p) {
       *reinterpret_cast<float2*>(o1 + col) = make_float2(o[i][2], o[i][3]);
     }
     if ((lane & 3) == 0) {
-      comb_ml[(ks * rows_pad + r0) * 2] = m_run[0];
+      comb_ml[(ks * rows_pad + r0) * 2] = m_used[0];
       comb_ml[(ks * rows_pad + r0) * 2 + 1] = l_run[0];
-      comb_ml[(ks * rows_pad + r1) * 2] = m_run[1];
+      comb_ml[(ks * rows_pad + r1) * 2] = m_used[1];
       comb_ml[(ks * rows_pad + r1) * 2 + 1] = l_run[1];
     }
   }
   __syncthreads();
-  emit_and_merge<T, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, KS, rows_pad, &s_ticket);
+  if (ctrl->abort_flag) return;
+  emit_and_merge<T, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, KS, rows_pad, &ctrl->ticket);
 }
 
 // ---------------------------------------------------------------------------
@@ -621,6 +734,7 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
   }
   p.num_pages = a.layout == B200ATTN_PAGED ? static_cast<int>(std::min<long long>(a.total_kv / p.page_size, 0x7fffffff)) : 0;
   p.causal = a.causal_drafts ? 1 : 0;
+  p.box_rows = kTileN;
   p.target_items = w.target_items; p.min_chunk = w.min_chunk; p.max_items = w.max_items;
   p.scale_log2 = a.sm_scale * 1.4426950408889634f;
 
@@ -637,23 +751,44 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
     else          { rc = set_smem(decode_simt_kernel<64>, smem);  if (rc) return rc; decode_simt_kernel<64><<<grid, 128, smem, stream>>>(p); }
   } else {
     const int nmt = p.n_mtiles;
-    const int ksl = nmt == 1 ? 4 : (nmt <= 4 ? 2 : 1);
-    const int threads = 32 * nmt * ksl;
+    const int ksl = nmt <= 2 ? 4 : (nmt <= 4 ? 2 : 1);
+    const int threads = 32 * (nmt * ksl + 1);   // + the producer warp
     const size_t stage_bytes = static_cast<size_t>(kStages) * 2 * kTileN * D * 2;
     const size_t comb_bytes = sizeof(float) * static_cast<size_t>(ksl) * nmt * 16 * (D + 2);
-    const size_t smem = static_cast<size_t>(nmt) * 16 * D * 2 + std::max(stage_bytes, comb_bytes);
+    const size_t smem = 1024 + std::max(stage_bytes, comb_bytes) + static_cast<size_t>(nmt) * 16 * D * 2 + sizeof(DecodeCtrl);
+    // tensor maps over K and V: (D, heads, tokens), one box = 64 elements x 1 head x box_rows keys
+    CUtensorMap tk, tv;
     int rc = 0;
+    long long tokens;
+    int heads;
+    p.box_rows = kTileN;
+    if (a.layout == B200ATTN_DENSE) { tokens = static_cast<long long>(a.batch) * a.kv_heads * a.max_kv; heads = 1; }
+    else { tokens = a.total_kv; heads = a.kv_heads; }
+    if (a.layout == B200ATTN_PAGED) {
+      int box = 1;
+      while (box < kTileN && (a.page_size % (box * 2)) == 0) box *= 2;
+      p.box_rows = box;
+    }
+    if ((rc = make_token_map(&tk, a.dtype, a.k, tokens, heads, D, p.box_rows))) return rc;
+    if ((rc = make_token_map(&tv, a.dtype, a.v, tokens, heads, D, p.box_rows))) return rc;
+#define B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, QREGS, MAXT, MINB)                                    \
+    do {                                                                                          \
+      rc = set_smem(decode_mma_kernel<TYPE, DIM, QREGS, MAXT, MINB>, smem);                       \
+      if (rc) return rc;                                                                          \
+      decode_mma_kernel<TYPE, DIM, QREGS, MAXT, MINB><<<grid, threads, smem, stream>>>(tk, tv, p);\
+    } while (0)
 #define B200ATTN_LAUNCH_DECODE(TYPE, DIM)                                         \
     do {                                                                          \
-      rc = set_smem(decode_mma_kernel<TYPE, DIM>, smem);                          \
-      if (rc) return rc;                                                          \
-      decode_mma_kernel<TYPE, DIM><<<grid, threads, smem, stream>>>(p);           \
+      if (threads <= 160) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, true, 160, 2);      \
+      else if (threads <= 224) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 224, 2);\
+      else B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 288, 1);                    \
     } while (0)
     if (a.dtype == B200ATTN_BF16) {
       if (D == 128) B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 128); else B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 64);
     } else {
       if (D == 128) B200ATTN_LAUNCH_DECODE(__half, 128); else B200ATTN_LAUNCH_DECODE(__half, 64);
     }
+#undef B200ATTN_LAUNCH_DECODE_V
 #undef B200ATTN_LAUNCH_DECODE
   }
   e = cudaGetLastError();

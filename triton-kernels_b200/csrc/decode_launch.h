@@ -37,6 +37,7 @@ struct DecodeParams {
   int page_size;
   int page_shift;    // log2(page_size) or -1
   int num_pages;
+  int box_rows;      // keys per TMA box (paged: a power of two that divides the page size)
   int causal;
   int target_items;
   int min_chunk;

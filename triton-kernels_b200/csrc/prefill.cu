@@ -29,6 +29,7 @@
 #include "common.cuh"
 #include "prefill_launch.h"
 #include "sm100_ptx.cuh"
+#include "tensor_map.h"
 
 namespace b200attn {
 
@@ -285,8 +286,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (t < w.len_k) {
             const int lp = t / p.page_size;
             const int page = __ldg(table + lp);
-            if (page >= 0 && page < p.num_pages) row = page * p.page_size + (t - lp * p.page_size);
-            else p.header[0] = DEV_ERR_PAGE_RANGE;
+            // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
+            const bool bad = page < 0 || page >= p.num_pages;
+            if (bad) p.header[0] = DEV_ERR_PAGE_RANGE;
+            if (p.num_pages > 0) row = (bad ? 0 : page) * p.page_size + (t - lp * p.page_size);
           }
           my_rows[nmine++] = row;
           if (row >= 0) ++count;
@@ -558,46 +561,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
 }
 
-// ---------------------------------------------------------------------------
-// host side: tensor maps
-// ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-  });
-  return fn;
-}
-
-// 3-D map over a [tokens][heads][D] (heads == 1 for per-head-contiguous dense tensors) 16-bit tensor,
-// box = 64 elements x 1 head x box_rows tokens, 128-byte swizzle, zero fill out of bounds.
-int make_map(CUtensorMap* m, int dtype, const void* base, long long tokens, int heads, int D, int box_rows) {
-  EncodeTiledFn fn = get_encode_fn();
-  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return B200ATTN_E_CUDA; }
-  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(tokens)};
-  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(D) * 2, static_cast<cuuint64_t>(D) * 2 * heads};
-  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(box_rows)};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUtensorMapDataType dt = dtype == B200ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const CUresult r = fn(m, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    set_error("cuTensorMapEncodeTiled failed with CUresult %d (tokens=%lld heads=%d D=%d box_rows=%d)", static_cast<int>(r),
-              tokens, heads, D, box_rows);
-    return B200ATTN_E_CUDA;
-  }
-  return 0;
-}
-
 }  // namespace
 
 namespace {
@@ -674,26 +637,26 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, cudaStream_t stream) {
   int rc;
   dim3 grid;
   if (a.layout == B200ATTN_RAGGED) {
-    if ((rc = make_map(&tq, a.dtype, a.q, a.total_q, a.q_heads, D, kBM))) return rc;
-    if ((rc = make_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, kBN))) return rc;
-    if ((rc = make_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, kBN))) return rc;
+    if ((rc = make_token_map(&tq, a.dtype, a.q, a.total_q, a.q_heads, D, kBM))) return rc;
+    if ((rc = make_token_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, kBN))) return rc;
+    if ((rc = make_token_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, kBN))) return rc;
     const long long pairs = a.total_q / (2 * kBM) + a.batch;
     grid = dim3(static_cast<unsigned>(pairs), a.q_heads, 1);
   } else {
     const long long q_rows = static_cast<long long>(a.batch) * a.q_heads * a.max_q;
-    if ((rc = make_map(&tq, a.dtype, a.q, q_rows, 1, D, kBM))) return rc;
+    if ((rc = make_token_map(&tq, a.dtype, a.q, q_rows, 1, D, kBM))) return rc;
     if (a.layout == B200ATTN_DENSE) {
       const long long kv_rows = static_cast<long long>(a.batch) * a.kv_heads * a.max_kv;
-      if ((rc = make_map(&tk, a.dtype, a.k, kv_rows, 1, D, kBN))) return rc;
-      if ((rc = make_map(&tv, a.dtype, a.v, kv_rows, 1, D, kBN))) return rc;
+      if ((rc = make_token_map(&tk, a.dtype, a.k, kv_rows, 1, D, kBN))) return rc;
+      if ((rc = make_token_map(&tv, a.dtype, a.v, kv_rows, 1, D, kBN))) return rc;
     } else {
       // largest power of two that divides the page size, capped at the tile: every box stays inside one page
       int box = 1;
       while (box < kBN && (a.page_size % (box * 2)) == 0) box *= 2;
       p.box_rows = box;
       p.num_pages = static_cast<int>(std::min<long long>(a.total_kv / a.page_size, 0x7fffffff));
-      if ((rc = make_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box))) return rc;
-      if ((rc = make_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box))) return rc;
+      if ((rc = make_token_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box))) return rc;
+      if ((rc = make_token_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box))) return rc;
     }
     grid = dim3((a.max_q + 2 * kBM - 1) / (2 * kBM), a.q_heads, a.batch);
   }
