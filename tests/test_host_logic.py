@@ -93,7 +93,7 @@ def test_decode_plan_bounds(qh, kvh, m):
         assert sum(items) <= plan.max_items
         assert all(i >= 1 for i in items)
         assert all((i - 1) * chunk < max(n, 1) for i, n in zip(items, lens))
-        assert plan.threads <= 256 and plan.mma_tiles * 16 >= (qh // kvh) * m
+        assert plan.threads <= 288 and plan.mma_tiles * 16 >= (qh // kvh) * m
 
 
 def test_prefill_grid_and_boxes():

@@ -34,7 +34,7 @@ namespace b200attn {
 namespace {
 
 constexpr int kTileN = 64;
-constexpr int kStages = 3;
+constexpr int kMaxStages = 4;
 constexpr int kPlanThreads = 1024;
 
 struct SeqInfo {
@@ -240,6 +240,18 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     if (tid == 0) s_carry = carry + s_warp[31];
     __syncthreads();
   }
+  __syncthreads();
+  // per-item records, so that a CTA learns everything about its work item from one 32-byte read
+  for (int b = tid; b < p.batch; b += kPlanThreads) {
+    const SeqInfo si = seq_info(p, b);
+    const int first = b == 0 ? 0 : p.item_start[b];
+    const int n = p.item_start[b + 1] - first;
+    for (int c = 0; c < n && first + c < p.max_items; ++c) {
+      p.item_info[2 * (first + c)] = make_int4(b, c, n, first);
+      p.item_info[2 * (first + c) + 1] = make_int4(si.len, 0, static_cast<int>(si.start & 0xffffffffll),
+                                                   static_cast<int>(si.start >> 32));
+    }
+  }
   if (tid == 0) {
     p.item_start[0] = 0;
     int n_items = s_carry;
@@ -259,11 +271,23 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
 // written by the TMA), then V in the same form.
 // ---------------------------------------------------------------------------
 struct __align__(8) DecodeCtrl {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   int ticket;
   int abort_flag;
 };
+
+// Byte offset of the 128-byte row (key t of the tile, column block cb) inside a K or V tile.  A tile is a
+// sequence of TMA boxes of `1 << box_shift` keys, each stored as [column block][key][128 B].
+template <int CHUNKS>
+__device__ __forceinline__ uint32_t tile_row_offset(int t, int cb, int box_shift) {
+  const int box = t >> box_shift, r = t & ((1 << box_shift) - 1);
+  return static_cast<uint32_t>((((box * CHUNKS + cb) << box_shift) + r) << 7);
+}
+// address of 16-byte piece `pc` (0..7) of that row under the 128-byte swizzle (tile base 1024-byte aligned)
+__device__ __forceinline__ uint32_t swz_piece(uint32_t row_off, int pc) {
+  return row_off + (((pc ^ (row_off >> 7)) & 7) << 4);
+}
 
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
   const bool ok = ptx::mbar_wait(bar, parity);
@@ -272,7 +296,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
 
 // kQRegs: keep the Q fragments in registers (one 16-row tile per warp, 4*D/16 registers); otherwise they are
 // re-read from shared memory at every k-step, which frees registers so that two CTAs fit on an SM.
-template <typename T, int D, bool kQRegs, int kMaxThreads, int kMinBlocks>
+template <typename T, int D, bool kQRegs, int kStages, int kMaxThreads, int kMinBlocks>
 __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                          const __grid_constant__ CUtensorMap tm_v,
                                                          const DecodeParams p) {
@@ -286,9 +310,11 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
   constexpr int KSTEPS = D / 16;
 
   const int n_items = p.header[2];
-  const int item = blockIdx.x;
+  // heads vary fastest across CTAs: the CTAs that run side by side walk the same pages and read
+  // neighbouring head slices of each token row, which keeps DRAM rows open
+  const int item = blockIdx.x / p.kv_heads;
   if (item >= n_items) return;
-  const int h = blockIdx.y;
+  const int h = blockIdx.x - item * p.kv_heads;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int NMT = p.n_mtiles;
   const int n_cwarps = (blockDim.x >> 5) - 1;   // consumer warps
@@ -297,12 +323,13 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
   const int rows_pad = NMT * 16;
   const bool is_producer = warp == n_cwarps;
 
-  const int b = find_sequence(p.item_start, p.batch, item);
-  const int item0 = p.item_start[b];
-  const int c = item - item0;
-  const int n_chunks = p.item_start[b + 1] - item0;
+  const int4 rec0 = __ldg(p.item_info + 2 * item);
+  const int4 rec1 = __ldg(p.item_info + 2 * item + 1);
+  const int b = rec0.x, c = rec0.y, n_chunks = rec0.z, item0 = rec0.w;
   const int chunk = p.header[1];
-  const SeqInfo si = seq_info(p, b);
+  SeqInfo si;
+  si.len = rec1.x;
+  si.start = (static_cast<long long>(rec1.w) << 32) | static_cast<unsigned int>(rec1.z);
   const int len = si.len;
   const int t_begin = c * chunk;
   const int t_end = min(len, t_begin + chunk);
@@ -367,21 +394,19 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
         if (lane == 0) {
           ptx::mbar_arrive_expect_tx(bar, STAGE_BYTES);
           const int row = static_cast<int>(row0 + t0);
-#pragma unroll
-          for (int cc = 0; cc < CHUNKS; ++cc) {
-            ptx::tma_load_3d(kdst + cc * CHUNK_BYTES, &tm_k, bar, cc * 64, h_coord, row);
-            ptx::tma_load_3d(vdst + cc * CHUNK_BYTES, &tm_v, bar, cc * 64, h_coord, row);
-          }
+          ptx::tma_load_4d(kdst, &tm_k, bar, 0, row, 0, h_coord);
+          ptx::tma_load_4d(vdst, &tm_v, bar, 0, row, 0, h_coord);
         }
       } else {
         // one box of box_rows keys per (lane, round); only pages that hold keys of this chunk are fetched
-        const int boxes = kTileN / p.box_rows;
+        const int boxes = kTileN >> p.box_shift;
+        const int box_rows = 1 << p.box_shift;
         const int* ktab = p.k_table + static_cast<long long>(b) * p.table_stride;
         const int* vtab = p.v_table + static_cast<long long>(b) * p.table_stride;
         int krow[2], vrow[2];
         int count = 0, n = 0;
         for (int i = lane; i < boxes; i += 32, ++n) {
-          const int t = t0 + i * p.box_rows;
+          const int t = t0 + i * box_rows;
           int kr = -1, vr = -1;
           if (t < t_end) {
             int lp, off;
@@ -400,16 +425,13 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
           count += (kr >= 0) + (vr >= 0);
         }
         for (int off = 16; off > 0; off >>= 1) count += __shfl_xor_sync(0xffffffffu, count, off);
-        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * p.box_rows * 128 * CHUNKS);
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * box_rows * 128 * CHUNKS);
         __syncwarp();
         n = 0;
         for (int i = lane; i < boxes; i += 32, ++n) {
-          const uint32_t roff = i * p.box_rows * 128;
-#pragma unroll
-          for (int cc = 0; cc < CHUNKS; ++cc) {
-            if (krow[n] >= 0) ptx::tma_load_3d(kdst + cc * CHUNK_BYTES + roff, &tm_k, bar, cc * 64, h_coord, krow[n]);
-            if (vrow[n] >= 0) ptx::tma_load_3d(vdst + cc * CHUNK_BYTES + roff, &tm_v, bar, cc * 64, h_coord, vrow[n]);
-          }
+          const uint32_t boff = static_cast<uint32_t>(i) * box_rows * 128 * CHUNKS;
+          if (krow[n] >= 0) ptx::tma_load_4d(kdst + boff, &tm_k, bar, 0, krow[n], 0, h_coord);
+          if (vrow[n] >= 0) ptx::tma_load_4d(vdst + boff, &tm_v, bar, 0, vrow[n], 0, h_coord);
         }
       }
       issued = tile + 1;
@@ -459,10 +481,10 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
           // the next sequence, stale shared memory): zero them so that 0 * x stays 0
           unsigned char* vtile = stage_base + stage * STAGE_BYTES + TILE_BYTES;
           const int first = max(valid, tok0);
-          const int npieces = (tok0 + 16 - first) * 8;
-          for (int cc = 0; cc < CHUNKS; ++cc) {
-            uint4* dst = reinterpret_cast<uint4*>(vtile + cc * CHUNK_BYTES + first * 128);
-            for (int i = lane; i < npieces; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          const int npieces = (tok0 + 16 - first) * CHUNKS * 8;
+          for (int i = lane; i < npieces; i += 32) {
+            const int t = first + i / (CHUNKS * 8), cb = (i >> 3) % CHUNKS;
+            *reinterpret_cast<uint4*>(vtile + tile_row_offset<CHUNKS>(t, cb, p.box_shift) + ((i & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
           }
           __syncwarp();
         }
@@ -472,13 +494,14 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
         {
           const int mat = lane >> 3;
           const int trow = tok0 + (mat >> 1) * 8 + (lane & 7);
-          const uint32_t rbase = ks_base + trow * 128;
-          const int sw = trow & 7;
+          uint32_t roff[CHUNKS];
+#pragma unroll
+          for (int cb = 0; cb < CHUNKS; ++cb) roff[cb] = tile_row_offset<CHUNKS>(trow, cb, p.box_shift);
 #pragma unroll
           for (int kk = 0; kk < KSTEPS; ++kk) {
             uint32_t kb[4];
             const int ch = kk * 2 + (mat & 1);   // 16-byte piece index along D
-            ldmatrix_x4(kb, rbase + (ch >> 3) * CHUNK_BYTES + (((ch & 7) ^ sw) << 4));
+            ldmatrix_x4(kb, ks_base + swz_piece(roff[ch >> 3], ch & 7));
             if constexpr (kQRegs) {
               mma_m16n8k16<T>(s[0], qf[kk], kb[0], kb[1]);
               mma_m16n8k16<T>(s[1], qf[kk], kb[2], kb[3]);
@@ -542,13 +565,14 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
         {
           const int mat = lane >> 3;
           const int trow = tok0 + (mat & 1) * 8 + (lane & 7);
-          const uint32_t rbase = vs_base + trow * 128;
-          const int sw = trow & 7;
+          uint32_t roff[CHUNKS];
+#pragma unroll
+          for (int cb = 0; cb < CHUNKS; ++cb) roff[cb] = tile_row_offset<CHUNKS>(trow, cb, p.box_shift);
 #pragma unroll
           for (int n0 = 0; n0 < D / 16; ++n0) {
             uint32_t vb[4];
             const int ch = n0 * 2 + (mat >> 1);
-            ldmatrix_x4_trans(vb, rbase + (ch >> 3) * CHUNK_BYTES + (((ch & 7) ^ sw) << 4));
+            ldmatrix_x4_trans(vb, vs_base + swz_piece(roff[ch >> 3], ch & 7));
             mma_m16n8k16<T>(o[2 * n0], pa, vb[0], vb[1]);
             mma_m16n8k16<T>(o[2 * n0 + 1], pa, vb[2], vb[3]);
           }
@@ -597,9 +621,11 @@ __global__ void __launch_bounds__(128) decode_simt_kernel(const DecodeParams p) 
   __shared__ int s_ticket;
   constexpr int VEC = D / 32;  // floats per lane
   const int n_items = p.header[2];
-  const int item = blockIdx.x;
+  // heads vary fastest across CTAs: the CTAs that run side by side walk the same pages and read
+  // neighbouring head slices of each token row, which keeps DRAM rows open
+  const int item = blockIdx.x / p.kv_heads;
   if (item >= n_items) return;
-  const int h = blockIdx.y;
+  const int h = blockIdx.x - item * p.kv_heads;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nwarps = blockDim.x >> 5;
   const int R = p.rows;
@@ -685,8 +711,8 @@ DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count) {
   DecodeWsLayout w;
   const int group = a.kv_heads > 0 ? a.q_heads / a.kv_heads : 1;
   const int rows = group * a.q_len;
-  // about 6 resident-CTA waves of (item, kv head) pairs at 2 CTAs per SM
-  long long target = (static_cast<long long>(sm_count) * 2 * 6) / std::max(1, a.kv_heads);
+    // about 4 waves of (item, kv head) CTAs at 2 CTAs per SM: fewer, longer CTAs amortise start-up and merge
+  long long target = (static_cast<long long>(sm_count) * 2 * 4) / std::max(1, a.kv_heads);
   if (target < 1) target = 1;
   w.target_items = static_cast<int>(target);
   // keep the partial write (rows x D fp32) small next to the chunk's K/V bytes
@@ -699,6 +725,7 @@ DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count) {
   size_t off = kHeaderBytes;
   w.item_start_off = off; off = up(off + sizeof(int) * (static_cast<size_t>(a.batch) + 1));
   w.counters_off = off;   off = up(off + sizeof(int) * static_cast<size_t>(a.batch) * a.kv_heads);
+  w.info_off = off;       off = up(off + 32 * static_cast<size_t>(w.max_items));
   const size_t slots = static_cast<size_t>(w.max_items) * a.kv_heads;
   w.ml_off = off;         off = up(off + sizeof(float) * slots * rows * 2);
   w.o_off = off;          off = up(off + sizeof(float) * slots * rows * a.head_dim);
@@ -719,6 +746,7 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
   p.header = reinterpret_cast<int*>(ws);
   p.item_start = reinterpret_cast<int*>(ws + w.item_start_off);
   p.counters = reinterpret_cast<int*>(ws + w.counters_off);
+  p.item_info = reinterpret_cast<int4*>(ws + w.info_off);
   p.part_ml = reinterpret_cast<float*>(ws + w.ml_off);
   p.part_o = reinterpret_cast<float*>(ws + w.o_off);
   p.total_kv = a.total_kv; p.table_stride = a.table_stride;
@@ -734,7 +762,7 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
   }
   p.num_pages = a.layout == B200ATTN_PAGED ? static_cast<int>(std::min<long long>(a.total_kv / p.page_size, 0x7fffffff)) : 0;
   p.causal = a.causal_drafts ? 1 : 0;
-  p.box_rows = kTileN;
+  p.box_shift = 6;
   p.target_items = w.target_items; p.min_chunk = w.min_chunk; p.max_items = w.max_items;
   p.scale_log2 = a.sm_scale * 1.4426950408889634f;
 
@@ -742,7 +770,7 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "decode_plan_kernel launch");
 
-  const dim3 grid(w.max_items, a.kv_heads);
+  const dim3 grid(static_cast<unsigned>(w.max_items) * a.kv_heads, 1);
   const int D = a.head_dim;
   if (a.dtype == B200ATTN_F32) {
     const size_t smem = sizeof(float) * static_cast<size_t>(p.rows) * (D + 2);
@@ -753,35 +781,42 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
     const int nmt = p.n_mtiles;
     const int ksl = nmt <= 2 ? 4 : (nmt <= 4 ? 2 : 1);
     const int threads = 32 * (nmt * ksl + 1);   // + the producer warp
-    const size_t stage_bytes = static_cast<size_t>(kStages) * 2 * kTileN * D * 2;
+    // measured on B200 (paged decode, 32/8 heads): 2 stages with Q re-read from shared memory lets three CTAs share an
+    // SM and hides each CTA's start-up and merge behind its neighbours; the larger CTAs keep 3 stages
+    const int stages = threads <= 160 ? 2 : 3;
+    const size_t stage_bytes = static_cast<size_t>(stages) * 2 * kTileN * D * 2;
     const size_t comb_bytes = sizeof(float) * static_cast<size_t>(ksl) * nmt * 16 * (D + 2);
     const size_t smem = 1024 + std::max(stage_bytes, comb_bytes) + static_cast<size_t>(nmt) * 16 * D * 2 + sizeof(DecodeCtrl);
     // tensor maps over K and V: (D, heads, tokens), one box = 64 elements x 1 head x box_rows keys
     CUtensorMap tk, tv;
     int rc = 0;
-    long long tokens;
-    int heads;
-    p.box_rows = kTileN;
-    if (a.layout == B200ATTN_DENSE) { tokens = static_cast<long long>(a.batch) * a.kv_heads * a.max_kv; heads = 1; }
-    else { tokens = a.total_kv; heads = a.kv_heads; }
+    int box = kTileN;
     if (a.layout == B200ATTN_PAGED) {
-      int box = 1;
+      box = 1;
       while (box < kTileN && (a.page_size % (box * 2)) == 0) box *= 2;
-      p.box_rows = box;
     }
-    if ((rc = make_token_map(&tk, a.dtype, a.k, tokens, heads, D, p.box_rows))) return rc;
-    if ((rc = make_token_map(&tv, a.dtype, a.v, tokens, heads, D, p.box_rows))) return rc;
-#define B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, QREGS, MAXT, MINB)                                    \
-    do {                                                                                          \
-      rc = set_smem(decode_mma_kernel<TYPE, DIM, QREGS, MAXT, MINB>, smem);                       \
-      if (rc) return rc;                                                                          \
-      decode_mma_kernel<TYPE, DIM, QREGS, MAXT, MINB><<<grid, threads, smem, stream>>>(tk, tv, p);\
+    p.box_shift = 0;
+    while ((1 << p.box_shift) < box) ++p.box_shift;
+    if (a.layout == B200ATTN_DENSE) {
+      const long long rows = static_cast<long long>(a.batch) * a.kv_heads * a.max_kv;
+      if ((rc = make_kv_rows_map(&tk, a.dtype, a.k, rows, 1, D, box, D * 2ll, D * 2ll))) return rc;
+      if ((rc = make_kv_rows_map(&tv, a.dtype, a.v, rows, 1, D, box, D * 2ll, D * 2ll))) return rc;
+    } else {
+      const long long rstride = static_cast<long long>(a.kv_heads) * D * 2;
+      if ((rc = make_kv_rows_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box, rstride, D * 2ll))) return rc;
+      if ((rc = make_kv_rows_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box, rstride, D * 2ll))) return rc;
+    }
+#define B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, QREGS, STAGES, MAXT, MINB)                                    \
+    do {                                                                                                  \
+      rc = set_smem(decode_mma_kernel<TYPE, DIM, QREGS, STAGES, MAXT, MINB>, smem);                       \
+      if (rc) return rc;                                                                                  \
+      decode_mma_kernel<TYPE, DIM, QREGS, STAGES, MAXT, MINB><<<grid, threads, smem, stream>>>(tk, tv, p);\
     } while (0)
-#define B200ATTN_LAUNCH_DECODE(TYPE, DIM)                                         \
-    do {                                                                          \
-      if (threads <= 160) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, true, 160, 2);      \
-      else if (threads <= 224) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 224, 2);\
-      else B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 288, 1);                    \
+#define B200ATTN_LAUNCH_DECODE(TYPE, DIM)                                          \
+    do {                                                                           \
+      if (threads <= 160) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 2, 160, 3);   \
+      else if (threads <= 224) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 224, 2);\
+      else B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 288, 1);                  \
     } while (0)
     if (a.dtype == B200ATTN_BF16) {
       if (D == 128) B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 128); else B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 64);

@@ -20,6 +20,7 @@ struct DecodeParams {
   int* header;       // [0] error code, [1] chunk tokens, [2] number of work items
   int* item_start;   // [batch + 1] prefix of per-sequence chunk counts
   int* counters;     // [batch * kv_heads] merge tickets
+  int4* item_info;   // [max_items][2]: {sequence, chunk, chunks of the sequence, first item of the sequence}, {len, -, start lo, start hi}
   float* part_ml;    // [slot][rows][2]  (running max in log2 units, running sum)
   float* part_o;     // [slot][rows][D]  un-normalised accumulators
   long long total_kv;
@@ -37,7 +38,7 @@ struct DecodeParams {
   int page_size;
   int page_shift;    // log2(page_size) or -1
   int num_pages;
-  int box_rows;      // keys per TMA box (paged: a power of two that divides the page size)
+  int box_shift;     // log2 of the keys per TMA box (paged: the largest power of two that divides the page size, <= 64)
   int causal;
   int target_items;
   int min_chunk;
@@ -48,6 +49,7 @@ struct DecodeParams {
 struct DecodeWsLayout {
   size_t item_start_off;
   size_t counters_off;
+  size_t info_off;
   size_t ml_off;
   size_t o_off;
   size_t total;

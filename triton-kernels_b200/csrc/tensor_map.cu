@@ -47,4 +47,25 @@ int make_token_map(CUtensorMap* m, int dtype, const void* base, long long tokens
   return 0;
 }
 
+int make_kv_rows_map(CUtensorMap* m, int dtype, const void* base, long long rows, int heads, int D, int box_rows,
+                     long long row_stride_bytes, long long head_stride_bytes) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) { set_error("cuTensorMapEncodeTiled is not available from the driver"); return B200ATTN_E_CUDA; }
+  if (rows < 1) rows = 1;
+  const int chunks = D / 64;
+  const cuuint64_t dims[4] = {64, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(chunks), static_cast<cuuint64_t>(heads)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(row_stride_bytes), 128, static_cast<cuuint64_t>(head_stride_bytes)};
+  const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(chunks), 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUtensorMapDataType dt = dtype == B200ATTN_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult r = fn(m, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (4-D) failed with CUresult %d (rows=%lld heads=%d D=%d box_rows=%d)", static_cast<int>(r),
+              rows, heads, D, box_rows);
+    return B200ATTN_E_CUDA;
+  }
+  return 0;
+}
+
 }  // namespace b200attn

@@ -10,4 +10,10 @@ namespace b200attn {
 // `dtype` is B200ATTN_F16 or B200ATTN_BF16.  Returns 0 or a B200ATTN_E_* code.
 int make_token_map(CUtensorMap* m, int dtype, const void* base, long long tokens, int heads, int D, int box_rows);
 
+// 4-D map used by the decode kernels: dims (64 elements, token rows, D/64 column blocks, heads) with strides
+// (row_stride_bytes, 128, head_stride_bytes); box = 64 x box_rows x D/64 x 1, 128-byte swizzle.  One copy
+// brings box_rows keys of one head as [column block][row][128 B] into shared memory.
+int make_kv_rows_map(CUtensorMap* m, int dtype, const void* base, long long rows, int heads, int D, int box_rows,
+                     long long row_stride_bytes, long long head_stride_bytes);
+
 }  // namespace b200attn

@@ -31,12 +31,12 @@ class DecodePlan:
 def decode_plan(sm_count: int, batch: int, q_heads: int, kv_heads: int, q_len: int) -> DecodePlan:
     group = q_heads // kv_heads
     rows = group * q_len
-    target = max(1, (sm_count * 2 * 6) // max(1, kv_heads))
+    target = max(1, (sm_count * 2 * 4) // max(1, kv_heads))
     by_rows = -(-(rows * 8) // DECODE_TILE_TOKENS) * DECODE_TILE_TOKENS
     min_chunk = max(128, by_rows)
     tiles = -(-rows // 16)
-    slices = 4 if tiles == 1 else (2 if tiles <= 4 else 1)
-    return DecodePlan(target, min_chunk, target + batch, tiles, slices, 32 * tiles * slices)
+    slices = 4 if tiles <= 2 else (2 if tiles <= 4 else 1)
+    return DecodePlan(target, min_chunk, target + batch, tiles, slices, 32 * (tiles * slices + 1))
 
 
 def decode_chunk_tokens(plan: DecodePlan, lengths: Sequence[int]) -> int:
