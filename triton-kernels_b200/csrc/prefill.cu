@@ -46,6 +46,14 @@ constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
+// Development aid (compiled out unless B200ATTN_TRACE is defined): CTA (0,0,0) stamps clock64 into the
+// workspace behind the header, one slot per (role, iteration, event).
+#ifdef B200ATTN_TRACE
+#define TRACE_AT(idx) do { if (trace_on) p.header[64 + (idx)] = static_cast<int>(clock64() - trace_t0); } while (0)
+#else
+#define TRACE_AT(idx) do { } while (0)
+#endif
+
 struct CtaWork {
   int b;
   int pair;          // index of the 256-row query block inside the sequence
@@ -68,6 +76,7 @@ struct __align__(8) Control {
   uint32_t tmem_base;
   int work_b;
   int work_pair;
+  int work_head;
   int abort_flag;
 };
 
@@ -146,19 +155,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   Control* ctrl = reinterpret_cast<Control*>(smem + Plan::kCtrlOff);
   const uint32_t smem_base = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+#ifdef B200ATTN_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+  const long long trace_t0 = clock64();
+#endif
 
   // ---------------- which (sequence, q head, 256-row block) is this CTA? ----------------
   if (warp == 0) {
-    int wb = -1, wpair = 0;
+    int wb = -1, wpair = 0, whead = 0;
     if (p.layout == B200ATTN_RAGGED) {
-      if (!find_ragged_work(p, blockIdx.x, lane, &wb, &wpair)) wb = -1;
+      whead = blockIdx.x % p.q_heads;
+      if (!find_ragged_work(p, blockIdx.x / p.q_heads, lane, &wb, &wpair)) wb = -1;
     } else {
-      wb = blockIdx.z;
+      // 256-row blocks are the slowest-varying index and, under a causal mask, run heaviest first: every
+      // wave of CTAs holds equally heavy blocks of all (batch, head) pairs, and the q heads of one KV head
+      // run side by side and share its K/V in L2
+      const int per_block = p.q_heads * p.batch;
       const int npairs = pairs_of(p.max_q);
-      // causal: heaviest (last) blocks are scheduled first
-      wpair = p.is_causal ? (npairs - 1 - static_cast<int>(blockIdx.x)) : static_cast<int>(blockIdx.x);
+      const int blk = blockIdx.x / per_block, rest = blockIdx.x - blk * per_block;
+      wpair = p.is_causal ? (npairs - 1 - blk) : blk;
+      whead = rest % p.q_heads;
+      wb = rest / p.q_heads;
     }
-    if (lane == 0) { ctrl->work_b = wb; ctrl->work_pair = wpair; ctrl->abort_flag = 0; }
+    if (lane == 0) { ctrl->work_b = wb; ctrl->work_pair = wpair; ctrl->work_head = whead; ctrl->abort_flag = 0; }
   }
   if (tid == 0) {
     mbar_init(smem_u32(&ctrl->q_full), 1);
@@ -176,7 +195,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   w.pair = ctrl->work_pair;
   if (w.b < 0) return;  // whole CTA: nothing allocated yet
 
-  const int q_head = blockIdx.y;
+  const int q_head = ctrl->work_head;
   const int kv_head = q_head / p.group;
   if (p.layout == B200ATTN_RAGGED) {
     const long long qa = load_index(p.q_indptr, p.indptr_is_i64, w.b);
@@ -306,6 +325,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       issued = e + 1;
+      TRACE_AT(3072 + e);
     }
     if (!ok) {
       if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
@@ -361,8 +381,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       bool v_ready = false;
       for (int s = 0; s < kSlots && ok; ++s) {
         if (j >= nkv[s]) continue;
+        TRACE_AT(2048 + (j * 2 + s) * 4 + 0);
         ok = warp_wait(smem_u32(&ctrl->p_ready[s]), j & 1);
         if (!ok) break;
+        TRACE_AT(2048 + (j * 2 + s) * 4 + 1);
         if (!v_ready) {
           ok = ring_full_wait(2 * j + 1);
           if (!ok) break;
@@ -384,12 +406,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         tc_fence_after();
         issue_pv(s, j);
+        TRACE_AT(2048 + (j * 2 + s) * 4 + 2);
         if (j + 1 < nkv[s]) {
           ok = ring_full_wait(2 * (j + 1));
           if (!ok) break;
           tc_fence_after();
           issue_s(s, j + 1);
         }
+        TRACE_AT(2048 + (j * 2 + s) * 4 + 3);
       }
       if (!ok) break;
       if (lane == 0) {
@@ -413,29 +437,51 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     float l = 0.f;
     bool ok = true;
     for (int j = 0; j < n; ++j) {
+      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 0);
       ok = warp_wait(smem_u32(&ctrl->s_full[s]), j & 1);
       if (!ok || *abort_flag) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[kBN];
-#pragma unroll
-      for (int c = 0; c < kBN / 32; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
-      tmem_wait_ld();
-      // masking is needed only on the tile that holds the sequence end or the causal diagonal
+      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 1);
+      // Two passes over the S row in TMEM, 32 columns at a time, the next chunk in flight while the current
+      // one is processed: pass 1 finds the row max, pass 2 exponentiates and writes P over the consumed
+      // columns.  Masking is needed only on the tile that holds the sequence end or the causal diagonal.
       int limit = w.len_k - 1 - j * kBN;
       if (p.is_causal) limit = min(limit, row_abs - j * kBN);
-      float mx = -INFINITY;
-      if (limit < kBN - 1) {
+      const bool masked = limit < kBN - 1;
+      uint32_t ca[32], cb[32];
+      float mx;
+      {
+        float mxs[4];
+        auto chunk_max = [&](const uint32_t (&v)[32], int c) {
+          float m = max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
 #pragma unroll
-        for (int c = 0; c < kBN; ++c) {
-          const float x = (c <= limit) ? __uint_as_float(sv[c]) : -INFINITY;
-          sv[c] = __float_as_uint(x);
-          mx = fmaxf(mx, x);
-        }
-      } else {
+          for (int i = 3; i + 1 < 32; i += 2) m = max3(m, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+          mxs[c] = fmaxf(m, __uint_as_float(v[31]));
+        };
+        auto chunk_mask = [&](uint32_t (&v)[32], int c) {
+          if (masked) {
 #pragma unroll
-        for (int c = 0; c < kBN; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
+            for (int i = 0; i < 32; ++i) if (c * 32 + i > limit) v[i] = 0xff800000u;  // -inf
+          }
+        };
+        tmem_ld32(tS, ca);
+        tmem_wait_ld();
+        tmem_ld32(tS + 32, cb);
+        chunk_mask(ca, 0); chunk_max(ca, 0);
+        tmem_wait_ld();
+        tmem_ld32(tS + 64, ca);
+        chunk_mask(cb, 1); chunk_max(cb, 1);
+        tmem_wait_ld();
+        tmem_ld32(tS + 96, cb);
+        chunk_mask(ca, 2); chunk_max(ca, 2);
+        tmem_wait_ld();
+        tmem_ld32(tS, ca);            // first chunk of pass 2
+        chunk_mask(cb, 3); chunk_max(cb, 3);
+        mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
       }
+      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 2);
       const float m_new = fmaxf(m_used, mx * sl2);
+      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 3);
       const bool need = (m_new - m_used) > kRescaleThreshold;   // false for NaN / (-inf)-(-inf)
       float alpha = 1.f;
       if (need) { alpha = fast_exp2(m_used - m_new); m_used = m_new; l *= alpha; }
@@ -457,25 +503,45 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       }
+      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 4);
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float neg_m = -m_eff;
-      float rs = 0.f;
+      float rs0 = 0.f, rs1 = 0.f;
+      auto chunk_exp = [&](const uint32_t (&v)[32], int c) {
+        uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < kBN / 64; ++c) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c * 64 + 2 * i]), sl2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c * 64 + 2 * i + 1]), sl2, neg_m));
-          rs += p0 + p1;
+        for (int i = 0; i < 16; ++i) {
+          float x0 = __uint_as_float(v[2 * i]), x1 = __uint_as_float(v[2 * i + 1]);
+          if (masked) {
+            if (c * 32 + 2 * i > limit) x0 = -INFINITY;
+            if (c * 32 + 2 * i + 1 > limit) x1 = -INFINITY;
+          }
+          const float p0 = fast_exp2(fmaf(x0, sl2, neg_m));
+          const float p1 = fast_exp2(fmaf(x1, sl2, neg_m));
+          rs0 += p0;
+          rs1 += p1;
           pk[i] = ElemTraits<T>::pack2(p0, p1);
         }
-        tmem_st32(tS + c * 32, pk);
-      }
+        tmem_st16(tS + c * 16, pk);
+      };
+      tmem_wait_ld();
+      tmem_ld32(tS + 32, cb);
+      chunk_exp(ca, 0);
+      tmem_wait_ld();
+      tmem_ld32(tS + 64, ca);
+      chunk_exp(cb, 1);
+      tmem_wait_ld();
+      tmem_ld32(tS + 96, cb);
+      chunk_exp(ca, 2);
+      tmem_wait_ld();
+      chunk_exp(cb, 3);
+      const float rs = rs0 + rs1;
       l += rs;
+      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 5);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&ctrl->p_ready[s]));
+      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 6);
     }
     // ---------------- epilogue ----------------
     if (ok && n > 0) ok = warp_wait(smem_u32(&ctrl->o_done[s]), (n - 1) & 1);
@@ -641,7 +707,7 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, cudaStream_t stream) {
     if ((rc = make_token_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, kBN))) return rc;
     if ((rc = make_token_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, kBN))) return rc;
     const long long pairs = a.total_q / (2 * kBM) + a.batch;
-    grid = dim3(static_cast<unsigned>(pairs), a.q_heads, 1);
+    grid = dim3(static_cast<unsigned>(pairs * a.q_heads), 1, 1);
   } else {
     const long long q_rows = static_cast<long long>(a.batch) * a.q_heads * a.max_q;
     if ((rc = make_token_map(&tq, a.dtype, a.q, q_rows, 1, D, kBM))) return rc;
@@ -658,7 +724,7 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, cudaStream_t stream) {
       if ((rc = make_token_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box))) return rc;
       if ((rc = make_token_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box))) return rc;
     }
-    grid = dim3((a.max_q + 2 * kBM - 1) / (2 * kBM), a.q_heads, a.batch);
+    grid = dim3(static_cast<unsigned>((a.max_q + 2 * kBM - 1) / (2 * kBM)) * a.q_heads * a.batch, 1, 1);
   }
   if (grid.x == 0 || grid.y == 0 || grid.z == 0) return B200ATTN_OK;
 
