@@ -38,13 +38,22 @@ namespace {
 using namespace ptx;
 
 constexpr int kBM = 128;           // query rows per slot
-constexpr int kBN = 128;           // keys per tile
+constexpr int kBN = 128;           // keys per K/V tile
+constexpr int kHalf = 64;          // keys per softmax / MMA step
 constexpr int kSlots = 2;
 constexpr int kRing = 4;           // K/V ring buffers (K_j, V_j alternate)
-constexpr int kThreads = 384;
-constexpr int kProducerWarp = 8;
-constexpr int kMmaWarp = 9;
+constexpr int kSoftmaxWarps = 16;  // 4 warpgroups: (slot 0 | slot 1) x (columns 0-63 | 64-127)
+constexpr int kThreads = 576;
+constexpr int kProducerWarp = 16;
+constexpr int kMmaWarp = 17;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+// Of every 4 pairs of scores, this many are exponentiated on the FMA pipes (range reduction + cubic
+// polynomial, relative error 7.5e-5, far below the 16-bit rounding of P) instead of the MUFU unit,
+// which at 16 results per clock per SM is as scarce as the tensor pipe at head_dim 128.
+#ifndef B200ATTN_EXP_EMU_OF4
+#define B200ATTN_EXP_EMU_OF4 0
+#endif
+constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
 
 // Development aid (compiled out unless B200ATTN_TRACE is defined): CTA (0,0,0) stamps clock64 into the
 // workspace behind the header, one slot per (role, iteration, event).
@@ -73,6 +82,8 @@ struct __align__(8) Control {
   uint64_t s_full[kSlots];
   uint64_t p_ready[kSlots];
   uint64_t o_done[kSlots];
+  uint64_t xchg_bar[kSlots];
+  float xchg[2][kSlots][2][kBM];   // [tile parity][slot][column half][row]: row max / final row sum exchange
   uint32_t tmem_base;
   int work_b;
   int work_pair;
@@ -184,8 +195,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int i = 0; i < kRing; ++i) { mbar_init(smem_u32(&ctrl->kv_full[i]), 1); mbar_init(smem_u32(&ctrl->kv_empty[i]), 1); }
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_u32(&ctrl->s_full[s]), 1);
-      mbar_init(smem_u32(&ctrl->p_ready[s]), kBM);
+      mbar_init(smem_u32(&ctrl->p_ready[s]), 2 * kBM);
       mbar_init(smem_u32(&ctrl->o_done[s]), 1);
+      mbar_init(smem_u32(&ctrl->xchg_bar[s]), 2 * kBM);
     }
     mbar_fence_init();
   }
@@ -241,7 +253,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     nkv[s] = n;
     nkv_max = max(nkv_max, n);
   }
-
   // ---------------- TMEM allocation (MMA warp owns it) ----------------
   if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
@@ -341,28 +352,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     auto ring_full_wait = [&](int e) -> bool {
       return warp_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
     };
+    // Descriptor words are prepared once: the high words never change, the low words are a base
+    // (start address >> 4) plus small constants, so issuing one MMA costs the single thread a few adds.
+    const uint64_t kdesc = make_smem_desc_sw128(smem_base, 16);                    // K-major operands (Q, K)
+    const uint64_t vdesc = make_smem_desc_sw128(smem_base, Plan::kChunkBytes);     // MN-major operand (V)
+    const uint32_t k_hi = static_cast<uint32_t>(kdesc >> 32), v_hi = static_cast<uint32_t>(vdesc >> 32);
+    const uint32_t k_lo = static_cast<uint32_t>(kdesc), v_lo = static_cast<uint32_t>(vdesc);
     auto issue_s = [&](int s, int j) {
       // S_s = Q_s K_j^T : K-major A and B, D/16 k-steps
       if (lane == 0) {
-        const uint32_t qa = smem_base + Plan::kQOff + s * Plan::kTileBytes;
-        const uint32_t kb = smem_base + Plan::kRingOff + ((2 * j) % kRing) * Plan::kTileBytes;
+        const uint32_t qa_lo = k_lo + ((Plan::kQOff + s * Plan::kTileBytes) >> 4);
+        const uint32_t kb_lo = k_lo + ((Plan::kRingOff + ((2 * j) % kRing) * Plan::kTileBytes) >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * Plan::kChunkBytes + (kk & 3) * 32;
-          mma_ss(tmem_S[s], make_smem_desc_sw128(qa + off, 16), make_smem_desc_sw128(kb + off, 16), idesc_s, kk > 0);
+          const uint32_t off = ((kk >> 2) * Plan::kChunkBytes + (kk & 3) * 32) >> 4;
+          mma_ss_lohi(tmem_S[s], qa_lo + off, k_hi, kb_lo + off, k_hi, idesc_s, kk > 0);
         }
         mma_commit(smem_u32(&ctrl->s_full[s]));
       }
       __syncwarp();
     };
     auto issue_pv = [&](int s, int j) {
-      // O_s (+)= P_s V_j : A = packed 16-bit P in TMEM (8 columns per k-step), B = V, MN-major
+      // O_s (+)= P_s V_j : A = packed 16-bit P in TMEM, B = V, MN-major.  P of columns 0-63 sits in TMEM columns
+      // 0-31 of the S tile and P of columns 64-127 in TMEM columns 64-95 (each warpgroup writes over its own half).
       if (lane == 0) {
-        const uint32_t vb = smem_base + Plan::kRingOff + ((2 * j + 1) % kRing) * Plan::kTileBytes;
+        const uint32_t vb_lo = v_lo + ((Plan::kRingOff + ((2 * j + 1) % kRing) * Plan::kTileBytes) >> 4);
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
-          mma_ts(tmem_O[s], tmem_S[s] + kk * 8, make_smem_desc_sw128(vb + kk * 16 * 128, Plan::kChunkBytes), idesc_o,
-                 (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts_lohi(tmem_O[s], tmem_S[s] + (kk >> 2) * kHalf + (kk & 3) * 8, vb_lo + ((kk * 16 * 128) >> 4), v_hi, idesc_o,
+                      (j > 0 || kk > 0) ? 1u : 0u);
         }
         mma_commit(smem_u32(&ctrl->o_done[s]));
       }
@@ -423,128 +441,154 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       __syncwarp();
     }
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
-  } else if (warp < kSlots * 4) {
+  } else if (warp < kSoftmaxWarps) {
     // =========================== softmax warpgroups ===========================
-    const int s = warp >> 2;
-    const int row = tid - s * kBM;                      // 0..127 inside the slot
+    // Warpgroup g = warp / 4 serves slot (g & 1) and the column half (g >> 1) of its score tile: thread `row`
+    // of the warpgroup owns 64 of the 128 scores of query row `row`; the two threads of a row agree on the row
+    // max through shared memory (an mbarrier, so the wait is bounded) and keep separate partial row sums.
+    const int g = warp >> 2;
+    const int s = g & 1;
+    const int half = g >> 1;
+    const int row = (warp & 3) * 32 + lane;             // 0..127 inside the slot
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem_S[s] + lane_off;
-    const uint32_t tO = tmem_O[s] + lane_off;
+    const uint32_t tSh = tmem_S[s] + lane_off + half * kHalf;
+    constexpr int kOCols = D / 2;                       // O columns rescaled / written out by this thread
+    const uint32_t tOh = tmem_O[s] + lane_off + half * kOCols;
     const int row_abs = m0[s] + row;                    // query index inside the sequence
     const int n = nkv[s];
     const float sl2 = p.scale_log2;
+    const bool tracer = (warp & 3) == 0 && half == 0;
     float m_used = -INFINITY;   // exponent reference currently baked into O and l
-    float l = 0.f;
+    float l = 0.f;              // partial row sum over this thread's columns
     bool ok = true;
     for (int j = 0; j < n; ++j) {
-      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 0);
+      if (tracer) TRACE_AT(s * 1024 + j * 8 + 0);
       ok = warp_wait(smem_u32(&ctrl->s_full[s]), j & 1);
       if (!ok || *abort_flag) { ok = false; break; }
       tc_fence_after();
-      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 1);
-      // Two passes over the S row in TMEM, 32 columns at a time, the next chunk in flight while the current
-      // one is processed: pass 1 finds the row max, pass 2 exponentiates and writes P over the consumed
-      // columns.  Masking is needed only on the tile that holds the sequence end or the causal diagonal.
-      int limit = w.len_k - 1 - j * kBN;
-      if (p.is_causal) limit = min(limit, row_abs - j * kBN);
-      const bool masked = limit < kBN - 1;
-      uint32_t ca[32], cb[32];
+      if (tracer) TRACE_AT(s * 1024 + j * 8 + 1);
+      // masking is needed only on the tile that holds the sequence end or the causal diagonal
+      int limit = w.len_k - 1 - j * kBN - half * kHalf;
+      if (p.is_causal) limit = min(limit, row_abs - j * kBN - half * kHalf);
+      const bool masked = limit < kHalf - 1;
       float mx;
       {
-        float mxs[4];
-        auto chunk_max = [&](const uint32_t (&v)[32], int c) {
-          float m = max3(__uint_as_float(v[0]), __uint_as_float(v[1]), __uint_as_float(v[2]));
+        // pass 1: the max of this thread's 64 scores (they are read again in pass 2; holding them across the
+        // exchange below would cost 64 registers per thread)
+        uint32_t ca[32], cb[32];
+        tmem_ld32(tSh, ca);
+        tmem_ld32(tSh + 32, cb);
+        tmem_wait_ld();
+        if (masked) {
 #pragma unroll
-          for (int i = 3; i + 1 < 32; i += 2) m = max3(m, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-          mxs[c] = fmaxf(m, __uint_as_float(v[31]));
-        };
-        auto chunk_mask = [&](uint32_t (&v)[32], int c) {
-          if (masked) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) if (c * 32 + i > limit) v[i] = 0xff800000u;  // -inf
+          for (int i = 0; i < 32; ++i) {
+            if (i > limit) ca[i] = 0xff800000u;        // -inf
+            if (32 + i > limit) cb[i] = 0xff800000u;
           }
-        };
-        tmem_ld32(tS, ca);
-        tmem_wait_ld();
-        tmem_ld32(tS + 32, cb);
-        chunk_mask(ca, 0); chunk_max(ca, 0);
-        tmem_wait_ld();
-        tmem_ld32(tS + 64, ca);
-        chunk_mask(cb, 1); chunk_max(cb, 1);
-        tmem_wait_ld();
-        tmem_ld32(tS + 96, cb);
-        chunk_mask(ca, 2); chunk_max(ca, 2);
-        tmem_wait_ld();
-        tmem_ld32(tS, ca);            // first chunk of pass 2
-        chunk_mask(cb, 3); chunk_max(cb, 3);
-        mx = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+        }
+        float ma = max3(__uint_as_float(ca[0]), __uint_as_float(ca[1]), __uint_as_float(ca[2]));
+        float mb = max3(__uint_as_float(cb[0]), __uint_as_float(cb[1]), __uint_as_float(cb[2]));
+#pragma unroll
+        for (int i = 3; i + 1 < 32; i += 2) {
+          ma = max3(ma, __uint_as_float(ca[i]), __uint_as_float(ca[i + 1]));
+          mb = max3(mb, __uint_as_float(cb[i]), __uint_as_float(cb[i + 1]));
+        }
+        mx = max3(ma, mb, fmaxf(__uint_as_float(ca[31]), __uint_as_float(cb[31])));
       }
-      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 2);
+      // exchange the half-row maxima
+      ctrl->xchg[j & 1][s][half][row] = mx;
+      mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
+      ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), j & 1);
+      if (!ok) break;
+      mx = fmaxf(mx, ctrl->xchg[j & 1][s][half ^ 1][row]);
+      if (tracer) TRACE_AT(s * 1024 + j * 8 + 2);
       const float m_new = fmaxf(m_used, mx * sl2);
-      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 3);
+      if (tracer) TRACE_AT(s * 1024 + j * 8 + 3);
       const bool need = (m_new - m_used) > kRescaleThreshold;   // false for NaN / (-inf)-(-inf)
       float alpha = 1.f;
       if (need) { alpha = fast_exp2(m_used - m_new); m_used = m_new; l *= alpha; }
-      if (j > 0) {
-        // PV(j-1) must have landed in O before it is touched (always true once S(j) is visible,
-        // the wait keeps the barrier phase in step)
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
+        // PV(j-1) has landed in O once S(j) is visible (the MMAs complete in issue order); waiting on its
+        // barrier phase (j-1) is then immediate, and skipping the wait on other iterations is harmless
+        // because the barrier can never run two phases ahead of this warpgroup
         ok = warp_wait(smem_u32(&ctrl->o_done[s]), (j - 1) & 1);
         if (!ok) break;
-        if (__any_sync(0xffffffffu, need)) {
-          tc_fence_after();
+        tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t ov[32];
-            tmem_ld32(tO + c * 32, ov);
-            tmem_wait_ld();
+        for (int c = 0; c < kOCols / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld32(tOh + c * 32, ov);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st32(tO + c * 32, ov);
-          }
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st32(tOh + c * 32, ov);
         }
       }
-      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 4);
+      if (tracer) TRACE_AT(s * 1024 + j * 8 + 4);
       const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
       const float neg_m = -m_eff;
-      float rs0 = 0.f, rs1 = 0.f;
-      auto chunk_exp = [&](const uint32_t (&v)[32], int c) {
+      uint64_t rs2 = pack_f2(0.f, 0.f);
+      const uint64_t sl2_2 = pack_f2(sl2, sl2), negm_2 = pack_f2(neg_m, neg_m);
+      auto chunk_exp = [&](int c) {
+        uint32_t v[32];
+        tmem_ld32(tSh + c * 32, v);
+        tmem_wait_ld();
+        if (masked) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (c * 32 + i > limit) v[i] = 0xff800000u;   // -inf
+        }
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float x0 = __uint_as_float(v[2 * i]), x1 = __uint_as_float(v[2 * i + 1]);
-          if (masked) {
-            if (c * 32 + 2 * i > limit) x0 = -INFINITY;
-            if (c * 32 + 2 * i + 1 > limit) x1 = -INFINITY;
+          const uint64_t t2 = fma_f2(pack_f2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), sl2_2, negm_2);
+          float p0, p1;
+          if ((i & 3) < kExpEmuOf4) {
+            // 2^t = 2^n * 2^r with n = round(t), r in [-0.5, 0.5]; n is read off the magic-number sum
+            float a, b;
+            unpack_f2(t2, a, b);
+            const uint64_t tc = pack_f2(fmaxf(a, -126.f), fmaxf(b, -126.f));
+            const uint64_t tm = add_f2(tc, pack_f2(12582912.f, 12582912.f));
+            const uint64_t nf = add_f2(tm, pack_f2(-12582912.f, -12582912.f));
+            const uint64_t r = fma_f2(nf, pack_f2(-1.f, -1.f), tc);
+            uint64_t q = fma_f2(r, pack_f2(0.055171482f, 0.055171482f), pack_f2(0.2426109f, 0.2426109f));
+            q = fma_f2(q, r, pack_f2(0.69326097f, 0.69326097f));
+            q = fma_f2(q, r, pack_f2(0.99992812f, 0.99992812f));
+            float q0, q1, m0f, m1f;
+            unpack_f2(q, q0, q1);
+            unpack_f2(tm, m0f, m1f);
+            p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(m0f) << 23));
+            p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(m1f) << 23));
+          } else {
+            float a, b;
+            unpack_f2(t2, a, b);
+            p0 = fast_exp2(a);
+            p1 = fast_exp2(b);
           }
-          const float p0 = fast_exp2(fmaf(x0, sl2, neg_m));
-          const float p1 = fast_exp2(fmaf(x1, sl2, neg_m));
-          rs0 += p0;
-          rs1 += p1;
+          rs2 = add_f2(rs2, pack_f2(p0, p1));
           pk[i] = ElemTraits<T>::pack2(p0, p1);
         }
-        tmem_st16(tS + c * 16, pk);
+        tmem_st16(tSh + c * 16, pk);
       };
-      tmem_wait_ld();
-      tmem_ld32(tS + 32, cb);
-      chunk_exp(ca, 0);
-      tmem_wait_ld();
-      tmem_ld32(tS + 64, ca);
-      chunk_exp(cb, 1);
-      tmem_wait_ld();
-      tmem_ld32(tS + 96, cb);
-      chunk_exp(ca, 2);
-      tmem_wait_ld();
-      chunk_exp(cb, 3);
-      const float rs = rs0 + rs1;
-      l += rs;
-      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 5);
+      chunk_exp(0);
+      chunk_exp(1);
+      float rs0, rs1;
+      unpack_f2(rs2, rs0, rs1);
+      l += rs0 + rs1;
+      if (tracer) TRACE_AT(s * 1024 + j * 8 + 5);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&ctrl->p_ready[s]));
-      if ((warp & 3) == 0) TRACE_AT(s * 1024 + j * 8 + 6);
+      if (tracer) TRACE_AT(s * 1024 + j * 8 + 6);
     }
     // ---------------- epilogue ----------------
     if (ok && n > 0) ok = warp_wait(smem_u32(&ctrl->o_done[s]), (n - 1) & 1);
+    if (ok) {
+      // total row sum = this thread's partial + its partner's (one more exchange, parity n & 1)
+      ctrl->xchg[n & 1][s][half][row] = l;
+      mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
+      ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), n & 1);
+      if (ok) l += ctrl->xchg[n & 1][s][half ^ 1][row];
+    }
     if (!ok) {
       if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
     } else if (m0[s] < w.len_q) {
@@ -552,16 +596,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int rows_valid = min(kBM, w.len_q - m0[s]);
       if constexpr (std::is_same<OutT, float>::value) {
-        // fp32 output: every thread stores its own row, 128 contiguous bytes per TMEM chunk
+        // fp32 output: every thread stores its own half row, 128 contiguous bytes per TMEM chunk
         float* out = static_cast<float*>(p.out);
         long long off;
         if (p.layout == B200ATTN_RAGGED) off = ((w.q_row0 + m0[s] + row) * p.q_heads + q_head) * D;
         else off = (w.q_row0 + m0[s] + row) * D;
+        off += half * kOCols;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < kOCols / 32; ++c) {
           uint32_t ov[32];
           if (n > 0) {
-            tmem_ld32(tO + c * 32, ov);
+            tmem_ld32(tOh + c * 32, ov);
             tmem_wait_ld();
           } else {
 #pragma unroll
@@ -576,13 +621,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
       } else {
-        unsigned char* stage = smem + Plan::kQOff + s * Plan::kTileBytes;  // [128][D] 16-bit, 16-byte pieces XOR-swizzled
-        constexpr int kPieces = D * 2 / 16;
+        // 16-bit output: stage the half rows in the dead Q buffer ([128][D] 16-bit, 16-byte pieces XOR-swizzled),
+        // then each warp writes its own 32 half rows with 16-byte stores
+        unsigned char* stage = smem + Plan::kQOff + s * Plan::kTileBytes;
+        constexpr int kPieces = kOCols * 2 / 16;   // 16-byte pieces per half row
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = 0; c < kOCols / 32; ++c) {
           uint32_t ov[32];
           if (n > 0) {
-            tmem_ld32(tO + c * 32, ov);
+            tmem_ld32(tOh + c * 32, ov);
             tmem_wait_ld();
           } else {
 #pragma unroll
@@ -595,19 +642,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             u.y = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
             u.z = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
             u.w = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
-            const int piece = c * 4 + q4;
+            const int piece = half * kPieces + c * 4 + q4;
             *reinterpret_cast<uint4*>(stage + row * (D * 2) + ((piece ^ (row & 7)) << 4)) = u;
           }
         }
         __syncwarp();
-        // coalesced write-out of this warp's own 32 rows: kPieces lanes cover one row
         T* out = static_cast<T*>(p.out);
         constexpr int kRowsPerPass = 32 / kPieces;
-        const int piece = lane % kPieces;
+        const int pl = lane % kPieces;
         const int wrow0 = (warp & 3) * 32;
         for (int rr = lane / kPieces; rr < 32; rr += kRowsPerPass) {
           const int r = wrow0 + rr;
           if (r >= rows_valid) break;
+          const int piece = half * kPieces + pl;
           const uint4 u = *reinterpret_cast<const uint4*>(stage + r * (D * 2) + ((piece ^ (r & 7)) << 4));
           long long off;
           if (p.layout == B200ATTN_RAGGED) off = ((w.q_row0 + m0[s] + r) * p.q_heads + q_head) * D;
