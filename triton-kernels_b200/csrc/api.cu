@@ -129,7 +129,7 @@ int b200attn_prefill(const b200attn_prefill_args_t* a, void* cuda_stream) {
   if (a->batch == 0) return B200ATTN_OK;
   DeviceGuard guard;
   if ((rc = guard.enter(a->device))) return rc;
-  return launch_prefill(*a, static_cast<cudaStream_t>(cuda_stream));
+  return launch_prefill(*a, info.sm_count, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int b200attn_decode(const b200attn_decode_args_t* a, void* cuda_stream) {

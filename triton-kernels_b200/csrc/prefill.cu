@@ -63,31 +63,22 @@ constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
 #define TRACE_AT(idx) do { } while (0)
 #endif
 
-struct CtaWork {
-  int b;
-  int pair;          // index of the 256-row query block inside the sequence
-  int len_q;
-  int len_k;
-  long long q_row0;  // first q row of the sequence in the q tensor map's token axis
-  long long kv_row0; // first kv row of the sequence (dense / ragged)
-  int q_head_coord;  // head coordinate in the q tensor map
-  int kv_head_coord;
-};
-
 // shared-memory control block placed after the tiles
 struct __align__(8) Control {
   uint64_t q_full;
+  uint64_t q_empty;
   uint64_t kv_full[kRing];
   uint64_t kv_empty[kRing];
   uint64_t s_full[kSlots];
   uint64_t p_ready[kSlots];
   uint64_t o_done[kSlots];
   uint64_t xchg_bar[kSlots];
+  uint64_t o_free[kSlots];
+  uint64_t sched_full[2];
+  uint64_t sched_empty[2];
+  int sched_item[2];
   float xchg[2][kSlots][2][kBM];   // [tile parity][slot][column half][row]: row max / final row sum exchange
   uint32_t tmem_base;
-  int work_b;
-  int work_pair;
-  int work_head;
   int abort_flag;
 };
 
@@ -155,6 +146,90 @@ __global__ void __launch_bounds__(256) cast_f32_to_f16_kernel(const float4* __re
   }
 }
 
+// Everything one work item (sequence, q head, 256-row query block) needs, derived by each warp on its own
+// from the item index so that the roles never exchange it.
+struct ItemWork {
+  bool valid;
+  int q_head;
+  int len_q, len_k;
+  long long q_row0;    // first q row of the sequence on the token axis of the q tensor map
+  long long kv_row0;   // first kv row of the sequence (dense / ragged)
+  int q_head_coord, kv_head_coord;
+  int b;
+  int m0[kSlots];      // first query row of each slot inside the sequence
+  int nkv[kSlots];     // 128-key tiles each slot visits
+  int nkv_max;
+};
+
+__device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item, int lane) {
+  ItemWork w;
+  int wb = -1, wpair = 0, whead = 0;
+  if (p.layout == B200ATTN_RAGGED) {
+    whead = item % p.q_heads;
+    if (!find_ragged_work(p, item / p.q_heads, lane, &wb, &wpair)) wb = -1;
+  } else {
+    // 256-row blocks are the slowest-varying index and, under a causal mask, are handed out heaviest first;
+    // the q heads of one KV head are neighbours and share its K/V in L2
+    const int per_block = p.q_heads * p.batch;
+    const int npairs = pairs_of(p.max_q);
+    const int blk = item / per_block, rest = item - blk * per_block;
+    wpair = p.is_causal ? (npairs - 1 - blk) : blk;
+    whead = rest % p.q_heads;
+    wb = rest / p.q_heads;
+  }
+  w.valid = wb >= 0;
+  w.b = wb;
+  w.q_head = whead;
+  w.len_q = w.len_k = 0;
+  w.q_row0 = w.kv_row0 = 0;
+  w.q_head_coord = w.kv_head_coord = 0;
+  if (w.valid) {
+    const int kv_head = whead / p.group;
+    if (p.layout == B200ATTN_RAGGED) {
+      const long long qa = load_index(p.q_indptr, p.indptr_is_i64, wb);
+      const long long qe = load_index(p.q_indptr, p.indptr_is_i64, wb + 1);
+      const long long ka = load_index(p.kv_indptr, p.indptr_is_i64, wb);
+      const long long ke = load_index(p.kv_indptr, p.indptr_is_i64, wb + 1);
+      w.len_q = static_cast<int>(qe > qa ? qe - qa : 0);
+      w.len_k = static_cast<int>(ke > ka ? ke - ka : 0);
+      w.q_row0 = qa;
+      w.kv_row0 = ka;
+      w.q_head_coord = whead;
+      w.kv_head_coord = kv_head;
+    } else {
+      w.len_q = p.max_q;
+      w.q_row0 = (static_cast<long long>(wb) * p.q_heads + whead) * p.max_q;
+      if (p.layout == B200ATTN_DENSE) {
+        w.len_k = p.max_kv;
+        w.kv_row0 = (static_cast<long long>(wb) * p.kv_heads + kv_head) * p.max_kv;
+      } else {
+        long long n = load_index(p.kv_indptr, p.indptr_is_i64, wb);
+        const long long cap = p.table_stride * static_cast<long long>(p.page_size);
+        n = n < 0 ? 0 : (n > cap ? cap : n);
+        w.len_k = static_cast<int>(n);
+        w.kv_head_coord = kv_head;
+      }
+    }
+  }
+  w.nkv_max = 0;
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+    w.m0[s] = (wpair * kSlots + s) * kBM;
+    int n = 0;
+    if (w.valid && w.m0[s] < w.len_q) {
+      int kv_hi = w.len_k;
+      if (p.is_causal) kv_hi = min(kv_hi, min(w.m0[s] + kBM, w.len_q));
+      n = (kv_hi + kBN - 1) / kBN;
+    }
+    w.nkv[s] = n;
+    w.nkv_max = max(w.nkv_max, n);
+  }
+  return w;
+}
+
+// Persistent kernel: one CTA per SM; work items are drawn from a global counter (heaviest first).
+// The producer warp is also the scheduler: it publishes item indices through a 2-deep ring, so it can fetch Q
+// and the first K/V tiles of the next item while the other roles finish the current one.
 template <typename T, int D, typename OutT>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -167,91 +242,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t smem_base = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 #ifdef B200ATTN_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0;
+  const bool trace_on = blockIdx.x == 0 && lane == 0;
   const long long trace_t0 = clock64();
 #endif
 
-  // ---------------- which (sequence, q head, 256-row block) is this CTA? ----------------
-  if (warp == 0) {
-    int wb = -1, wpair = 0, whead = 0;
-    if (p.layout == B200ATTN_RAGGED) {
-      whead = blockIdx.x % p.q_heads;
-      if (!find_ragged_work(p, blockIdx.x / p.q_heads, lane, &wb, &wpair)) wb = -1;
-    } else {
-      // 256-row blocks are the slowest-varying index and, under a causal mask, run heaviest first: every
-      // wave of CTAs holds equally heavy blocks of all (batch, head) pairs, and the q heads of one KV head
-      // run side by side and share its K/V in L2
-      const int per_block = p.q_heads * p.batch;
-      const int npairs = pairs_of(p.max_q);
-      const int blk = blockIdx.x / per_block, rest = blockIdx.x - blk * per_block;
-      wpair = p.is_causal ? (npairs - 1 - blk) : blk;
-      whead = rest % p.q_heads;
-      wb = rest / p.q_heads;
-    }
-    if (lane == 0) { ctrl->work_b = wb; ctrl->work_pair = wpair; ctrl->work_head = whead; ctrl->abort_flag = 0; }
-  }
   if (tid == 0) {
     mbar_init(smem_u32(&ctrl->q_full), 1);
+    mbar_init(smem_u32(&ctrl->q_empty), 1);
     for (int i = 0; i < kRing; ++i) { mbar_init(smem_u32(&ctrl->kv_full[i]), 1); mbar_init(smem_u32(&ctrl->kv_empty[i]), 1); }
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_u32(&ctrl->s_full[s]), 1);
       mbar_init(smem_u32(&ctrl->p_ready[s]), 2 * kBM);
       mbar_init(smem_u32(&ctrl->o_done[s]), 1);
       mbar_init(smem_u32(&ctrl->xchg_bar[s]), 2 * kBM);
+      mbar_init(smem_u32(&ctrl->o_free[s]), 8);          // one arrival per softmax warp of the slot
     }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&ctrl->sched_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->sched_empty[i]), kSoftmaxWarps + 1);
+    }
+    ctrl->abort_flag = 0;
     mbar_fence_init();
-  }
-  __syncthreads();
-  CtaWork w;
-  w.b = ctrl->work_b;
-  w.pair = ctrl->work_pair;
-  if (w.b < 0) return;  // whole CTA: nothing allocated yet
-
-  const int q_head = ctrl->work_head;
-  const int kv_head = q_head / p.group;
-  if (p.layout == B200ATTN_RAGGED) {
-    const long long qa = load_index(p.q_indptr, p.indptr_is_i64, w.b);
-    const long long qe = load_index(p.q_indptr, p.indptr_is_i64, w.b + 1);
-    const long long ka = load_index(p.kv_indptr, p.indptr_is_i64, w.b);
-    const long long ke = load_index(p.kv_indptr, p.indptr_is_i64, w.b + 1);
-    w.len_q = static_cast<int>(qe > qa ? qe - qa : 0);
-    w.len_k = static_cast<int>(ke > ka ? ke - ka : 0);
-    w.q_row0 = qa;
-    w.kv_row0 = ka;
-    w.q_head_coord = q_head;
-    w.kv_head_coord = kv_head;
-  } else {
-    w.len_q = p.max_q;
-    w.q_row0 = (static_cast<long long>(w.b) * p.q_heads + q_head) * p.max_q;
-    w.q_head_coord = 0;
-    if (p.layout == B200ATTN_DENSE) {
-      w.len_k = p.max_kv;
-      w.kv_row0 = (static_cast<long long>(w.b) * p.kv_heads + kv_head) * p.max_kv;
-      w.kv_head_coord = 0;
-    } else {
-      long long n = load_index(p.kv_indptr, p.indptr_is_i64, w.b);
-      const long long cap = p.table_stride * static_cast<long long>(p.page_size);
-      n = n < 0 ? 0 : (n > cap ? cap : n);
-      w.len_k = static_cast<int>(n);
-      w.kv_row0 = 0;
-      w.kv_head_coord = kv_head;
-    }
-  }
-
-  // per-slot extents
-  int m0[kSlots], nkv[kSlots];
-  int nkv_max = 0;
-#pragma unroll
-  for (int s = 0; s < kSlots; ++s) {
-    m0[s] = (w.pair * kSlots + s) * kBM;
-    int n = 0;
-    if (m0[s] < w.len_q) {
-      int kv_hi = w.len_k;
-      if (p.is_causal) kv_hi = min(kv_hi, min(m0[s] + kBM, w.len_q));
-      n = (kv_hi + kBN - 1) / kBN;
-    }
-    nkv[s] = n;
-    nkv_max = max(nkv_max, n);
   }
   // ---------------- TMEM allocation (MMA warp owns it) ----------------
   if (warp == kMmaWarp) {
@@ -262,107 +273,133 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = ctrl->tmem_base;
-  const uint32_t tmem_S[kSlots] = {tmem, tmem + kBN};
-  const uint32_t tmem_O[kSlots] = {tmem + 2 * kBN, tmem + 2 * kBN + D};
   volatile int* abort_flag = &ctrl->abort_flag;
 
   if (warp == kProducerWarp) {
-    // =========================== TMA producer ===========================
+    // =========================== scheduler + TMA producer ===========================
     if (lane == 0) { prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); }
     bool ok = true;
-    if (lane == 0) {
-      uint32_t bytes = 0;
-      for (int s = 0; s < kSlots; ++s) if (nkv[s] > 0) bytes += Plan::kTileBytes;
-      if (bytes > 0) {
-        mbar_arrive_expect_tx(smem_u32(&ctrl->q_full), bytes);
-        for (int s = 0; s < kSlots; ++s) {
-          if (nkv[s] == 0) continue;
-          for (int c = 0; c < Plan::kChunks; ++c)
-            tma_load_3d(smem_base + Plan::kQOff + s * Plan::kTileBytes + c * Plan::kChunkBytes, &tm_q,
-                        smem_u32(&ctrl->q_full), c * 64, w.q_head_coord, static_cast<int>(w.q_row0 + m0[s]));
-        }
-      }
-    }
-    int issued = 0;
-    for (int e = 0; e < 2 * nkv_max && ok; ++e) {
-      const int j = e >> 1;
-      const bool is_v = e & 1;
-      const int buf = e % kRing;
-      const int use = e / kRing;
-      if (use > 0) {
-        ok = warp_wait(smem_u32(&ctrl->kv_empty[buf]), (use - 1) & 1);
+    int ring_e = 0;       // K/V ring entries issued so far (K_j, V_j alternate), across items
+    int ring_lo = 0;      // first entry of the current item
+    for (int k = 0; ok; ++k) {
+      if (k >= 2) {
+        ok = warp_wait(smem_u32(&ctrl->sched_empty[k & 1]), ((k >> 1) - 1) & 1);
         if (!ok || *abort_flag) { ok = false; break; }
       }
-      const uint32_t dst = smem_base + Plan::kRingOff + buf * Plan::kTileBytes;
-      const uint32_t bar = smem_u32(&ctrl->kv_full[buf]);
-      const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
-      if (p.layout != B200ATTN_PAGED) {
-        if (lane == 0) {
-          mbar_arrive_expect_tx(bar, Plan::kTileBytes);
-          for (int c = 0; c < Plan::kChunks; ++c)
-            tma_load_3d(dst + c * Plan::kChunkBytes, tm, bar, c * 64, w.kv_head_coord,
-                        static_cast<int>(w.kv_row0 + static_cast<long long>(j) * kBN));
-        }
-      } else {
-        // one box of `box_rows` tokens per lane per round; only pages that exist are fetched
-        const int* table = (is_v ? p.v_table : p.k_table) + static_cast<long long>(w.b) * p.table_stride;
-        const int boxes = kBN / p.box_rows;
-        int my_rows[4];
-        int nmine = 0;
-        int count = 0;
-        for (int i = lane; i < boxes; i += 32) {
-          const int t = j * kBN + i * p.box_rows;
-          int row = -1;
-          if (t < w.len_k) {
-            const int lp = t / p.page_size;
-            const int page = __ldg(table + lp);
-            // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
-            const bool bad = page < 0 || page >= p.num_pages;
-            if (bad) p.header[0] = DEV_ERR_PAGE_RANGE;
-            if (p.num_pages > 0) row = (bad ? 0 : page) * p.page_size + (t - lp * p.page_size);
+      int item = -1;
+      if (lane == 0) {
+        item = atomicAdd(p.work_counter, 1);
+        if (item >= p.total_items) item = -1;
+        ctrl->sched_item[k & 1] = item;
+        mbar_arrive(smem_u32(&ctrl->sched_full[k & 1]));
+      }
+      item = __shfl_sync(0xffffffffu, item, 0);
+      if (item < 0) break;
+      const ItemWork w = decode_item(p, item, lane);
+      // Q may be overwritten once every S MMA of the previous item has completed
+      if (k >= 1) {
+        ok = warp_wait(smem_u32(&ctrl->q_empty), (k - 1) & 1);
+        if (!ok || *abort_flag) { ok = false; break; }
+      }
+      if (lane == 0) {
+        uint32_t bytes = 0;
+        for (int s = 0; s < kSlots; ++s) if (w.nkv[s] > 0) bytes += Plan::kTileBytes;
+        if (bytes > 0) {
+          mbar_arrive_expect_tx(smem_u32(&ctrl->q_full), bytes);
+          for (int s = 0; s < kSlots; ++s) {
+            if (w.nkv[s] == 0) continue;
+            for (int c = 0; c < Plan::kChunks; ++c)
+              tma_load_3d(smem_base + Plan::kQOff + s * Plan::kTileBytes + c * Plan::kChunkBytes, &tm_q,
+                          smem_u32(&ctrl->q_full), c * 64, w.q_head_coord, static_cast<int>(w.q_row0 + w.m0[s]));
           }
-          my_rows[nmine++] = row;
-          if (row >= 0) ++count;
-        }
-        for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
-        if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * p.box_rows * 128 * Plan::kChunks);
-        __syncwarp();
-        int k = 0;
-        for (int i = lane; i < boxes; i += 32, ++k) {
-          const int row = my_rows[k];
-          if (row < 0) continue;
-          for (int c = 0; c < Plan::kChunks; ++c)
-            tma_load_3d(dst + c * Plan::kChunkBytes + i * p.box_rows * 128, tm, bar, c * 64, w.kv_head_coord, row);
+        } else {
+          mbar_arrive(smem_u32(&ctrl->q_full));   // keeps one q_full phase per item
         }
       }
-      issued = e + 1;
-      TRACE_AT(3072 + e);
+      ring_lo = ring_e;
+      for (int e = 0; e < 2 * w.nkv_max && ok; ++e, ++ring_e) {
+        const int j = e >> 1;
+        const bool is_v = e & 1;
+        const int buf = ring_e % kRing;
+        const int use = ring_e / kRing;
+        if (use > 0) {
+          ok = warp_wait(smem_u32(&ctrl->kv_empty[buf]), (use - 1) & 1);
+          if (!ok || *abort_flag) { ok = false; break; }
+        }
+        const uint32_t dst = smem_base + Plan::kRingOff + buf * Plan::kTileBytes;
+        const uint32_t bar = smem_u32(&ctrl->kv_full[buf]);
+        const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+        if (p.layout != B200ATTN_PAGED) {
+          if (lane == 0) {
+            mbar_arrive_expect_tx(bar, Plan::kTileBytes);
+            for (int c = 0; c < Plan::kChunks; ++c)
+              tma_load_3d(dst + c * Plan::kChunkBytes, tm, bar, c * 64, w.kv_head_coord,
+                          static_cast<int>(w.kv_row0 + static_cast<long long>(j) * kBN));
+          }
+        } else {
+          // one box of `box_rows` tokens per lane per round; only pages that exist are fetched
+          const int* table = (is_v ? p.v_table : p.k_table) + static_cast<long long>(w.b) * p.table_stride;
+          const int boxes = kBN / p.box_rows;
+          int my_rows[4];
+          int nmine = 0;
+          int count = 0;
+          for (int i = lane; i < boxes; i += 32) {
+            const int t = j * kBN + i * p.box_rows;
+            int row = -1;
+            if (t < w.len_k) {
+              const int lp = t / p.page_size;
+              const int page = __ldg(table + lp);
+              // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
+              const bool bad = page < 0 || page >= p.num_pages;
+              if (bad) p.header[0] = DEV_ERR_PAGE_RANGE;
+              if (p.num_pages > 0) row = (bad ? 0 : page) * p.page_size + (t - lp * p.page_size);
+            }
+            my_rows[nmine++] = row;
+            if (row >= 0) ++count;
+          }
+          for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
+          if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * p.box_rows * 128 * Plan::kChunks);
+          __syncwarp();
+          int kk = 0;
+          for (int i = lane; i < boxes; i += 32, ++kk) {
+            const int row = my_rows[kk];
+            if (row < 0) continue;
+            for (int c = 0; c < Plan::kChunks; ++c)
+              tma_load_3d(dst + c * Plan::kChunkBytes + i * p.box_rows * 128, tm, bar, c * 64, w.kv_head_coord, row);
+          }
+        }
+        TRACE_AT(3072 + (ring_e & 255));
+      }
     }
     if (!ok) {
       if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
       // drain: wait (bounded) for the copies still in flight before the CTA may exit
-      for (int e = max(0, issued - kRing); e < issued; ++e) mbar_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
+      for (int e = max(ring_lo, ring_e - kRing); e < ring_e; ++e) mbar_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
     }
   } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===========================
     constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
     constexpr uint32_t idesc_s = make_idesc_f16(kBM, kBN, kFmt, 0);
     constexpr uint32_t idesc_o = make_idesc_f16(kBM, D, kFmt, 1);
+    const uint32_t tmem_S[kSlots] = {tmem, tmem + kBN};
+    const uint32_t tmem_O[kSlots] = {tmem + 2 * kBN, tmem + 2 * kBN + D};
     bool ok = true;
-    auto ring_full_wait = [&](int e) -> bool {
-      return warp_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
-    };
     // Descriptor words are prepared once: the high words never change, the low words are a base
     // (start address >> 4) plus small constants, so issuing one MMA costs the single thread a few adds.
     const uint64_t kdesc = make_smem_desc_sw128(smem_base, 16);                    // K-major operands (Q, K)
     const uint64_t vdesc = make_smem_desc_sw128(smem_base, Plan::kChunkBytes);     // MN-major operand (V)
     const uint32_t k_hi = static_cast<uint32_t>(kdesc >> 32), v_hi = static_cast<uint32_t>(vdesc >> 32);
     const uint32_t k_lo = static_cast<uint32_t>(kdesc), v_lo = static_cast<uint32_t>(vdesc);
-    auto issue_s = [&](int s, int j) {
-      // S_s = Q_s K_j^T : K-major A and B, D/16 k-steps
+    int ring_base = 0;            // ring entry of K_0 of the current item
+    int tiles_done[kSlots] = {0, 0};  // score tiles issued per slot so far (barrier phases run across items)
+    auto ring_full_wait = [&](int e) -> bool {
+      return warp_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
+    };
+    auto issue_s = [&](int s, int e_k) {
+      // S_s = Q_s K^T : K-major A and B, D/16 k-steps
       if (lane == 0) {
         const uint32_t qa_lo = k_lo + ((Plan::kQOff + s * Plan::kTileBytes) >> 4);
-        const uint32_t kb_lo = k_lo + ((Plan::kRingOff + ((2 * j) % kRing) * Plan::kTileBytes) >> 4);
+        const uint32_t kb_lo = k_lo + ((Plan::kRingOff + (e_k % kRing) * Plan::kTileBytes) >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk >> 2) * Plan::kChunkBytes + (kk & 3) * 32) >> 4;
@@ -372,72 +409,98 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       __syncwarp();
     };
-    auto issue_pv = [&](int s, int j) {
-      // O_s (+)= P_s V_j : A = packed 16-bit P in TMEM, B = V, MN-major.  P of columns 0-63 sits in TMEM columns
+    auto issue_pv = [&](int s, int e_v, bool first) {
+      // O_s (+)= P_s V : A = packed 16-bit P in TMEM, B = V, MN-major.  P of columns 0-63 sits in TMEM columns
       // 0-31 of the S tile and P of columns 64-127 in TMEM columns 64-95 (each warpgroup writes over its own half).
       if (lane == 0) {
-        const uint32_t vb_lo = v_lo + ((Plan::kRingOff + ((2 * j + 1) % kRing) * Plan::kTileBytes) >> 4);
+        const uint32_t vb_lo = v_lo + ((Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes) >> 4);
 #pragma unroll
         for (int kk = 0; kk < kBN / 16; ++kk) {
           mma_ts_lohi(tmem_O[s], tmem_S[s] + (kk >> 2) * kHalf + (kk & 3) * 8, vb_lo + ((kk * 16 * 128) >> 4), v_hi, idesc_o,
-                      (j > 0 || kk > 0) ? 1u : 0u);
+                      (!first || kk > 0) ? 1u : 0u);
         }
         mma_commit(smem_u32(&ctrl->o_done[s]));
       }
       __syncwarp();
     };
 
-    if (nkv_max > 0) {
-      ok = warp_wait(smem_u32(&ctrl->q_full), 0) && ring_full_wait(0);
-      if (ok) {
-        tc_fence_after();
-        for (int s = 0; s < kSlots; ++s) if (nkv[s] > 0) issue_s(s, 0);
-        if (lane == 0) mma_commit(smem_u32(&ctrl->kv_empty[0]));
-      }
-    }
-    for (int j = 0; j < nkv_max && ok; ++j) {
-      bool v_ready = false;
-      for (int s = 0; s < kSlots && ok; ++s) {
-        if (j >= nkv[s]) continue;
-        TRACE_AT(2048 + (j * 2 + s) * 4 + 0);
-        ok = warp_wait(smem_u32(&ctrl->p_ready[s]), j & 1);
-        if (!ok) break;
-        TRACE_AT(2048 + (j * 2 + s) * 4 + 1);
-        if (!v_ready) {
-          ok = ring_full_wait(2 * j + 1);
-          if (!ok) break;
-          v_ready = true;
-          const int valid = w.len_k - j * kBN;
-          if (valid < kBN) {
-            // keys past the sequence end carry P == 0 but their V rows may hold anything (stale
-            // shared memory, the next sequence, poisoned page tails): zero them so 0 * x stays 0
-            unsigned char* vbuf = smem + Plan::kRingOff + ((2 * j + 1) % kRing) * Plan::kTileBytes;
-            const int first = valid > 0 ? valid : 0;
-            const int n16 = (kBN - first) * 8;  // 16-byte pieces per column block
-            for (int c = 0; c < Plan::kChunks; ++c) {
-              uint4* dst = reinterpret_cast<uint4*>(vbuf + c * Plan::kChunkBytes + first * 128);
-              for (int i = lane; i < n16; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-          }
-        }
-        tc_fence_after();
-        issue_pv(s, j);
-        TRACE_AT(2048 + (j * 2 + s) * 4 + 2);
-        if (j + 1 < nkv[s]) {
-          ok = ring_full_wait(2 * (j + 1));
-          if (!ok) break;
-          tc_fence_after();
-          issue_s(s, j + 1);
-        }
-        TRACE_AT(2048 + (j * 2 + s) * 4 + 3);
-      }
+    for (int k = 0; ok; ++k) {
+      ok = warp_wait(smem_u32(&ctrl->sched_full[k & 1]), (k >> 1) & 1);
+      if (!ok || *abort_flag) { ok = false; break; }
+      const int item = ctrl->sched_item[k & 1];
+      if (item < 0) break;
+      const ItemWork w = decode_item(p, item, lane);
+      ok = warp_wait(smem_u32(&ctrl->q_full), k & 1);
       if (!ok) break;
-      if (lane == 0) {
-        mma_commit(smem_u32(&ctrl->kv_empty[(2 * j + 1) % kRing]));
-        if (j + 1 < nkv_max) mma_commit(smem_u32(&ctrl->kv_empty[(2 * j + 2) % kRing]));
+      if (w.nkv_max > 0) {
+        ok = ring_full_wait(ring_base);
+        if (!ok) break;
+        tc_fence_after();
+        for (int s = 0; s < kSlots; ++s) if (w.nkv[s] > 0) issue_s(s, ring_base);
+        if (lane == 0) {
+          mma_commit(smem_u32(&ctrl->kv_empty[ring_base % kRing]));
+          if (w.nkv_max == 1) mma_commit(smem_u32(&ctrl->q_empty));
+        }
+        __syncwarp();
+      } else if (lane == 0) {
+        mma_commit(smem_u32(&ctrl->q_empty));
       }
+      for (int j = 0; j < w.nkv_max && ok; ++j) {
+        bool v_ready = false;
+        const int e_v = ring_base + 2 * j + 1;
+        for (int s = 0; s < kSlots && ok; ++s) {
+          if (j >= w.nkv[s]) continue;
+          TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 0);
+          ok = warp_wait(smem_u32(&ctrl->p_ready[s]), tiles_done[s] & 1);
+          if (!ok) break;
+          TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 1);
+          if (!v_ready) {
+            ok = ring_full_wait(e_v);
+            if (!ok) break;
+            v_ready = true;
+            const int valid = w.len_k - j * kBN;
+            if (valid < kBN) {
+              // keys past the sequence end carry P == 0 but their V rows may hold anything (stale
+              // shared memory, the next sequence, poisoned page tails): zero them so 0 * x stays 0
+              unsigned char* vbuf = smem + Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes;
+              const int first = valid > 0 ? valid : 0;
+              const int n16 = (kBN - first) * 8;  // 16-byte pieces per column block
+              for (int c = 0; c < Plan::kChunks; ++c) {
+                uint4* dst = reinterpret_cast<uint4*>(vbuf + c * Plan::kChunkBytes + first * 128);
+                for (int i = lane; i < n16; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+            }
+          }
+          if (j == 0 && k > 0) {
+            // the first PV of an item overwrites O: the epilogue of the previous item must have read it out
+            ok = warp_wait(smem_u32(&ctrl->o_free[s]), (k - 1) & 1);
+            if (!ok) break;
+          }
+          tc_fence_after();
+          issue_pv(s, e_v, j == 0);
+          TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 2);
+          if (j + 1 < w.nkv[s]) {
+            ok = ring_full_wait(e_v + 1);
+            if (!ok) break;
+            tc_fence_after();
+            issue_s(s, e_v + 1);
+          }
+          TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 3);
+          ++tiles_done[s];
+        }
+        if (!ok) break;
+        if (lane == 0) {
+          mma_commit(smem_u32(&ctrl->kv_empty[e_v % kRing]));
+          if (j + 1 < w.nkv_max) mma_commit(smem_u32(&ctrl->kv_empty[(e_v + 1) % kRing]));
+          // the last score MMAs of the item have been issued: Q may be replaced once they complete
+          if (j + 2 == w.nkv_max) mma_commit(smem_u32(&ctrl->q_empty));
+        }
+        __syncwarp();
+      }
+      ring_base += 2 * w.nkv_max;
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));
       __syncwarp();
     }
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
@@ -451,218 +514,208 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int half = g >> 1;
     const int row = (warp & 3) * 32 + lane;             // 0..127 inside the slot
     const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tSh = tmem_S[s] + lane_off + half * kHalf;
+    const uint32_t tSh = tmem + s * kBN + lane_off + half * kHalf;
     constexpr int kOCols = D / 2;                       // O columns rescaled / written out by this thread
-    const uint32_t tOh = tmem_O[s] + lane_off + half * kOCols;
-    const int row_abs = m0[s] + row;                    // query index inside the sequence
-    const int n = nkv[s];
+    const uint32_t tOh = tmem + 2 * kBN + s * D + lane_off + half * kOCols;
     const float sl2 = p.scale_log2;
     const bool tracer = (warp & 3) == 0 && half == 0;
-    float m_used = -INFINITY;   // exponent reference currently baked into O and l
-    float l = 0.f;              // partial row sum over this thread's columns
+    int tile_cnt = 0;     // score tiles of this slot consumed so far (barrier phases run across items)
+    int xchg_cnt = 0;     // exchanges done so far
     bool ok = true;
-    for (int j = 0; j < n; ++j) {
-      if (tracer) TRACE_AT(s * 1024 + j * 8 + 0);
-      ok = warp_wait(smem_u32(&ctrl->s_full[s]), j & 1);
+    for (int k = 0; ok; ++k) {
+      ok = warp_wait(smem_u32(&ctrl->sched_full[k & 1]), (k >> 1) & 1);
       if (!ok || *abort_flag) { ok = false; break; }
-      tc_fence_after();
-      if (tracer) TRACE_AT(s * 1024 + j * 8 + 1);
-      // masking is needed only on the tile that holds the sequence end or the causal diagonal
-      int limit = w.len_k - 1 - j * kBN - half * kHalf;
-      if (p.is_causal) limit = min(limit, row_abs - j * kBN - half * kHalf);
-      const bool masked = limit < kHalf - 1;
-      float mx;
-      {
-        // pass 1: the max of this thread's 64 scores (they are read again in pass 2; holding them across the
-        // exchange below would cost 64 registers per thread)
-        uint32_t ca[32], cb[32];
-        tmem_ld32(tSh, ca);
-        tmem_ld32(tSh + 32, cb);
-        tmem_wait_ld();
-        if (masked) {
+      const int item = ctrl->sched_item[k & 1];
+      if (item < 0) break;
+      const ItemWork w = decode_item(p, item, lane);
+      const int n = s == 0 ? w.nkv[0] : w.nkv[1];
+      const int m0s = s == 0 ? w.m0[0] : w.m0[1];
+      const int row_abs = m0s + row;                    // query index inside the sequence
+      float m_used = -INFINITY;   // exponent reference currently baked into O and l
+      float l = 0.f;              // partial row sum over this thread's columns
+      for (int j = 0; j < n; ++j, ++tile_cnt) {
+        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 0);
+        ok = warp_wait(smem_u32(&ctrl->s_full[s]), tile_cnt & 1);
+        if (!ok || *abort_flag) { ok = false; break; }
+        tc_fence_after();
+        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 1);
+        // masking is needed only on the tile that holds the sequence end or the causal diagonal
+        int limit = w.len_k - 1 - j * kBN - half * kHalf;
+        if (p.is_causal) limit = min(limit, row_abs - j * kBN - half * kHalf);
+        const bool masked = limit < kHalf - 1;
+        float mx;
+        {
+          // pass 1: the max of this thread's 64 scores (they are read again in pass 2; holding them across the
+          // exchange below would cost 64 registers per thread)
+          uint32_t ca[32], cb[32];
+          tmem_ld32(tSh, ca);
+          tmem_ld32(tSh + 32, cb);
+          tmem_wait_ld();
+          if (masked) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (i > limit) ca[i] = 0xff800000u;        // -inf
-            if (32 + i > limit) cb[i] = 0xff800000u;
+            for (int i = 0; i < 32; ++i) {
+              if (i > limit) ca[i] = 0xff800000u;        // -inf
+              if (32 + i > limit) cb[i] = 0xff800000u;
+            }
+          }
+          float ma = max3(__uint_as_float(ca[0]), __uint_as_float(ca[1]), __uint_as_float(ca[2]));
+          float mb = max3(__uint_as_float(cb[0]), __uint_as_float(cb[1]), __uint_as_float(cb[2]));
+#pragma unroll
+          for (int i = 3; i + 1 < 32; i += 2) {
+            ma = max3(ma, __uint_as_float(ca[i]), __uint_as_float(ca[i + 1]));
+            mb = max3(mb, __uint_as_float(cb[i]), __uint_as_float(cb[i + 1]));
+          }
+          mx = max3(ma, mb, fmaxf(__uint_as_float(ca[31]), __uint_as_float(cb[31])));
+        }
+        // exchange the half-row maxima
+        ctrl->xchg[xchg_cnt & 1][s][half][row] = mx;
+        mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
+        ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), xchg_cnt & 1);
+        if (!ok) break;
+        mx = fmaxf(mx, ctrl->xchg[xchg_cnt & 1][s][half ^ 1][row]);
+        ++xchg_cnt;
+        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 2);
+        const float m_new = fmaxf(m_used, mx * sl2);
+        const bool need = (m_new - m_used) > kRescaleThreshold;   // false for NaN / (-inf)-(-inf)
+        float alpha = 1.f;
+        if (need) { alpha = fast_exp2(m_used - m_new); m_used = m_new; l *= alpha; }
+        if (j > 0 && __any_sync(0xffffffffu, need)) {
+          // PV(j-1) has landed in O once S(j) is visible (the MMAs complete in issue order); waiting on its
+          // barrier phase is then immediate, and skipping the wait on other tiles is harmless because the
+          // barrier can never run two phases ahead of this warpgroup
+          ok = warp_wait(smem_u32(&ctrl->o_done[s]), (tile_cnt - 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < kOCols / 32; ++c) {
+            uint32_t ov[32];
+            tmem_ld32(tOh + c * 32, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st32(tOh + c * 32, ov);
           }
         }
-        float ma = max3(__uint_as_float(ca[0]), __uint_as_float(ca[1]), __uint_as_float(ca[2]));
-        float mb = max3(__uint_as_float(cb[0]), __uint_as_float(cb[1]), __uint_as_float(cb[2]));
+        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 4);
+        const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
+        const float neg_m = -m_eff;
+        uint64_t rs2 = pack_f2(0.f, 0.f);
+        const uint64_t sl2_2 = pack_f2(sl2, sl2), negm_2 = pack_f2(neg_m, neg_m);
+        auto chunk_exp = [&](int c) {
+          uint32_t v[32];
+          tmem_ld32(tSh + c * 32, v);
+          tmem_wait_ld();
+          if (masked) {
 #pragma unroll
-        for (int i = 3; i + 1 < 32; i += 2) {
-          ma = max3(ma, __uint_as_float(ca[i]), __uint_as_float(ca[i + 1]));
-          mb = max3(mb, __uint_as_float(cb[i]), __uint_as_float(cb[i + 1]));
-        }
-        mx = max3(ma, mb, fmaxf(__uint_as_float(ca[31]), __uint_as_float(cb[31])));
+            for (int i = 0; i < 32; ++i) if (c * 32 + i > limit) v[i] = 0xff800000u;   // -inf
+          }
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const uint64_t t2 = fma_f2(pack_f2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), sl2_2, negm_2);
+            float p0, p1;
+            if ((i & 3) < kExpEmuOf4) {
+              // 2^t = 2^n * 2^r with n = round(t), r in [-0.5, 0.5]; n is read off the magic-number sum
+              float a, b;
+              unpack_f2(t2, a, b);
+              const uint64_t tc = pack_f2(fmaxf(a, -126.f), fmaxf(b, -126.f));
+              const uint64_t tm = add_f2(tc, pack_f2(12582912.f, 12582912.f));
+              const uint64_t nf = add_f2(tm, pack_f2(-12582912.f, -12582912.f));
+              const uint64_t r = fma_f2(nf, pack_f2(-1.f, -1.f), tc);
+              uint64_t q = fma_f2(r, pack_f2(0.055171482f, 0.055171482f), pack_f2(0.2426109f, 0.2426109f));
+              q = fma_f2(q, r, pack_f2(0.69326097f, 0.69326097f));
+              q = fma_f2(q, r, pack_f2(0.99992812f, 0.99992812f));
+              float q0, q1, m0f, m1f;
+              unpack_f2(q, q0, q1);
+              unpack_f2(tm, m0f, m1f);
+              p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(m0f) << 23));
+              p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(m1f) << 23));
+            } else {
+              float a, b;
+              unpack_f2(t2, a, b);
+              p0 = fast_exp2(a);
+              p1 = fast_exp2(b);
+            }
+            rs2 = add_f2(rs2, pack_f2(p0, p1));
+            pk[i] = ElemTraits<T>::pack2(p0, p1);
+          }
+          tmem_st16(tSh + c * 16, pk);
+        };
+        chunk_exp(0);
+        chunk_exp(1);
+        float rs0, rs1;
+        unpack_f2(rs2, rs0, rs1);
+        l += rs0 + rs1;
+        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 5);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctrl->p_ready[s]));
+        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 6);
       }
-      // exchange the half-row maxima
-      ctrl->xchg[j & 1][s][half][row] = mx;
-      mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
-      ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), j & 1);
       if (!ok) break;
-      mx = fmaxf(mx, ctrl->xchg[j & 1][s][half ^ 1][row]);
-      if (tracer) TRACE_AT(s * 1024 + j * 8 + 2);
-      const float m_new = fmaxf(m_used, mx * sl2);
-      if (tracer) TRACE_AT(s * 1024 + j * 8 + 3);
-      const bool need = (m_new - m_used) > kRescaleThreshold;   // false for NaN / (-inf)-(-inf)
-      float alpha = 1.f;
-      if (need) { alpha = fast_exp2(m_used - m_new); m_used = m_new; l *= alpha; }
-      if (j > 0 && __any_sync(0xffffffffu, need)) {
-        // PV(j-1) has landed in O once S(j) is visible (the MMAs complete in issue order); waiting on its
-        // barrier phase (j-1) is then immediate, and skipping the wait on other iterations is harmless
-        // because the barrier can never run two phases ahead of this warpgroup
-        ok = warp_wait(smem_u32(&ctrl->o_done[s]), (j - 1) & 1);
+      // ---------------- epilogue of the item ----------------
+      if (n > 0) {
+        ok = warp_wait(smem_u32(&ctrl->o_done[s]), (tile_cnt - 1) & 1);
         if (!ok) break;
-        tc_fence_after();
+      }
+      // total row sum = this thread's partial + its partner's
+      ctrl->xchg[xchg_cnt & 1][s][half][row] = l;
+      mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
+      ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), xchg_cnt & 1);
+      if (!ok) break;
+      l += ctrl->xchg[xchg_cnt & 1][s][half ^ 1][row];
+      ++xchg_cnt;
+      tc_fence_after();
+      const bool slot_live = w.valid && m0s < w.len_q;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      const int rows_valid = slot_live ? min(kBM, w.len_q - m0s) : 0;
+      long long off;
+      if (p.layout == B200ATTN_RAGGED) off = ((w.q_row0 + m0s + row) * p.q_heads + w.q_head) * D;
+      else off = (w.q_row0 + m0s + row) * D;
+      off += half * kOCols;
+      // every thread writes its own half row: 32 contiguous output columns per TMEM chunk
 #pragma unroll
-        for (int c = 0; c < kOCols / 32; ++c) {
-          uint32_t ov[32];
+      for (int c = 0; c < kOCols / 32; ++c) {
+        uint32_t ov[32];
+        if (n > 0) {
           tmem_ld32(tOh + c * 32, ov);
           tmem_wait_ld();
+        } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          tmem_st32(tOh + c * 32, ov);
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
         }
-      }
-      if (tracer) TRACE_AT(s * 1024 + j * 8 + 4);
-      const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-      const float neg_m = -m_eff;
-      uint64_t rs2 = pack_f2(0.f, 0.f);
-      const uint64_t sl2_2 = pack_f2(sl2, sl2), negm_2 = pack_f2(neg_m, neg_m);
-      auto chunk_exp = [&](int c) {
-        uint32_t v[32];
-        tmem_ld32(tSh + c * 32, v);
-        tmem_wait_ld();
-        if (masked) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) if (c * 32 + i > limit) v[i] = 0xff800000u;   // -inf
+        if (c == kOCols / 32 - 1) {
+          // O has been read out: the MMA warp may start the next item's PV into it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctrl->o_free[s]));
         }
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint64_t t2 = fma_f2(pack_f2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), sl2_2, negm_2);
-          float p0, p1;
-          if ((i & 3) < kExpEmuOf4) {
-            // 2^t = 2^n * 2^r with n = round(t), r in [-0.5, 0.5]; n is read off the magic-number sum
-            float a, b;
-            unpack_f2(t2, a, b);
-            const uint64_t tc = pack_f2(fmaxf(a, -126.f), fmaxf(b, -126.f));
-            const uint64_t tm = add_f2(tc, pack_f2(12582912.f, 12582912.f));
-            const uint64_t nf = add_f2(tm, pack_f2(-12582912.f, -12582912.f));
-            const uint64_t r = fma_f2(nf, pack_f2(-1.f, -1.f), tc);
-            uint64_t q = fma_f2(r, pack_f2(0.055171482f, 0.055171482f), pack_f2(0.2426109f, 0.2426109f));
-            q = fma_f2(q, r, pack_f2(0.69326097f, 0.69326097f));
-            q = fma_f2(q, r, pack_f2(0.99992812f, 0.99992812f));
-            float q0, q1, m0f, m1f;
-            unpack_f2(q, q0, q1);
-            unpack_f2(tm, m0f, m1f);
-            p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(m0f) << 23));
-            p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(m1f) << 23));
-          } else {
-            float a, b;
-            unpack_f2(t2, a, b);
-            p0 = fast_exp2(a);
-            p1 = fast_exp2(b);
-          }
-          rs2 = add_f2(rs2, pack_f2(p0, p1));
-          pk[i] = ElemTraits<T>::pack2(p0, p1);
-        }
-        tmem_st16(tSh + c * 16, pk);
-      };
-      chunk_exp(0);
-      chunk_exp(1);
-      float rs0, rs1;
-      unpack_f2(rs2, rs0, rs1);
-      l += rs0 + rs1;
-      if (tracer) TRACE_AT(s * 1024 + j * 8 + 5);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&ctrl->p_ready[s]));
-      if (tracer) TRACE_AT(s * 1024 + j * 8 + 6);
-    }
-    // ---------------- epilogue ----------------
-    if (ok && n > 0) ok = warp_wait(smem_u32(&ctrl->o_done[s]), (n - 1) & 1);
-    if (ok) {
-      // total row sum = this thread's partial + its partner's (one more exchange, parity n & 1)
-      ctrl->xchg[n & 1][s][half][row] = l;
-      mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
-      ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), n & 1);
-      if (ok) l += ctrl->xchg[n & 1][s][half ^ 1][row];
-    }
-    if (!ok) {
-      if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
-    } else if (m0[s] < w.len_q) {
-      tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int rows_valid = min(kBM, w.len_q - m0[s]);
-      if constexpr (std::is_same<OutT, float>::value) {
-        // fp32 output: every thread stores its own half row, 128 contiguous bytes per TMEM chunk
-        float* out = static_cast<float*>(p.out);
-        long long off;
-        if (p.layout == B200ATTN_RAGGED) off = ((w.q_row0 + m0[s] + row) * p.q_heads + q_head) * D;
-        else off = (w.q_row0 + m0[s] + row) * D;
-        off += half * kOCols;
-#pragma unroll
-        for (int c = 0; c < kOCols / 32; ++c) {
-          uint32_t ov[32];
-          if (n > 0) {
-            tmem_ld32(tOh + c * 32, ov);
-            tmem_wait_ld();
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = 0u;
-          }
-          if (row < rows_valid) {
+        if (row < rows_valid) {
+          if constexpr (std::is_same<OutT, float>::value) {
+            float* out = static_cast<float*>(p.out) + off + c * 32;
 #pragma unroll
             for (int q4 = 0; q4 < 8; ++q4)
-              *reinterpret_cast<float4*>(out + off + c * 32 + q4 * 4) =
+              *reinterpret_cast<float4*>(out + q4 * 4) =
                   make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
                               __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
-          }
-        }
-      } else {
-        // 16-bit output: stage the half rows in the dead Q buffer ([128][D] 16-bit, 16-byte pieces XOR-swizzled),
-        // then each warp writes its own 32 half rows with 16-byte stores
-        unsigned char* stage = smem + Plan::kQOff + s * Plan::kTileBytes;
-        constexpr int kPieces = kOCols * 2 / 16;   // 16-byte pieces per half row
-#pragma unroll
-        for (int c = 0; c < kOCols / 32; ++c) {
-          uint32_t ov[32];
-          if (n > 0) {
-            tmem_ld32(tOh + c * 32, ov);
-            tmem_wait_ld();
           } else {
+            T* out = static_cast<T*>(p.out) + off + c * 32;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = 0u;
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 u;
+              u.x = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
+              u.y = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
+              u.z = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
+              u.w = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(out + q4 * 8) = u;
+            }
           }
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 u;
-            u.x = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
-            u.y = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
-            u.z = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
-            u.w = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
-            const int piece = half * kPieces + c * 4 + q4;
-            *reinterpret_cast<uint4*>(stage + row * (D * 2) + ((piece ^ (row & 7)) << 4)) = u;
-          }
-        }
-        __syncwarp();
-        T* out = static_cast<T*>(p.out);
-        constexpr int kRowsPerPass = 32 / kPieces;
-        const int pl = lane % kPieces;
-        const int wrow0 = (warp & 3) * 32;
-        for (int rr = lane / kPieces; rr < 32; rr += kRowsPerPass) {
-          const int r = wrow0 + rr;
-          if (r >= rows_valid) break;
-          const int piece = half * kPieces + pl;
-          const uint4 u = *reinterpret_cast<const uint4*>(stage + r * (D * 2) + ((piece ^ (r & 7)) << 4));
-          long long off;
-          if (p.layout == B200ATTN_RAGGED) off = ((w.q_row0 + m0[s] + r) * p.q_heads + q_head) * D;
-          else off = (w.q_row0 + m0[s] + r) * D;
-          *reinterpret_cast<uint4*>(out + off + piece * 8) = u;
         }
       }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));
     }
+    if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
   }
 
   // ---------------- teardown ----------------
@@ -705,7 +758,7 @@ size_t prefill_workspace_bytes(const b200attn_prefill_args_t& a) {
   return kHeaderBytes;
 }
 
-int launch_prefill(const b200attn_prefill_args_t& a_in, cudaStream_t stream) {
+int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream_t stream) {
   const size_t need = prefill_workspace_bytes(a_in);
   if (a_in.workspace == nullptr || a_in.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a_in.workspace) & 255)) {
     set_error("prefill: workspace needs %zu bytes, 256-byte aligned (got %zu)", need, a_in.workspace_bytes);
@@ -736,6 +789,7 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, cudaStream_t stream) {
   p.out = a.out; p.q_indptr = a.q_indptr; p.kv_indptr = a.kv_indptr;
   p.k_table = a.k_table; p.v_table = a.v_table;
   p.header = static_cast<int*>(a.workspace);
+  p.work_counter = p.header + 8;
   p.table_stride = a.table_stride;
   p.layout = a.layout; p.indptr_is_i64 = a.indptr_is_i64;
   p.batch = a.batch; p.q_heads = a.q_heads; p.kv_heads = a.kv_heads; p.group = a.q_heads / a.kv_heads;
@@ -749,12 +803,13 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, cudaStream_t stream) {
   CUtensorMap tq, tk, tv;
   int rc;
   dim3 grid;
+  long long total_items = 0;
   if (a.layout == B200ATTN_RAGGED) {
     if ((rc = make_token_map(&tq, a.dtype, a.q, a.total_q, a.q_heads, D, kBM))) return rc;
     if ((rc = make_token_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, kBN))) return rc;
     if ((rc = make_token_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, kBN))) return rc;
     const long long pairs = a.total_q / (2 * kBM) + a.batch;
-    grid = dim3(static_cast<unsigned>(pairs * a.q_heads), 1, 1);
+    total_items = pairs * a.q_heads;
   } else {
     const long long q_rows = static_cast<long long>(a.batch) * a.q_heads * a.max_q;
     if ((rc = make_token_map(&tq, a.dtype, a.q, q_rows, 1, D, kBM))) return rc;
@@ -771,9 +826,15 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, cudaStream_t stream) {
       if ((rc = make_token_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box))) return rc;
       if ((rc = make_token_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box))) return rc;
     }
-    grid = dim3(static_cast<unsigned>((a.max_q + 2 * kBM - 1) / (2 * kBM)) * a.q_heads * a.batch, 1, 1);
+    total_items = static_cast<long long>((a.max_q + 2 * kBM - 1) / (2 * kBM)) * a.q_heads * a.batch;
   }
-  if (grid.x == 0 || grid.y == 0 || grid.z == 0) return B200ATTN_OK;
+  if (total_items <= 0) return B200ATTN_OK;
+  if (total_items > 0x7fffffff) { set_error("prefill: too many work items"); return B200ATTN_E_UNSUPPORTED; }
+  p.total_items = static_cast<int>(total_items);
+  grid = dim3(static_cast<unsigned>(std::min<long long>(total_items, sm_count)), 1, 1);
+  // the work counter of the persistent kernel starts from zero on every launch
+  cudaError_t me = cudaMemsetAsync(p.work_counter, 0, sizeof(int), stream);
+  if (me != cudaSuccess) return cuda_fail(me, "cudaMemsetAsync(work counter)");
 
   cudaError_t e;
 #define B200ATTN_LAUNCH_PREFILL(TYPE, DIM, OUT)                                                          \

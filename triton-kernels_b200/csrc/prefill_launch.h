@@ -15,6 +15,8 @@ struct PrefillParams {
   const int* k_table;
   const int* v_table;
   int* header;          // workspace header, word 0 = device error code
+  int* work_counter;    // workspace header word 8: next work item of the persistent kernel
+  int total_items;
   long long table_stride;
   int layout;
   int indptr_is_i64;
@@ -32,6 +34,6 @@ struct PrefillParams {
 };
 
 size_t prefill_workspace_bytes(const b200attn_prefill_args_t& a);
-int launch_prefill(const b200attn_prefill_args_t& a, cudaStream_t stream);
+int launch_prefill(const b200attn_prefill_args_t& a, int sm_count, cudaStream_t stream);
 
 }  // namespace b200attn
