@@ -63,6 +63,20 @@ constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
 #define TRACE_AT(idx) do { } while (0)
 #endif
 
+// Everything one work item (sequence, q head, 256-row query block) needs; decoded once by the scheduler warp.
+struct ItemWork {
+  bool valid;
+  int q_head;
+  int len_q, len_k;
+  long long q_row0;    // first q row of the sequence on the token axis of the q tensor map
+  long long kv_row0;   // first kv row of the sequence (dense / ragged)
+  int q_head_coord, kv_head_coord;
+  int b;
+  int m0[kSlots];      // first query row of each slot inside the sequence
+  int nkv[kSlots];     // 128-key tiles each slot visits
+  int nkv_max;
+};
+
 // shared-memory control block placed after the tiles
 struct __align__(8) Control {
   uint64_t q_full;
@@ -77,6 +91,7 @@ struct __align__(8) Control {
   uint64_t sched_full[2];
   uint64_t sched_empty[2];
   int sched_item[2];
+  ItemWork sched_work[2];   // decoded by the scheduler, read by every other warp
   float xchg[2][kSlots][2][kBM];   // [tile parity][slot][column half][row]: row max / final row sum exchange
   uint32_t tmem_base;
   int abort_flag;
@@ -145,21 +160,6 @@ __global__ void __launch_bounds__(256) cast_f32_to_f16_kernel(const float4* __re
     dst[i] = u;
   }
 }
-
-// Everything one work item (sequence, q head, 256-row query block) needs, derived by each warp on its own
-// from the item index so that the roles never exchange it.
-struct ItemWork {
-  bool valid;
-  int q_head;
-  int len_q, len_k;
-  long long q_row0;    // first q row of the sequence on the token axis of the q tensor map
-  long long kv_row0;   // first kv row of the sequence (dense / ragged)
-  int q_head_coord, kv_head_coord;
-  int b;
-  int m0[kSlots];      // first query row of each slot inside the sequence
-  int nkv[kSlots];     // 128-key tiles each slot visits
-  int nkv_max;
-};
 
 __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item, int lane) {
   ItemWork w;
@@ -290,12 +290,31 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (lane == 0) {
         item = atomicAdd(p.work_counter, 1);
         if (item >= p.total_items) item = -1;
+      }
+      item = __shfl_sync(0xffffffffu, item, 0);
+      ItemWork w;
+      if (item >= 0) w = decode_item(p, item, lane);
+      if (lane == 0) {
+        if (item >= 0) ctrl->sched_work[k & 1] = w;
         ctrl->sched_item[k & 1] = item;
         mbar_arrive(smem_u32(&ctrl->sched_full[k & 1]));
       }
-      item = __shfl_sync(0xffffffffu, item, 0);
       if (item < 0) break;
-      const ItemWork w = decode_item(p, item, lane);
+      if (k >= 1 && lane == 0) {
+        // the previous item is still running: pull this item's Q tiles and first K/V tiles into L2 now, so the
+        // copies issued once the Q buffer is free only pay an L2 round trip
+        for (int s = 0; s < kSlots; ++s) {
+          if (w.nkv[s] == 0) continue;
+          for (int c = 0; c < Plan::kChunks; ++c)
+            tma_prefetch_3d(&tm_q, c * 64, w.q_head_coord, static_cast<int>(w.q_row0 + w.m0[s]));
+        }
+        if (p.layout != B200ATTN_PAGED && w.nkv_max > 0) {
+          for (int c = 0; c < Plan::kChunks; ++c) {
+            tma_prefetch_3d(&tm_k, c * 64, w.kv_head_coord, static_cast<int>(w.kv_row0));
+            tma_prefetch_3d(&tm_v, c * 64, w.kv_head_coord, static_cast<int>(w.kv_row0));
+          }
+        }
+      }
       // Q may be overwritten once every S MMA of the previous item has completed
       if (k >= 1) {
         ok = warp_wait(smem_u32(&ctrl->q_empty), (k - 1) & 1);
@@ -316,6 +335,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mbar_arrive(smem_u32(&ctrl->q_full));   // keeps one q_full phase per item
         }
       }
+      TRACE_AT(3840 + (k & 31) * 2 + 0);
       ring_lo = ring_e;
       for (int e = 0; e < 2 * w.nkv_max && ok; ++e, ++ring_e) {
         const int j = e >> 1;
@@ -425,18 +445,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     };
 
     for (int k = 0; ok; ++k) {
+      TRACE_AT(3328 + (k & 31) * 8 + 0);
       ok = warp_wait(smem_u32(&ctrl->sched_full[k & 1]), (k >> 1) & 1);
       if (!ok || *abort_flag) { ok = false; break; }
       const int item = ctrl->sched_item[k & 1];
       if (item < 0) break;
-      const ItemWork w = decode_item(p, item, lane);
+      const ItemWork w = ctrl->sched_work[k & 1];
+      TRACE_AT(3328 + (k & 31) * 8 + 1);
       ok = warp_wait(smem_u32(&ctrl->q_full), k & 1);
       if (!ok) break;
+      TRACE_AT(3328 + (k & 31) * 8 + 2);
       if (w.nkv_max > 0) {
         ok = ring_full_wait(ring_base);
         if (!ok) break;
+        TRACE_AT(3328 + (k & 31) * 8 + 3);
         tc_fence_after();
         for (int s = 0; s < kSlots; ++s) if (w.nkv[s] > 0) issue_s(s, ring_base);
+        TRACE_AT(3328 + (k & 31) * 8 + 4);
         if (lane == 0) {
           mma_commit(smem_u32(&ctrl->kv_empty[ring_base % kRing]));
           if (w.nkv_max == 1) mma_commit(smem_u32(&ctrl->q_empty));
@@ -527,7 +552,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok || *abort_flag) { ok = false; break; }
       const int item = ctrl->sched_item[k & 1];
       if (item < 0) break;
-      const ItemWork w = decode_item(p, item, lane);
+      const ItemWork w = ctrl->sched_work[k & 1];
       const int n = s == 0 ? w.nkv[0] : w.nkv[1];
       const int m0s = s == 0 ? w.m0[0] : w.m0[1];
       const int row_abs = m0s + row;                    // query index inside the sequence
@@ -654,6 +679,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       if (!ok) break;
       // ---------------- epilogue of the item ----------------
+      if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 0);
       if (n > 0) {
         ok = warp_wait(smem_u32(&ctrl->o_done[s]), (tile_cnt - 1) & 1);
         if (!ok) break;
@@ -666,6 +692,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       l += ctrl->xchg[xchg_cnt & 1][s][half ^ 1][row];
       ++xchg_cnt;
       tc_fence_after();
+      if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 1);
       const bool slot_live = w.valid && m0s < w.len_q;
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int rows_valid = slot_live ? min(kBM, w.len_q - m0s) : 0;
@@ -713,6 +740,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       __syncwarp();
+      if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 2);
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));
     }
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
