@@ -43,7 +43,8 @@ L2_FLUSH_BYTES = 512 << 20
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/; None until a capture exists for the workload.
 NCU_TRAFFIC_BYTES = {"c2": None, "c3": None, "c4": None, "c5": None}
-# kernels of this library launched per call of the entry point
+# kernels of this library launched per call of the entry point (prefill: the persistent kernel;
+# decode: planner + split kernel with fused merge)
 LAUNCHES_PER_STEP = {"c2": 1, "c3": 1, "c4": 2, "c5": 2}
 
 

@@ -17,9 +17,9 @@ def all_gather_outputs(shard: torch.Tensor, group: Optional[dist.ProcessGroup] =
     if world == 1:
         return [shard]
     flat = shard.contiguous()
-    out = torch.empty((world,) + tuple(flat.shape), dtype=flat.dtype, device=flat.device)
+    out = torch.empty((world * flat.shape[0],) + tuple(flat.shape[1:]), dtype=flat.dtype, device=flat.device)
     dist.all_gather_into_tensor(out, flat, group=group)
-    return list(out.unbind(0))
+    return list(out.chunk(world, dim=0))
 
 
 def all_gather_ragged(shard: torch.Tensor, group: Optional[dist.ProcessGroup] = None) -> List[torch.Tensor]:
