@@ -165,7 +165,7 @@ def time_resident(wl, steps, warmup, flush, world):
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     for i in range(steps):
         flush.zero_()                      # evicts L2; also keeps the GPU busy while the host prepares the launch
-        torch.cuda._sleep(200_000)
+        torch.cuda._sleep(2_000_000)   # ~1 ms: the host finishes preparing the launch meanwhile
         starts[i].record()
         wl.run()
         stops[i].record()

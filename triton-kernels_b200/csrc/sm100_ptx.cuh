@@ -1,6 +1,6 @@
 // Inline-PTX wrappers for the Blackwell (sm_100a) features the prefill kernel uses:
 // mbarrier, TMA tiled loads, tensor memory (TMEM) allocation / load / store and
-// tcgen05.mma with shared-memory descriptors.  No cluster multicast anywhere.
+// tcgen05.mma with shared-memory descriptors.  Every copy targets this CTA only (no clusters).
 #pragma once
 
 #include <cuda.h>
