@@ -296,7 +296,8 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
 
 // kQRegs: keep the Q fragments in registers (one 16-row tile per warp, 4*D/16 registers); otherwise they are
 // re-read from shared memory at every k-step, which frees registers so that two CTAs fit on an SM.
-template <typename T, int D, bool kQRegs, int kStages, int kMaxThreads, int kMinBlocks>
+// NB: 16-key blocks a consumer warp handles per step (2 when a warp owns 32 or more keys of a stage).
+template <typename T, int D, bool kQRegs, int kStages, int NB, int kMaxThreads, int kMinBlocks>
 __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                          const __grid_constant__ CUtensorMap tm_v,
                                                          const DecodeParams p) {
@@ -472,60 +473,65 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
       const int tile_t0 = t_begin + tile * kTileN;
       const int valid = len - tile_t0;  // keys of this tile that belong to the sequence
 
-      for (int sb = ks; sb < kTileN / 16; sb += KS) {
+      // one step = NB consecutive 16-key blocks: the softmax bookkeeping (max, shuffles, rescale test) and the
+      // Q fragment reads are shared by the NB blocks
+      for (int sb = ks * NB; sb < kTileN / 16; sb += KS * NB) {
         const int tok0 = sb * 16;             // within tile
         const int abs0 = tile_t0 + tok0;      // within sequence
         if (abs0 >= t_end) break;
-        if (valid < tok0 + 16) {
+        if (valid < tok0 + 16 * NB) {
           // keys past the sequence end get P == 0, but their V rows may hold anything (page tails,
           // the next sequence, stale shared memory): zero them so that 0 * x stays 0
           unsigned char* vtile = stage_base + stage * STAGE_BYTES + TILE_BYTES;
           const int first = max(valid, tok0);
-          const int npieces = (tok0 + 16 - first) * CHUNKS * 8;
+          const int npieces = (tok0 + 16 * NB - first) * CHUNKS * 8;
           for (int i = lane; i < npieces; i += 32) {
             const int t = first + i / (CHUNKS * 8), cb = (i >> 3) % CHUNKS;
             *reinterpret_cast<uint4*>(vtile + tile_row_offset<CHUNKS>(t, cb, p.box_shift) + ((i & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
           }
           __syncwarp();
         }
-        float s[2][4];
+        float s[2 * NB][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
+        for (int i = 0; i < 2 * NB; ++i) { s[i][0] = 0.f; s[i][1] = 0.f; s[i][2] = 0.f; s[i][3] = 0.f; }
         {
           const int mat = lane >> 3;
-          const int trow = tok0 + (mat >> 1) * 8 + (lane & 7);
-          uint32_t roff[CHUNKS];
+          uint32_t roff[NB][CHUNKS];
 #pragma unroll
-          for (int cb = 0; cb < CHUNKS; ++cb) roff[cb] = tile_row_offset<CHUNKS>(trow, cb, p.box_shift);
+          for (int nb = 0; nb < NB; ++nb) {
+            const int trow = tok0 + nb * 16 + (mat >> 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int cb = 0; cb < CHUNKS; ++cb) roff[nb][cb] = tile_row_offset<CHUNKS>(trow, cb, p.box_shift);
+          }
 #pragma unroll
           for (int kk = 0; kk < KSTEPS; ++kk) {
-            uint32_t kb[4];
             const int ch = kk * 2 + (mat & 1);   // 16-byte piece index along D
-            ldmatrix_x4(kb, ks_base + swz_piece(roff[ch >> 3], ch & 7));
-            if constexpr (kQRegs) {
-              mma_m16n8k16<T>(s[0], qf[kk], kb[0], kb[1]);
-              mma_m16n8k16<T>(s[1], qf[kk], kb[2], kb[3]);
-            } else {
+            if constexpr (!kQRegs) {
               const int qch = kk * 2 + (lane >> 4);
               ldmatrix_x4(qf[0], q_rbase + ((qch ^ (q_row & 7)) << 4));
-              mma_m16n8k16<T>(s[0], qf[0], kb[0], kb[1]);
-              mma_m16n8k16<T>(s[1], qf[0], kb[2], kb[3]);
+            }
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+              uint32_t kb[4];
+              ldmatrix_x4(kb, ks_base + swz_piece(roff[nb][ch >> 3], ch & 7));
+              mma_m16n8k16<T>(s[2 * nb], qf[kQRegs ? kk : 0], kb[0], kb[1]);
+              mma_m16n8k16<T>(s[2 * nb + 1], qf[kQRegs ? kk : 0], kb[2], kb[3]);
             }
           }
         }
-        // scale, mask (only where the tile reaches a row's last visible key), online softmax in the exp2 domain
+        // scale, mask (only where the step reaches a row's last visible key), online softmax in the exp2 domain
         float mx0 = -INFINITY, mx1 = -INFINITY;
-        const bool all_visible = __all_sync(0xffffffffu, abs0 + 15 <= lim_min);
+        const bool all_visible = __all_sync(0xffffffffu, abs0 + 16 * NB - 1 <= lim_min);
         if (all_visible) {
 #pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
+          for (int nt = 0; nt < 2 * NB; ++nt) {
             s[nt][0] *= sl2; s[nt][1] *= sl2; s[nt][2] *= sl2; s[nt][3] *= sl2;
             mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
             mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
           }
         } else {
 #pragma unroll
-          for (int nt = 0; nt < 2; ++nt) {
+          for (int nt = 0; nt < 2 * NB; ++nt) {
             const int col = abs0 + nt * 8 + 2 * (lane & 3);
             s[nt][0] = (col <= lim0) ? s[nt][0] * sl2 : -INFINITY;
             s[nt][1] = (col + 1 <= lim0) ? s[nt][1] * sl2 : -INFINITY;
@@ -552,29 +558,35 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
         }
         const float ms0 = (m_used[0] == -INFINITY) ? 0.f : m_used[0];
         const float ms1 = (m_used[1] == -INFINITY) ? 0.f : m_used[1];
-        uint32_t pa[4];
+        uint32_t pa[NB][4];
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
+        for (int nt = 0; nt < 2 * NB; ++nt) {
           const float p0 = fast_exp2(s[nt][0] - ms0), p1 = fast_exp2(s[nt][1] - ms0);
           const float p2 = fast_exp2(s[nt][2] - ms1), p3 = fast_exp2(s[nt][3] - ms1);
           l_run[0] += p0 + p1;   // per-lane partial row sums; reduced over the quad at the end
           l_run[1] += p2 + p3;
-          pa[nt * 2 + 0] = ElemTraits<T>::pack2(p0, p1);
-          pa[nt * 2 + 1] = ElemTraits<T>::pack2(p2, p3);
+          pa[nt >> 1][(nt & 1) * 2 + 0] = ElemTraits<T>::pack2(p0, p1);
+          pa[nt >> 1][(nt & 1) * 2 + 1] = ElemTraits<T>::pack2(p2, p3);
         }
         {
           const int mat = lane >> 3;
-          const int trow = tok0 + (mat & 1) * 8 + (lane & 7);
-          uint32_t roff[CHUNKS];
+          uint32_t roff[NB][CHUNKS];
 #pragma unroll
-          for (int cb = 0; cb < CHUNKS; ++cb) roff[cb] = tile_row_offset<CHUNKS>(trow, cb, p.box_shift);
+          for (int nb = 0; nb < NB; ++nb) {
+            const int trow = tok0 + nb * 16 + (mat & 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int cb = 0; cb < CHUNKS; ++cb) roff[nb][cb] = tile_row_offset<CHUNKS>(trow, cb, p.box_shift);
+          }
 #pragma unroll
           for (int n0 = 0; n0 < D / 16; ++n0) {
-            uint32_t vb[4];
             const int ch = n0 * 2 + (mat >> 1);
-            ldmatrix_x4_trans(vb, vs_base + swz_piece(roff[ch >> 3], ch & 7));
-            mma_m16n8k16<T>(o[2 * n0], pa, vb[0], vb[1]);
-            mma_m16n8k16<T>(o[2 * n0 + 1], pa, vb[2], vb[3]);
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+              uint32_t vb[4];
+              ldmatrix_x4_trans(vb, vs_base + swz_piece(roff[nb][ch >> 3], ch & 7));
+              mma_m16n8k16<T>(o[2 * n0], pa[nb], vb[0], vb[1]);
+              mma_m16n8k16<T>(o[2 * n0 + 1], pa[nb], vb[2], vb[3]);
+            }
           }
         }
       }
@@ -806,17 +818,18 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
       if ((rc = make_kv_rows_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box, rstride, D * 2ll))) return rc;
       if ((rc = make_kv_rows_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box, rstride, D * 2ll))) return rc;
     }
-#define B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, QREGS, STAGES, MAXT, MINB)                                    \
+#define B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, QREGS, STAGES, NBLK, MAXT, MINB)                                    \
     do {                                                                                                  \
-      rc = set_smem(decode_mma_kernel<TYPE, DIM, QREGS, STAGES, MAXT, MINB>, smem);                       \
+      rc = set_smem(decode_mma_kernel<TYPE, DIM, QREGS, STAGES, NBLK, MAXT, MINB>, smem);                       \
       if (rc) return rc;                                                                                  \
-      decode_mma_kernel<TYPE, DIM, QREGS, STAGES, MAXT, MINB><<<grid, threads, smem, stream>>>(tk, tv, p);\
+      decode_mma_kernel<TYPE, DIM, QREGS, STAGES, NBLK, MAXT, MINB><<<grid, threads, smem, stream>>>(tk, tv, p);\
     } while (0)
-#define B200ATTN_LAUNCH_DECODE(TYPE, DIM)                                          \
-    do {                                                                           \
-      if (threads <= 160) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 2, 160, 3);   \
-      else if (threads <= 224) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 224, 2);\
-      else B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 288, 1);                  \
+#define B200ATTN_LAUNCH_DECODE(TYPE, DIM)                                                \
+    do {                                                                                 \
+      if (threads <= 160) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 2, 1, 160, 3);      \
+      else if (threads <= 224) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 2, 224, 2); \
+      else if (ksl == 4) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 1, 288, 1);       \
+      else B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 2, 288, 1);                     \
     } while (0)
     if (a.dtype == B200ATTN_BF16) {
       if (D == 128) B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 128); else B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 64);
