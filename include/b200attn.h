@@ -171,6 +171,38 @@ int b200attn_decode(const b200attn_decode_args_t* args, void* cuda_stream);
 int b200attn_decode_static(const b200attn_decode_args_t* args, void* cuda_stream);
 
 /*
+ * Paged KV-cache append: copies the new rows of every sequence into the pages its block table names.
+ *   src        [total_rows, heads, head_dim]  new K (or V) rows of all sequences, packed
+ *   src_indptr [B+1] prefix sums over src rows;  dst_pos [B] position in each sequence of its first new row
+ *              (NULL = 0: build the cache from scratch); both share the width given by indptr_is_i64
+ *   cache      [cache_rows, heads, head_dim], cache_rows = pages * page_size;  table [B, table_stride] int32
+ * Row r of sequence b lands in cache row table[b][(dst_pos[b]+r) / page_size] * page_size + (dst_pos[b]+r) % page_size.
+ * row_bytes = heads * head_dim * element size must be a multiple of 16; src and cache 16-byte aligned.
+ * Table entries outside the cache are reported through the workspace error word and skipped.
+ * Replaces the Python scatter loops of the reference's fixtures (tests/test_attention.py:101-134,
+ * tests/test_decode.py:93-130, benchmarks/attention.py:351-431).
+ */
+typedef struct b200attn_paged_append_args_t {
+  const void* src;
+  void* cache;
+  const void* src_indptr;
+  const void* dst_pos;
+  const int32_t* table;
+  void* workspace;        /* >= 256 bytes, 256-byte aligned; word 0 is the device error code */
+  size_t workspace_bytes;
+  int64_t total_rows;
+  int64_t cache_rows;
+  int64_t table_stride;
+  int32_t row_bytes;
+  int32_t indptr_is_i64;
+  int32_t batch;
+  int32_t page_size;
+  int32_t device;
+} b200attn_paged_append_args_t;
+
+int b200attn_paged_append(const b200attn_paged_append_args_t* args, void* cuda_stream);
+
+/*
  * Reads (and clears) the error word a kernel of an earlier call may have set in
  * `workspace` (bounded wait expired, page index out of range).  Synchronises
  * `cuda_stream`.  Returns 0, or B200ATTN_E_DEVICE with the code in *code.

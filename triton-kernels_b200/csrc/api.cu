@@ -5,6 +5,7 @@
 
 #include "common.cuh"
 #include "decode_launch.h"
+#include "paged_append_launch.h"
 #include "prefill_launch.h"
 
 namespace b200attn {
@@ -168,6 +169,22 @@ int b200attn_decode_static(const b200attn_decode_args_t* a, void* cuda_stream) {
   DeviceGuard guard;
   if ((rc = guard.enter(a->device))) return rc;
   return launch_decode_static(*a, info.sm_count, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int b200attn_paged_append(const b200attn_paged_append_args_t* a, void* cuda_stream) {
+  if (!a) { set_error("args is null"); return B200ATTN_E_INVALID; }
+  if (a->batch < 0 || a->total_rows < 0 || a->cache_rows < 0 || a->table_stride < 0 || a->page_size <= 0) { set_error("paged_append: negative extent or bad page size"); return B200ATTN_E_INVALID; }
+  if (a->row_bytes <= 0 || (a->row_bytes & 15)) { set_error("paged_append: row_bytes %d is not a positive multiple of 16", a->row_bytes); return B200ATTN_E_UNSUPPORTED; }
+  if (a->batch == 0 || a->total_rows == 0) return B200ATTN_OK;
+  if (!a->src || !a->cache || !a->src_indptr || !a->table) { set_error("paged_append: null pointer"); return B200ATTN_E_INVALID; }
+  if (!aligned16(a->src) || !aligned16(a->cache)) { set_error("paged_append: src and cache must be 16-byte aligned"); return B200ATTN_E_INVALID; }
+  if (!a->workspace || a->workspace_bytes < static_cast<size_t>(kHeaderBytes)) { set_error("paged_append: workspace needs %d bytes", kHeaderBytes); return B200ATTN_E_WORKSPACE; }
+  b200attn_device_info_t info;
+  int rc;
+  if ((rc = check_arch(a->device, &info))) return rc;
+  DeviceGuard guard;
+  if ((rc = guard.enter(a->device))) return rc;
+  return launch_paged_append(*a, info.sm_count, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int b200attn_check_workspace(void* workspace, void* cuda_stream, int32_t* code) {

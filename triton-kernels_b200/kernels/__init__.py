@@ -5,6 +5,7 @@ from .attention import (
     flash_attention_v2,
 )
 from .decode import decode_attention
+from .paged_cache import append_paged_kv
 from .speculative_decode import (
     speculative_decode_attention,
 )
@@ -14,4 +15,5 @@ __all__ = [
     "flash_attention_v2",
     "speculative_decode_attention",
     "decode_attention",
+    "append_paged_kv",
 ]

@@ -32,6 +32,7 @@ EXPORTS = (
     "b200attn_prefill",
     "b200attn_decode",
     "b200attn_decode_static",
+    "b200attn_paged_append",
     "b200attn_check_workspace",
 )
 
@@ -105,6 +106,26 @@ class DecodeArgs(C.Structure):
     ]
 
 
+class PagedAppendArgs(C.Structure):
+    _fields_ = [
+        ("src", C.c_void_p),
+        ("cache", C.c_void_p),
+        ("src_indptr", C.c_void_p),
+        ("dst_pos", C.c_void_p),
+        ("table", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+        ("total_rows", C.c_int64),
+        ("cache_rows", C.c_int64),
+        ("table_stride", C.c_int64),
+        ("row_bytes", C.c_int32),
+        ("indptr_is_i64", C.c_int32),
+        ("batch", C.c_int32),
+        ("page_size", C.c_int32),
+        ("device", C.c_int32),
+    ]
+
+
 _lib: Optional[C.CDLL] = None
 _lib_lock = threading.Lock()
 
@@ -142,6 +163,8 @@ def lib() -> C.CDLL:
         handle.b200attn_decode.restype = C.c_int
         handle.b200attn_decode_static.argtypes = [C.POINTER(DecodeArgs), C.c_void_p]
         handle.b200attn_decode_static.restype = C.c_int
+        handle.b200attn_paged_append.argtypes = [C.POINTER(PagedAppendArgs), C.c_void_p]
+        handle.b200attn_paged_append.restype = C.c_int
         handle.b200attn_check_workspace.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
         handle.b200attn_check_workspace.restype = C.c_int
         got = handle.b200attn_abi_version()
