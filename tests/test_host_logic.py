@@ -97,12 +97,13 @@ def test_decode_plan_bounds(qh, kvh, m):
 
 
 def test_prefill_grid_and_boxes():
-    from utils.launch_config import paged_box_rows, prefill_ctas
+    from utils.launch_config import paged_box_rows, prefill_items
 
-    assert prefill_ctas("dense", 2, 32, max_q=2048) == 2 * 32 * 8
+    assert prefill_items("dense", 2, 32, 8, max_q=2048) == 2 * 16 * 16       # head pairs x 128-row tiles
+    assert prefill_items("dense", 2, 8, 8, max_q=2048) == 2 * 8 * 8          # MHA: 256-row blocks per head
     lens = [2638, 3890, 2767, 3581]
-    need = sum(-(-n // 256) for n in lens)
-    assert prefill_ctas("ragged", len(lens), 1, total_q=sum(lens)) >= need
+    assert prefill_items("ragged", len(lens), 1, 1, total_q=sum(lens)) >= sum(-(-n // 256) for n in lens)
+    assert prefill_items("ragged", len(lens), 2, 1, total_q=sum(lens)) >= sum(-(-n // 128) for n in lens)
     assert [paged_box_rows(p) for p in (1, 8, 16, 24, 48, 128, 256, 384)] == [1, 8, 16, 8, 16, 128, 128, 128]
     for p in (1, 8, 16, 24, 48, 128, 256, 384):
         assert p % paged_box_rows(p) == 0 or paged_box_rows(p) == 128 and p % 128 == 0

@@ -54,6 +54,14 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 #define B200ATTN_EXP_EMU_OF4 0
 #endif
 constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
+// P = exp2(t) evaluated directly in the 16-bit format of P (ex2.approx on bf16x2 / f16x2: two results per MUFU
+// operation, no separate conversion).  The argument t = s*scale*log2e - m is rounded to 16 bits first; entries near
+// the row max have |t| small and lose nothing, far entries lose relative accuracy where their weight is negligible
+// (measured on causal S=2048, D=128: max-abs error vs fp32 SDPA 7.5e-3 either way for bf16, 1.1e-3 vs 0.8e-3 for fp16).
+#ifndef B200ATTN_PACKED_EXP
+#define B200ATTN_PACKED_EXP 0
+#endif
+constexpr bool kPackedExp = B200ATTN_PACKED_EXP != 0;
 
 // Development aid (compiled out unless B200ATTN_TRACE is defined): CTA (0,0,0) stamps clock64 into the
 // workspace behind the header, one slot per (role, iteration, event).
@@ -63,15 +71,18 @@ constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
 #define TRACE_AT(idx) do { } while (0)
 #endif
 
-// Everything one work item (sequence, q head, 256-row query block) needs; decoded once by the scheduler warp.
+// Everything one work item needs; decoded once by the scheduler warp.  An item is two 128-row query tiles
+// ("slots") that share one KV head: with an even GQA group the same 128 rows of two neighbouring q heads (equal
+// causal extents, so both slots always have work), otherwise two consecutive row tiles of one q head.
 struct ItemWork {
   bool valid;
-  int q_head;
   int len_q, len_k;
-  long long q_row0;    // first q row of the sequence on the token axis of the q tensor map
   long long kv_row0;   // first kv row of the sequence (dense / ragged)
-  int q_head_coord, kv_head_coord;
+  int kv_head_coord;
   int b;
+  int q_head[kSlots];
+  long long q_row0[kSlots];   // first q row of the sequence on the token axis of the q tensor map
+  int q_head_coord[kSlots];
   int m0[kSlots];      // first query row of each slot inside the sequence
   int nkv[kSlots];     // 128-key tiles each slot visits
   int nkv_max;
@@ -114,10 +125,10 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ok);
 }
 
-__device__ __forceinline__ int pairs_of(int len_q) { return (len_q + 2 * kBM - 1) / (2 * kBM); }
+__device__ __forceinline__ int blocks_of(int len_q, int rows) { return (len_q + rows - 1) / rows; }
 
-// Ragged layout: warp-cooperative search of the (sequence, pair) that owns flat pair index x.
-__device__ __forceinline__ bool find_ragged_work(const PrefillParams& p, int x, int lane, int* out_b, int* out_pair) {
+// Ragged layout: warp-cooperative search of the (sequence, row block) that owns flat block index x.
+__device__ __forceinline__ bool find_ragged_work(const PrefillParams& p, int x, int rows, int lane, int* out_b, int* out_pair) {
   int base = 0;
   for (int b0 = 0; b0 < p.batch; b0 += 32) {
     const int b = b0 + lane;
@@ -126,7 +137,7 @@ __device__ __forceinline__ bool find_ragged_work(const PrefillParams& p, int x, 
       const long long a = load_index(p.q_indptr, p.indptr_is_i64, b);
       const long long e = load_index(p.q_indptr, p.indptr_is_i64, b + 1);
       const long long n = e > a ? e - a : 0;
-      cnt = pairs_of(static_cast<int>(n));
+      cnt = blocks_of(static_cast<int>(n), rows);
     }
     int incl = cnt;
     for (int o = 1; o < 32; o <<= 1) {
@@ -163,28 +174,37 @@ __global__ void __launch_bounds__(256) cast_f32_to_f16_kernel(const float4* __re
 
 __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item, int lane) {
   ItemWork w;
-  int wb = -1, wpair = 0, whead = 0;
+  const int heads_per_item = p.head_pair ? 2 : 1;
+  const int head_units = p.q_heads / heads_per_item;
+  const int rows = p.head_pair ? kBM : 2 * kBM;      // query rows an item covers
+  int wb = -1, wblock = 0, wunit = 0;
   if (p.layout == B200ATTN_RAGGED) {
-    whead = item % p.q_heads;
-    if (!find_ragged_work(p, item / p.q_heads, lane, &wb, &wpair)) wb = -1;
+    wunit = item % head_units;
+    if (!find_ragged_work(p, item / head_units, rows, lane, &wb, &wblock)) wb = -1;
   } else {
-    // 256-row blocks are the slowest-varying index and, under a causal mask, are handed out heaviest first;
+    // row blocks are the slowest-varying index and, under a causal mask, are handed out heaviest first;
     // the q heads of one KV head are neighbours and share its K/V in L2
-    const int per_block = p.q_heads * p.batch;
-    const int npairs = pairs_of(p.max_q);
+    const int per_block = head_units * p.batch;
+    const int nblocks = blocks_of(p.max_q, rows);
     const int blk = item / per_block, rest = item - blk * per_block;
-    wpair = p.is_causal ? (npairs - 1 - blk) : blk;
-    whead = rest % p.q_heads;
-    wb = rest / p.q_heads;
+    wblock = p.is_causal ? (nblocks - 1 - blk) : blk;
+    wunit = rest % head_units;
+    wb = rest / head_units;
   }
   w.valid = wb >= 0;
   w.b = wb;
-  w.q_head = whead;
   w.len_q = w.len_k = 0;
-  w.q_row0 = w.kv_row0 = 0;
-  w.q_head_coord = w.kv_head_coord = 0;
+  w.kv_row0 = 0;
+  w.kv_head_coord = 0;
+#pragma unroll
+  for (int s = 0; s < kSlots; ++s) {
+    w.q_head[s] = p.head_pair ? wunit * 2 + s : wunit;
+    w.m0[s] = p.head_pair ? wblock * kBM : (wblock * kSlots + s) * kBM;
+    w.q_row0[s] = 0;
+    w.q_head_coord[s] = 0;
+  }
   if (w.valid) {
-    const int kv_head = whead / p.group;
+    const int kv_head = w.q_head[0] / p.group;
     if (p.layout == B200ATTN_RAGGED) {
       const long long qa = load_index(p.q_indptr, p.indptr_is_i64, wb);
       const long long qe = load_index(p.q_indptr, p.indptr_is_i64, wb + 1);
@@ -192,13 +212,14 @@ __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item
       const long long ke = load_index(p.kv_indptr, p.indptr_is_i64, wb + 1);
       w.len_q = static_cast<int>(qe > qa ? qe - qa : 0);
       w.len_k = static_cast<int>(ke > ka ? ke - ka : 0);
-      w.q_row0 = qa;
       w.kv_row0 = ka;
-      w.q_head_coord = whead;
       w.kv_head_coord = kv_head;
+#pragma unroll
+      for (int s = 0; s < kSlots; ++s) { w.q_row0[s] = qa; w.q_head_coord[s] = w.q_head[s]; }
     } else {
       w.len_q = p.max_q;
-      w.q_row0 = (static_cast<long long>(wb) * p.q_heads + whead) * p.max_q;
+#pragma unroll
+      for (int s = 0; s < kSlots; ++s) w.q_row0[s] = (static_cast<long long>(wb) * p.q_heads + w.q_head[s]) * p.max_q;
       if (p.layout == B200ATTN_DENSE) {
         w.len_k = p.max_kv;
         w.kv_row0 = (static_cast<long long>(wb) * p.kv_heads + kv_head) * p.max_kv;
@@ -214,7 +235,6 @@ __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item
   w.nkv_max = 0;
 #pragma unroll
   for (int s = 0; s < kSlots; ++s) {
-    w.m0[s] = (wpair * kSlots + s) * kBM;
     int n = 0;
     if (w.valid && w.m0[s] < w.len_q) {
       int kv_hi = w.len_k;
@@ -306,7 +326,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         for (int s = 0; s < kSlots; ++s) {
           if (w.nkv[s] == 0) continue;
           for (int c = 0; c < Plan::kChunks; ++c)
-            tma_prefetch_3d(&tm_q, c * 64, w.q_head_coord, static_cast<int>(w.q_row0 + w.m0[s]));
+            tma_prefetch_3d(&tm_q, c * 64, w.q_head_coord[s], static_cast<int>(w.q_row0[s] + w.m0[s]));
         }
         if (p.layout != B200ATTN_PAGED && w.nkv_max > 0) {
           for (int c = 0; c < Plan::kChunks; ++c) {
@@ -329,7 +349,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (w.nkv[s] == 0) continue;
             for (int c = 0; c < Plan::kChunks; ++c)
               tma_load_3d(smem_base + Plan::kQOff + s * Plan::kTileBytes + c * Plan::kChunkBytes, &tm_q,
-                          smem_u32(&ctrl->q_full), c * 64, w.q_head_coord, static_cast<int>(w.q_row0 + w.m0[s]));
+                          smem_u32(&ctrl->q_full), c * 64, w.q_head_coord[s], static_cast<int>(w.q_row0[s] + w.m0[s]));
           }
         } else {
           mbar_arrive(smem_u32(&ctrl->q_full));   // keeps one q_full phase per item
@@ -639,6 +659,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           for (int i = 0; i < 16; ++i) {
             const uint64_t t2 = fma_f2(pack_f2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), sl2_2, negm_2);
             float p0, p1;
+            if constexpr (kPackedExp) {
+              float a, b;
+              unpack_f2(t2, a, b);
+              pk[i] = ex2_packed(ElemTraits<T>::pack2(a, b), T());
+              unpack16(pk[i], T(), p0, p1);
+              rs2 = add_f2(rs2, pack_f2(p0, p1));
+              continue;
+            }
             if ((i & 3) < kExpEmuOf4) {
               // 2^t = 2^n * 2^r with n = round(t), r in [-0.5, 0.5]; n is read off the magic-number sum
               float a, b;
@@ -697,8 +725,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const int rows_valid = slot_live ? min(kBM, w.len_q - m0s) : 0;
       long long off;
-      if (p.layout == B200ATTN_RAGGED) off = ((w.q_row0 + m0s + row) * p.q_heads + w.q_head) * D;
-      else off = (w.q_row0 + m0s + row) * D;
+      const long long qrow0 = s == 0 ? w.q_row0[0] : w.q_row0[1];
+      const int qhead = s == 0 ? w.q_head[0] : w.q_head[1];
+      if (p.layout == B200ATTN_RAGGED) off = ((qrow0 + m0s + row) * p.q_heads + qhead) * D;
+      else off = (qrow0 + m0s + row) * D;
       off += half * kOCols;
       // every thread writes its own half row: 32 contiguous output columns per TMEM chunk
 #pragma unroll
@@ -826,6 +856,9 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
   p.box_rows = kBN;
   p.num_pages = 0;
   p.is_causal = a.is_causal ? 1 : 0;
+  p.head_pair = (p.group % 2 == 0) ? 1 : 0;
+  const int item_rows = p.head_pair ? kBM : 2 * kBM;
+  const int head_units = p.head_pair ? a.q_heads / 2 : a.q_heads;
   p.scale_log2 = a.sm_scale * 1.4426950408889634f;
 
   CUtensorMap tq, tk, tv;
@@ -836,8 +869,8 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
     if ((rc = make_token_map(&tq, a.dtype, a.q, a.total_q, a.q_heads, D, kBM))) return rc;
     if ((rc = make_token_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, kBN))) return rc;
     if ((rc = make_token_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, kBN))) return rc;
-    const long long pairs = a.total_q / (2 * kBM) + a.batch;
-    total_items = pairs * a.q_heads;
+    const long long pairs = a.total_q / item_rows + a.batch;
+    total_items = pairs * head_units;
   } else {
     const long long q_rows = static_cast<long long>(a.batch) * a.q_heads * a.max_q;
     if ((rc = make_token_map(&tq, a.dtype, a.q, q_rows, 1, D, kBM))) return rc;
@@ -854,7 +887,7 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
       if ((rc = make_token_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box))) return rc;
       if ((rc = make_token_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box))) return rc;
     }
-    total_items = static_cast<long long>((a.max_q + 2 * kBM - 1) / (2 * kBM)) * a.q_heads * a.batch;
+    total_items = static_cast<long long>((a.max_q + item_rows - 1) / item_rows) * head_units * a.batch;
   }
   if (total_items <= 0) return B200ATTN_OK;
   if (total_items > 0x7fffffff) { set_error("prefill: too many work items"); return B200ATTN_E_UNSUPPORTED; }

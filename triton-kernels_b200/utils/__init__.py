@@ -3,7 +3,7 @@ from .launch_config import (
     decode_items,
     decode_plan,
     paged_box_rows,
-    prefill_ctas,
+    prefill_items,
 )
 from .validation import (
     AttentionProblem,
@@ -19,7 +19,7 @@ __all__ = [
     "decode_plan",
     "detect_layout",
     "paged_box_rows",
-    "prefill_ctas",
+    "prefill_items",
     "validate_decode",
     "validate_prefill",
 ]

@@ -53,12 +53,15 @@ def decode_items(plan: DecodePlan, lengths: Sequence[int]) -> List[int]:
     return [max(1, -(-max(0, int(n)) // chunk)) for n in lengths]
 
 
-def prefill_ctas(layout: str, batch: int, q_heads: int, max_q: int = 0, total_q: int = 0) -> int:
-    """CTAs launched by the prefill kernel (each owns PREFILL_SLOTS x PREFILL_BLOCK_M query rows)."""
-    rows = PREFILL_BLOCK_M * PREFILL_SLOTS
+def prefill_items(layout: str, batch: int, q_heads: int, kv_heads: int, max_q: int = 0, total_q: int = 0) -> int:
+    """Work items of the persistent prefill kernel.  An item is two 128-row query tiles that share a KV head: two
+    neighbouring q heads over the same rows when the GQA group is even, else two consecutive row tiles of one head."""
+    head_pair = (q_heads // kv_heads) % 2 == 0
+    rows = PREFILL_BLOCK_M if head_pair else PREFILL_BLOCK_M * PREFILL_SLOTS
+    units = q_heads // 2 if head_pair else q_heads
     if layout == "ragged":
-        return (total_q // rows + batch) * q_heads
-    return -(-max_q // rows) * q_heads * batch
+        return (total_q // rows + batch) * units
+    return -(-max_q // rows) * units * batch
 
 
 def paged_box_rows(page_size: int) -> int:
