@@ -23,6 +23,7 @@
 //       performs the log-sum-exp merge.  No CTA ever waits for another.
 #include <algorithm>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "decode_launch.h"
@@ -625,6 +626,360 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
 }
 
 // ---------------------------------------------------------------------------
+// tcgen05 kernel for many q rows per KV head (speculative decode: group x drafts > 16 rows).
+//
+// With 17..128 rows the warp-level MMA kernel above is bound by shared-memory bandwidth: every K/V fragment is
+// re-read by ldmatrix once per 16-row tile.  Here the rows are padded to one 128-row tcgen05 tile whose A operands
+// live in tensor memory (Q is written there once per CTA, P once per key tile), so shared memory is read exactly
+// once per K/V byte, by the tensor core.  Per 64-key tile: S = Q K^T (TS MMA, 128 x 64 x D) -> the softmax warps
+// (thread = q row, only the warps that hold real rows work) read S from TMEM, mask, keep the running max / sum in
+// the exp2 domain with the lazy 2^8 rescale, write P as packed 16-bit over S -> O += P V (TS MMA, V is the
+// MN-major B operand).  Two CTAs share an SM (256 TMEM columns, 3 stages of 64 keys each), which overlaps one CTA's
+// softmax with the other's MMAs.  Planner, partials and the ticket merge are shared with the kernels above.
+// ---------------------------------------------------------------------------
+constexpr int kUmmaStages = 3;
+constexpr int kUmmaTmemCols = 256;
+
+struct __align__(8) UmmaCtrl {
+  uint64_t full[kUmmaStages];
+  uint64_t empty[kUmmaStages];
+  uint64_t q_ready;
+  uint64_t s_full;
+  uint64_t p_ready;
+  uint64_t o_done;
+  uint32_t tmem_base;
+  int ticket;
+  int abort_flag;
+};
+
+template <typename T, int D>
+__global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_constant__ CUtensorMap tm_k,
+                                                             const __grid_constant__ CUtensorMap tm_v,
+                                                             const DecodeParams p) {
+  using namespace ptx;
+  extern __shared__ unsigned char smem_raw[];
+  constexpr int CHUNKS = D / 64;
+  constexpr int CHUNK_BYTES = kTileN * 128;
+  constexpr int TILE_BYTES = CHUNKS * CHUNK_BYTES;
+  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
+  constexpr int kQCols = D / 2;               // TMEM columns of the packed 16-bit Q tile
+  constexpr int kSCol = kQCols;               // S (64 fp32 columns); P overwrites its first 32
+  constexpr int kOCol = kQCols + kTileN;      // O (D fp32 columns)
+  static_assert(kOCol + D <= kUmmaTmemCols, "TMEM budget");
+
+  const int n_items = p.header[2];
+  const int item = blockIdx.x / p.kv_heads;
+  if (item >= n_items) return;
+  const int h = blockIdx.x - item * p.kv_heads;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int kProducer = 4, kMma = 5;
+
+  const int4 rec0 = __ldg(p.item_info + 2 * item);
+  const int4 rec1 = __ldg(p.item_info + 2 * item + 1);
+  const int b = rec0.x, c = rec0.y, n_chunks = rec0.z, item0 = rec0.w;
+  const int chunk = p.header[1];
+  const int len = rec1.x;
+  const long long seq_start = (static_cast<long long>(rec1.w) << 32) | static_cast<unsigned int>(rec1.z);
+  const int t_begin = c * chunk;
+  const int t_end = min(len, t_begin + chunk);
+  const int ntiles = t_end > t_begin ? (t_end - t_begin + kTileN - 1) / kTileN : 0;
+  const int R = p.rows;
+  const int active_warps = (R + 31) >> 5;      // softmax warps that own real rows
+
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  UmmaCtrl* ctrl = reinterpret_cast<UmmaCtrl*>(smem + kUmmaStages * STAGE_BYTES);
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (tid == 0) {
+    for (int i = 0; i < kUmmaStages; ++i) { mbar_init(smem_u32(&ctrl->full[i]), 1); mbar_init(smem_u32(&ctrl->empty[i]), 1); }
+    mbar_init(smem_u32(&ctrl->q_ready), active_warps * 32);
+    mbar_init(smem_u32(&ctrl->s_full), 1);
+    mbar_init(smem_u32(&ctrl->p_ready), active_warps * 32);
+    mbar_init(smem_u32(&ctrl->o_done), 1);
+    ctrl->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kMma) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), kUmmaTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctrl->tmem_base;
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  // per-row softmax state of the softmax threads (row = tid)
+  float m_used = -INFINITY, l_run = 0.f;
+
+  if (warp == kProducer) {
+    // =========================== TMA producer ===========================
+    if (lane == 0) { prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); }
+    int h_coord = h;
+    long long row0 = seq_start;
+    if (p.layout == B200ATTN_DENSE) { h_coord = 0; row0 = (static_cast<long long>(b) * p.kv_heads + h) * p.max_kv; }
+    bool ok = true;
+    int issued = 0;
+    const int box_rows = 1 << p.box_shift;
+    for (int tile = 0; tile < ntiles; ++tile) {
+      const int stage = tile % kUmmaStages, use = tile / kUmmaStages;
+      if (use > 0) {
+        ok = warp_wait(smem_u32(&ctrl->empty[stage]), (use - 1) & 1);
+        if (!ok || *abort_flag) { ok = false; break; }
+      }
+      const int t0 = t_begin + tile * kTileN;
+      const uint32_t kdst = smem_base + stage * STAGE_BYTES;
+      const uint32_t vdst = kdst + TILE_BYTES;
+      const uint32_t bar = smem_u32(&ctrl->full[stage]);
+      if (p.layout != B200ATTN_PAGED) {
+        if (lane == 0) {
+          mbar_arrive_expect_tx(bar, STAGE_BYTES);
+          const int row = static_cast<int>(row0 + t0);
+#pragma unroll
+          for (int cc = 0; cc < CHUNKS; ++cc) {
+            tma_load_3d(kdst + cc * CHUNK_BYTES, &tm_k, bar, cc * 64, h_coord, row);
+            tma_load_3d(vdst + cc * CHUNK_BYTES, &tm_v, bar, cc * 64, h_coord, row);
+          }
+        }
+      } else {
+        const int boxes = kTileN >> p.box_shift;
+        const int* ktab = p.k_table + static_cast<long long>(b) * p.table_stride;
+        const int* vtab = p.v_table + static_cast<long long>(b) * p.table_stride;
+        int krow[2], vrow[2];
+        int count = 0, n = 0;
+        for (int i = lane; i < boxes; i += 32, ++n) {
+          const int t = t0 + i * box_rows;
+          int kr = -1, vr = -1;
+          if (t < t_end) {
+            int lp, off;
+            if (p.page_shift >= 0) { lp = t >> p.page_shift; off = t & (p.page_size - 1); }
+            else { lp = t / p.page_size; off = t - lp * p.page_size; }
+            const int kp = __ldg(ktab + lp), vp = __ldg(vtab + lp);
+            // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
+            const bool kbad = kp < 0 || kp >= p.num_pages, vbad = vp < 0 || vp >= p.num_pages;
+            if (kbad || vbad) p.header[0] = DEV_ERR_PAGE_RANGE;
+            if (p.num_pages > 0) {
+              kr = (kbad ? 0 : kp) * p.page_size + off;
+              vr = (vbad ? 0 : vp) * p.page_size + off;
+            }
+          }
+          krow[n] = kr; vrow[n] = vr;
+          count += (kr >= 0) + (vr >= 0);
+        }
+        for (int off = 16; off > 0; off >>= 1) count += __shfl_xor_sync(0xffffffffu, count, off);
+        if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * box_rows * 128 * CHUNKS);
+        __syncwarp();
+        n = 0;
+        for (int i = lane; i < boxes; i += 32, ++n) {
+          const uint32_t roff = static_cast<uint32_t>(i) * box_rows * 128;
+#pragma unroll
+          for (int cc = 0; cc < CHUNKS; ++cc) {
+            if (krow[n] >= 0) tma_load_3d(kdst + cc * CHUNK_BYTES + roff, &tm_k, bar, cc * 64, h_coord, krow[n]);
+            if (vrow[n] >= 0) tma_load_3d(vdst + cc * CHUNK_BYTES + roff, &tm_v, bar, cc * 64, h_coord, vrow[n]);
+          }
+        }
+      }
+      issued = tile + 1;
+    }
+    if (!ok) {
+      if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
+      for (int t = max(0, issued - kUmmaStages); t < issued; ++t)
+        mbar_wait(smem_u32(&ctrl->full[t % kUmmaStages]), (t / kUmmaStages) & 1);
+    }
+  } else if (warp == kMma) {
+    // =========================== MMA issuer ===========================
+    constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+    constexpr uint32_t idesc_s = make_idesc_f16(128, kTileN, kFmt, 0);
+    constexpr uint32_t idesc_o = make_idesc_f16(128, D, kFmt, 1);
+    const uint64_t kdesc = make_smem_desc_sw128(smem_base, 16);
+    const uint64_t vdesc = make_smem_desc_sw128(smem_base, CHUNK_BYTES);
+    const uint32_t k_hi = static_cast<uint32_t>(kdesc >> 32), v_hi = static_cast<uint32_t>(vdesc >> 32);
+    const uint32_t k_lo = static_cast<uint32_t>(kdesc), v_lo = static_cast<uint32_t>(vdesc);
+    bool ok = ntiles == 0 || warp_wait(smem_u32(&ctrl->q_ready), 0);
+    auto issue_s = [&](int tile) {
+      if (lane == 0) {
+        const uint32_t kb_lo = k_lo + (((tile % kUmmaStages) * STAGE_BYTES) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = ((kk >> 2) * CHUNK_BYTES + (kk & 3) * 32) >> 4;
+          mma_ts_lohi(tmem + kSCol, tmem + kk * 8, kb_lo + off, k_hi, idesc_s, kk > 0);
+        }
+        mma_commit(smem_u32(&ctrl->s_full));
+      }
+      __syncwarp();
+    };
+    if (ok && ntiles > 0) {
+      ok = warp_wait(smem_u32(&ctrl->full[0]), 0);
+      if (ok) { tc_fence_after(); issue_s(0); }
+    }
+    for (int tile = 0; tile < ntiles && ok; ++tile) {
+      const int stage = tile % kUmmaStages;
+      ok = warp_wait(smem_u32(&ctrl->p_ready), tile & 1);
+      if (!ok) break;
+      const int valid = len - (t_begin + tile * kTileN);
+      if (valid < kTileN) {
+        // keys past the sequence end carry P == 0 but their V rows may hold anything: zero them so 0 * x stays 0
+        unsigned char* vbuf = smem + stage * STAGE_BYTES + TILE_BYTES;
+        const int first = valid > 0 ? valid : 0;
+        const int n16 = (kTileN - first) * 8;
+        for (int cc = 0; cc < CHUNKS; ++cc) {
+          uint4* dst = reinterpret_cast<uint4*>(vbuf + cc * CHUNK_BYTES + first * 128);
+          for (int i = lane; i < n16; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t vb_lo = v_lo + ((stage * STAGE_BYTES + TILE_BYTES) >> 4);
+#pragma unroll
+        for (int kk = 0; kk < kTileN / 16; ++kk)
+          mma_ts_lohi(tmem + kOCol, tmem + kSCol + kk * 8, vb_lo + ((kk * 16 * 128) >> 4), v_hi, idesc_o, (tile > 0 || kk > 0) ? 1u : 0u);
+        mma_commit(smem_u32(&ctrl->o_done));
+      }
+      __syncwarp();
+      if (tile + 1 < ntiles) {
+        ok = warp_wait(smem_u32(&ctrl->full[(tile + 1) % kUmmaStages]), ((tile + 1) / kUmmaStages) & 1);
+        if (!ok) break;
+        tc_fence_after();
+        issue_s(tile + 1);
+      }
+      // K_tile was read by S(tile) (complete: its P has come back) and V_tile by the PV just issued
+      if (lane == 0) mma_commit(smem_u32(&ctrl->empty[stage]));
+      __syncwarp();
+    }
+    if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
+  } else if (warp < active_warps) {
+    // =========================== softmax warps: thread = q row ===========================
+    const int row = tid;
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    // Q row -> TMEM as the packed 16-bit A operand (rows past R are zero)
+    {
+      const T* qg = static_cast<const T*>(p.q) +
+                    ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.group) * p.q_len) * D;
+#pragma unroll
+      for (int cc = 0; cc < kQCols / 32; ++cc) {
+        uint32_t qv[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          uint4 u = make_uint4(0u, 0u, 0u, 0u);
+          if (row < R) u = __ldg(reinterpret_cast<const uint4*>(qg + static_cast<long long>(row) * D) + cc * 8 + i);
+          qv[i * 4 + 0] = u.x; qv[i * 4 + 1] = u.y; qv[i * 4 + 2] = u.z; qv[i * 4 + 3] = u.w;
+        }
+        tmem_st32(tmem + lane_off + cc * 32, qv);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctrl->q_ready));
+    }
+    int lim = len - 1;                                   // last visible key of this row
+    if (p.causal) lim = len - p.q_len + (row % p.q_len);
+    const float sl2 = p.scale_log2;
+    const uint32_t tS = tmem + lane_off + kSCol;
+    const uint32_t tO = tmem + lane_off + kOCol;
+    bool ok = true;
+    for (int tile = 0; tile < ntiles; ++tile) {
+      ok = warp_wait(smem_u32(&ctrl->s_full), tile & 1);
+      if (!ok || *abort_flag) { ok = false; break; }
+      tc_fence_after();
+      const int limit = lim - (t_begin + tile * kTileN);   // columns 0..limit of this tile are visible
+      uint32_t ca[32], cb[32];
+      tmem_ld32(tS, ca);
+      tmem_ld32(tS + 32, cb);
+      tmem_wait_ld();
+      if (limit < kTileN - 1) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          if (i > limit) ca[i] = 0xff800000u;          // -inf
+          if (32 + i > limit) cb[i] = 0xff800000u;
+        }
+      }
+      float ma = max3(__uint_as_float(ca[0]), __uint_as_float(ca[1]), __uint_as_float(ca[2]));
+      float mb = max3(__uint_as_float(cb[0]), __uint_as_float(cb[1]), __uint_as_float(cb[2]));
+#pragma unroll
+      for (int i = 3; i + 1 < 32; i += 2) {
+        ma = max3(ma, __uint_as_float(ca[i]), __uint_as_float(ca[i + 1]));
+        mb = max3(mb, __uint_as_float(cb[i]), __uint_as_float(cb[i + 1]));
+      }
+      const float mx = max3(ma, mb, fmaxf(__uint_as_float(ca[31]), __uint_as_float(cb[31]))) * sl2;
+      const bool need = (mx - m_used) > 8.f;
+      float alpha = 1.f;
+      if (need) { alpha = fast_exp2(m_used - mx); m_used = mx; l_run *= alpha; }
+      if (tile > 0 && __any_sync(0xffffffffu, need)) {
+        // PV(tile-1) has completed once S(tile) is visible (MMAs complete in issue order); the wait is immediate
+        ok = warp_wait(smem_u32(&ctrl->o_done), (tile - 1) & 1);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int cc = 0; cc < D / 32; ++cc) {
+          uint32_t ov[32];
+          tmem_ld32(tO + cc * 32, ov);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          tmem_st32(tO + cc * 32, ov);
+        }
+      }
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+      float rs = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(ca[2 * i]), sl2, neg_m));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(ca[2 * i + 1]), sl2, neg_m));
+        const float p2 = fast_exp2(fmaf(__uint_as_float(cb[2 * i]), sl2, neg_m));
+        const float p3 = fast_exp2(fmaf(__uint_as_float(cb[2 * i + 1]), sl2, neg_m));
+        rs += (p0 + p1) + (p2 + p3);
+        pk[i] = ElemTraits<T>::pack2(p0, p1);
+        pk[16 + i] = ElemTraits<T>::pack2(p2, p3);
+      }
+      l_run += rs;
+      tmem_st32(tS, pk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(smem_u32(&ctrl->p_ready));
+    }
+    if (ok && ntiles > 0) ok = warp_wait(smem_u32(&ctrl->o_done), (ntiles - 1) & 1);
+    if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
+  }
+  __syncthreads();   // every tile consumed (or the CTA gave up): the stage ring is free for the row exchange
+  if (ctrl->abort_flag) {
+    if (warp == kMma) { tc_fence_after(); tmem_dealloc(tmem, kUmmaTmemCols); }
+    return;
+  }
+  // O rows (fp32, un-normalised) and (m, l) -> shared memory, then the common emit / ticket merge
+  float* comb_o = reinterpret_cast<float*>(smem);
+  float* comb_ml = comb_o + static_cast<size_t>(R) * D;
+  if (warp < active_warps) {
+    const int row = tid;
+    tc_fence_after();
+    const uint32_t tO = tmem + (static_cast<uint32_t>(warp * 32) << 16) + kOCol;
+#pragma unroll
+    for (int cc = 0; cc < D / 32; ++cc) {
+      uint32_t ov[32];
+      if (ntiles > 0) {
+        tmem_ld32(tO + cc * 32, ov);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ov[i] = 0u;
+      }
+      if (row < R) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          *reinterpret_cast<uint4*>(comb_o + static_cast<size_t>(row) * D + cc * 32 + i * 4) =
+              make_uint4(ov[i * 4], ov[i * 4 + 1], ov[i * 4 + 2], ov[i * 4 + 3]);
+      }
+    }
+    if (row < R) { comb_ml[row * 2] = m_used; comb_ml[row * 2 + 1] = l_run; }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMma) { tc_fence_after(); tmem_dealloc(tmem, kUmmaTmemCols); }
+  emit_and_merge<T, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, 1, R, &ctrl->ticket);
+}
+
+// ---------------------------------------------------------------------------
 // fp32 kernel: fp32 FMA dot products, one warp per q row, lanes split head_dim
 // ---------------------------------------------------------------------------
 template <int D>
@@ -789,6 +1144,38 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
     int rc = 0;
     if (D == 128) { rc = set_smem(decode_simt_kernel<128>, smem); if (rc) return rc; decode_simt_kernel<128><<<grid, 128, smem, stream>>>(p); }
     else          { rc = set_smem(decode_simt_kernel<64>, smem);  if (rc) return rc; decode_simt_kernel<64><<<grid, 128, smem, stream>>>(p); }
+  } else if (p.rows > 16) {
+    // many q rows per KV head: one 128-row tcgen05 tile with Q and P in tensor memory
+    CUtensorMap tk, tv;
+    int rc = 0;
+    int box = kTileN;
+    if (a.layout == B200ATTN_PAGED) {
+      box = 1;
+      while (box < kTileN && (a.page_size % (box * 2)) == 0) box *= 2;
+    }
+    p.box_shift = 0;
+    while ((1 << p.box_shift) < box) ++p.box_shift;
+    long long tokens;
+    int heads;
+    if (a.layout == B200ATTN_DENSE) { tokens = static_cast<long long>(a.batch) * a.kv_heads * a.max_kv; heads = 1; }
+    else { tokens = a.total_kv; heads = a.kv_heads; }
+    if ((rc = make_token_map(&tk, a.dtype, a.k, tokens, heads, D, box))) return rc;
+    if ((rc = make_token_map(&tv, a.dtype, a.v, tokens, heads, D, box))) return rc;
+    const size_t stage_bytes = static_cast<size_t>(kUmmaStages) * 2 * kTileN * D * 2;
+    const size_t comb_bytes = sizeof(float) * static_cast<size_t>(p.rows) * (D + 2);
+    const size_t smem = 1024 + std::max(stage_bytes, comb_bytes) + sizeof(UmmaCtrl);
+#define B200ATTN_LAUNCH_UMMA(TYPE, DIM)                                  \
+    do {                                                                 \
+      rc = set_smem(decode_umma_kernel<TYPE, DIM>, smem);                \
+      if (rc) return rc;                                                 \
+      decode_umma_kernel<TYPE, DIM><<<grid, 192, smem, stream>>>(tk, tv, p); \
+    } while (0)
+    if (a.dtype == B200ATTN_BF16) {
+      if (D == 128) B200ATTN_LAUNCH_UMMA(__nv_bfloat16, 128); else B200ATTN_LAUNCH_UMMA(__nv_bfloat16, 64);
+    } else {
+      if (D == 128) B200ATTN_LAUNCH_UMMA(__half, 128); else B200ATTN_LAUNCH_UMMA(__half, 64);
+    }
+#undef B200ATTN_LAUNCH_UMMA
   } else {
     const int nmt = p.n_mtiles;
     const int ksl = nmt <= 2 ? 4 : (nmt <= 4 ? 2 : 1);
