@@ -86,12 +86,13 @@ def c3_ragged_prefill(device, seed: int = 0, *, n_seqs: int = 16, lo: int = 128,
                       q_heads: int = 32, kv_heads: int = 8, head_dim: int = 128, dtype=torch.bfloat16,
                       shard: Tuple[int, int] = (0, 1), index_dtype=torch.int32, weak: bool = False) -> Workload:
     """Ragged varlen causal prefill.  Strong scaling: the n_seqs sequences are split over ranks by
-    balanced causal cost.  Weak scaling: every rank draws its own n_seqs sequences."""
+    balanced causal cost.  Weak scaling: every rank holds n_seqs sequences of the configuration's lengths with its
+    own values."""
     from kernels.attention import flash_attention_v2
 
     rank, world = shard
     if weak or world == 1:
-        lens = c3_lengths(seed + rank, n_seqs, lo, hi)
+        lens = c3_lengths(seed, n_seqs, lo, hi)      # weak scaling: every rank draws the same lengths, other values
     else:
         all_lens = c3_lengths(seed, n_seqs, lo, hi)
         lens = [all_lens[i] for i in balance_sequences(all_lens, world, causal_prefill=True)[rank]]
@@ -150,7 +151,7 @@ def c4_paged_decode(device, seed: int = 0, *, batch: int = 64, lo: int = 512, hi
 
     rank, world = shard
     if weak or world == 1:
-        lens = _lengths(seed + rank, batch, lo, hi)
+        lens = _lengths(seed, batch, lo, hi)         # weak scaling: every rank draws the same lengths, other values
     else:
         all_lens = _lengths(seed, batch, lo, hi)
         b0, b1 = contiguous_shard(batch, world, rank)
@@ -179,7 +180,7 @@ def c5_paged_spec_decode(device, seed: int = 0, *, batch: int = 32, drafts: int 
 
     rank, world = shard
     group = q_heads // kv_heads
-    ctx = _lengths(seed + (rank if weak else 0), batch, lo, hi)
+    ctx = _lengths(seed, batch, lo, hi)
     lens = [c + drafts for c in ctx]
     if weak or world == 1:
         my_heads = kv_heads
