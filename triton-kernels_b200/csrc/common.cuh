@@ -64,29 +64,6 @@ template <> struct ElemTraits<__nv_bfloat16> {
   __device__ static __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
   __device__ static __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
 };
-// packed 16-bit exp2: two results per MUFU operation, already in the format of P
-__device__ __forceinline__ uint32_t ex2_packed(uint32_t x, __half) {
-  uint32_t y;
-  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-__device__ __forceinline__ uint32_t ex2_packed(uint32_t x, __nv_bfloat16) {
-  uint32_t y;
-  asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(y) : "r"(x));
-  return y;
-}
-// the two fp32 values of a packed 16-bit pair (low element first)
-__device__ __forceinline__ void unpack16(uint32_t x, __nv_bfloat16, float& lo, float& hi) {
-  lo = __uint_as_float(x << 16);
-  hi = __uint_as_float(x & 0xffff0000u);
-}
-__device__ __forceinline__ void unpack16(uint32_t x, __half, float& lo, float& hi) {
-  const __half2 h = *reinterpret_cast<const __half2*>(&x);
-  const float2 f = __half22float2(h);
-  lo = f.x;
-  hi = f.y;
-}
-
 template <> struct ElemTraits<float> {
   static constexpr int kDtype = B200ATTN_F32;
   __device__ static __forceinline__ float to_float(float x) { return x; }

@@ -295,10 +295,10 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ok);
 }
 
-// kQRegs: keep the Q fragments in registers (one 16-row tile per warp, 4*D/16 registers); otherwise they are
-// re-read from shared memory at every k-step, which frees registers so that two CTAs fit on an SM.
+// The Q fragments are re-read from shared memory at every k-step instead of living in 4*D/16 registers per thread:
+// that keeps the kernel at 128 registers, so two or three CTAs share an SM.
 // NB: 16-key blocks a consumer warp handles per step (2 when a warp owns 32 or more keys of a stage).
-template <typename T, int D, bool kQRegs, int kStages, int NB, int kMaxThreads, int kMinBlocks>
+template <typename T, int D, int kStages, int NB, int kMaxThreads, int kMinBlocks>
 __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                          const __grid_constant__ CUtensorMap tm_v,
                                                          const DecodeParams p) {
@@ -446,16 +446,9 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
     }
   } else {
     // =========================== consumers ===========================
-    uint32_t qf[kQRegs ? KSTEPS : 1][4];
+    uint32_t qf[4];
     const int q_row = mt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
     const uint32_t q_rbase = q_s + q_row * ROW_BYTES;
-    if constexpr (kQRegs) {
-#pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) {
-        const int ch = kk * 2 + (lane >> 4);
-        ldmatrix_x4(qf[kk], q_rbase + ((ch ^ (q_row & 7)) << 4));
-      }
-    }
     int lim0 = len - 1, lim1 = len - 1;  // last visible key index for each of this lane's two rows
     if (p.causal) {
       lim0 = len - p.q_len + (r0 % p.q_len);
@@ -507,16 +500,14 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
 #pragma unroll
           for (int kk = 0; kk < KSTEPS; ++kk) {
             const int ch = kk * 2 + (mat & 1);   // 16-byte piece index along D
-            if constexpr (!kQRegs) {
-              const int qch = kk * 2 + (lane >> 4);
-              ldmatrix_x4(qf[0], q_rbase + ((qch ^ (q_row & 7)) << 4));
-            }
+            const int qch = kk * 2 + (lane >> 4);
+            ldmatrix_x4(qf, q_rbase + ((qch ^ (q_row & 7)) << 4));
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb) {
               uint32_t kb[4];
               ldmatrix_x4(kb, ks_base + swz_piece(roff[nb][ch >> 3], ch & 7));
-              mma_m16n8k16<T>(s[2 * nb], qf[kQRegs ? kk : 0], kb[0], kb[1]);
-              mma_m16n8k16<T>(s[2 * nb + 1], qf[kQRegs ? kk : 0], kb[2], kb[3]);
+              mma_m16n8k16<T>(s[2 * nb], qf, kb[0], kb[1]);
+              mma_m16n8k16<T>(s[2 * nb + 1], qf, kb[2], kb[3]);
             }
           }
         }
@@ -1205,18 +1196,18 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
       if ((rc = make_kv_rows_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box, rstride, D * 2ll))) return rc;
       if ((rc = make_kv_rows_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box, rstride, D * 2ll))) return rc;
     }
-#define B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, QREGS, STAGES, NBLK, MAXT, MINB)                                    \
+#define B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, STAGES, NBLK, MAXT, MINB)                                    \
     do {                                                                                                  \
-      rc = set_smem(decode_mma_kernel<TYPE, DIM, QREGS, STAGES, NBLK, MAXT, MINB>, smem);                       \
+      rc = set_smem(decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB>, smem);                       \
       if (rc) return rc;                                                                                  \
-      decode_mma_kernel<TYPE, DIM, QREGS, STAGES, NBLK, MAXT, MINB><<<grid, threads, smem, stream>>>(tk, tv, p);\
+      decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB><<<grid, threads, smem, stream>>>(tk, tv, p);\
     } while (0)
 #define B200ATTN_LAUNCH_DECODE(TYPE, DIM)                                                \
     do {                                                                                 \
-      if (threads <= 160) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 2, 1, 160, 3);      \
-      else if (threads <= 224) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 2, 224, 2); \
-      else if (ksl == 4) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 1, 288, 1);       \
-      else B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, false, 3, 2, 288, 1);                     \
+      if (threads <= 160) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 2, 1, 160, 3);      \
+      else if (threads <= 224) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 3, 2, 224, 2); \
+      else if (ksl == 4) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 3, 1, 288, 1);       \
+      else B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 3, 2, 288, 1);                     \
     } while (0)
     if (a.dtype == B200ATTN_BF16) {
       if (D == 128) B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 128); else B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 64);

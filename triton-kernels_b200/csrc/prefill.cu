@@ -47,21 +47,7 @@ constexpr int kThreads = 576;
 constexpr int kProducerWarp = 16;
 constexpr int kMmaWarp = 17;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
-// Of every 4 pairs of scores, this many are exponentiated on the FMA pipes (range reduction + cubic
-// polynomial, relative error 7.5e-5, far below the 16-bit rounding of P) instead of the MUFU unit,
-// which at 16 results per clock per SM is as scarce as the tensor pipe at head_dim 128.
-#ifndef B200ATTN_EXP_EMU_OF4
-#define B200ATTN_EXP_EMU_OF4 0
-#endif
-constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
-// P = exp2(t) evaluated directly in the 16-bit format of P (ex2.approx on bf16x2 / f16x2: two results per MUFU
-// operation, no separate conversion).  The argument t = s*scale*log2e - m is rounded to 16 bits first; entries near
-// the row max have |t| small and lose nothing, far entries lose relative accuracy where their weight is negligible
-// (measured on causal S=2048, D=128: max-abs error vs fp32 SDPA 7.5e-3 either way for bf16, 1.1e-3 vs 0.8e-3 for fp16).
-#ifndef B200ATTN_PACKED_EXP
-#define B200ATTN_PACKED_EXP 0
-#endif
-constexpr bool kPackedExp = B200ATTN_PACKED_EXP != 0;
+
 
 // Development aid (compiled out unless B200ATTN_TRACE is defined): CTA (0,0,0) stamps clock64 into the
 // workspace behind the header, one slot per (role, iteration, event).
@@ -658,37 +644,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const uint64_t t2 = fma_f2(pack_f2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), sl2_2, negm_2);
-            float p0, p1;
-            if constexpr (kPackedExp) {
-              float a, b;
-              unpack_f2(t2, a, b);
-              pk[i] = ex2_packed(ElemTraits<T>::pack2(a, b), T());
-              unpack16(pk[i], T(), p0, p1);
-              rs2 = add_f2(rs2, pack_f2(p0, p1));
-              continue;
-            }
-            if ((i & 3) < kExpEmuOf4) {
-              // 2^t = 2^n * 2^r with n = round(t), r in [-0.5, 0.5]; n is read off the magic-number sum
-              float a, b;
-              unpack_f2(t2, a, b);
-              const uint64_t tc = pack_f2(fmaxf(a, -126.f), fmaxf(b, -126.f));
-              const uint64_t tm = add_f2(tc, pack_f2(12582912.f, 12582912.f));
-              const uint64_t nf = add_f2(tm, pack_f2(-12582912.f, -12582912.f));
-              const uint64_t r = fma_f2(nf, pack_f2(-1.f, -1.f), tc);
-              uint64_t q = fma_f2(r, pack_f2(0.055171482f, 0.055171482f), pack_f2(0.2426109f, 0.2426109f));
-              q = fma_f2(q, r, pack_f2(0.69326097f, 0.69326097f));
-              q = fma_f2(q, r, pack_f2(0.99992812f, 0.99992812f));
-              float q0, q1, m0f, m1f;
-              unpack_f2(q, q0, q1);
-              unpack_f2(tm, m0f, m1f);
-              p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(m0f) << 23));
-              p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(m1f) << 23));
-            } else {
-              float a, b;
-              unpack_f2(t2, a, b);
-              p0 = fast_exp2(a);
-              p1 = fast_exp2(b);
-            }
+            float a, b;
+            unpack_f2(t2, a, b);
+            const float p0 = fast_exp2(a), p1 = fast_exp2(b);
             rs2 = add_f2(rs2, pack_f2(p0, p1));
             pk[i] = ElemTraits<T>::pack2(p0, p1);
           }

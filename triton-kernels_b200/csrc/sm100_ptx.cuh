@@ -51,9 +51,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
 }
-__device__ __forceinline__ void named_barrier_sync(uint32_t id, uint32_t nthreads) {
-  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory");
-}
 
 // ------------------------------ TMA ------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
