@@ -1,0 +1,107 @@
+"""Edge cases the reference never exercises: empty sequences, very many short sequences (device-side planner and
+work search beyond one warp / one thread block of sequences), lengths around tile and chunk boundaries."""
+import pytest
+import torch
+
+from helpers import assert_close_both
+from oracle import sdpa_ref
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rand(gen, shape, dtype=torch.bfloat16):
+    return torch.randn(shape, generator=gen).to(dtype).to(DEV)
+
+
+def test_decode_many_short_sequences_and_empty_ones():
+    from kernels.decode import decode_attention
+
+    gen = torch.Generator().manual_seed(21)
+    B, QH, KVH, D = 1500, 8, 2, 64
+    lens = torch.randint(0, 41, (B,), generator=gen).tolist()
+    lens[0] = 0
+    lens[-1] = 0
+    qs = [_rand(gen, (QH, D)) for _ in range(B)]
+    ks = [_rand(gen, (n, KVH, D)) for n in lens]
+    vs = [_rand(gen, (n, KVH, D)) for n in lens]
+    k, ip = sdpa_ref.pack_ragged(ks)
+    v, _ = sdpa_ref.pack_ragged(vs)
+    out = decode_attention(torch.stack(qs), k, v, kv_indptr=ip)
+    assert torch.isfinite(out.float()).all()
+    live = [i for i in range(B) if lens[i] > 0]
+    refs = sdpa_ref.decode_reference([qs[i] for i in live], [ks[i] for i in live], [vs[i] for i in live], QH, KVH)
+    got = out[live].float().cpu()
+    torch.testing.assert_close(got, torch.stack(refs).cpu(), atol=2e-2, rtol=2e-2)
+    assert (out[[0, B - 1]] == 0).all()      # empty sequences: defined as zeros here (0/0 in the reference)
+
+
+def test_prefill_many_short_sequences_and_empty_ones():
+    from kernels.attention import flash_attention_v2
+
+    gen = torch.Generator().manual_seed(22)
+    B, QH, KVH, D = 300, 8, 2, 64
+    lens = torch.randint(0, 50, (B,), generator=gen).tolist()
+    lens[3] = 0
+    lens[150] = 300
+    qs = [_rand(gen, (n, QH, D)) for n in lens]
+    ks = [_rand(gen, (n, KVH, D)) for n in lens]
+    vs = [_rand(gen, (n, KVH, D)) for n in lens]
+    q, ip = sdpa_ref.pack_ragged(qs, torch.int64)
+    k, _ = sdpa_ref.pack_ragged(ks, torch.int64)
+    v, _ = sdpa_ref.pack_ragged(vs, torch.int64)
+    out = flash_attention_v2(q, k, v, is_causal=True, q_indptr=ip, kv_indptr=ip)
+    assert torch.isfinite(out.float()).all()
+    live = [i for i in range(B) if lens[i] > 0]
+    refs = sdpa_ref.prefill_reference([qs[i] for i in live], [ks[i] for i in live], [vs[i] for i in live], QH, KVH, True)
+    torch.testing.assert_close(out.float().cpu(), torch.cat(refs).cpu(), atol=2e-2, rtol=2e-2)
+
+
+def test_prefill_queries_without_keys_give_zeros():
+    from kernels.attention import flash_attention_v2
+
+    gen = torch.Generator().manual_seed(23)
+    q = _rand(gen, (40, 8, 64))
+    k = _rand(gen, (17, 2, 64))
+    v = _rand(gen, (17, 2, 64))
+    qi = torch.tensor([0, 25, 40], dtype=torch.int32, device=DEV)
+    ki = torch.tensor([0, 0, 17], dtype=torch.int32, device=DEV)   # first sequence has no keys
+    out = flash_attention_v2(q, k, v, q_indptr=qi, kv_indptr=ki)
+    assert (out[:25] == 0).all()
+    ref = sdpa_ref.prefill_reference([q[25:]], [k], [v], 8, 2, False)[0]
+    assert_close_both(out[25:], ref, torch.bfloat16, 17)
+
+
+@pytest.mark.parametrize("n", [63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257])
+def test_lengths_around_tile_boundaries(n):
+    from kernels.attention import flash_attention_v2
+    from kernels.decode import decode_attention
+    from kernels.speculative_decode import speculative_decode_attention
+
+    gen = torch.Generator().manual_seed(100 + n)
+    QH, KVH, D = 8, 2, 128
+    q = _rand(gen, (1, QH, n, D))
+    k = _rand(gen, (1, KVH, n, D))
+    v = _rand(gen, (1, KVH, n, D))
+    ref = sdpa_ref.prefill_reference([q[0].transpose(0, 1)], [k[0].transpose(0, 1)], [v[0].transpose(0, 1)], QH, KVH, True)[0]
+    assert_close_both(flash_attention_v2(q, k, v, is_causal=True)[0].transpose(0, 1), ref, torch.bfloat16, n, "prefill")
+    qd = _rand(gen, (1, QH, D))
+    refd = sdpa_ref.decode_reference([qd[0]], [k[0].transpose(0, 1)], [v[0].transpose(0, 1)], QH, KVH)[0]
+    assert_close_both(decode_attention(qd, k, v)[0], refd, torch.bfloat16, n, "decode")
+    qs = _rand(gen, (1, QH, 7, D))   # 28 rows per KV head: tcgen05 decode path
+    refs = sdpa_ref.spec_decode_reference([qs[0]], [k[0].transpose(0, 1)], [v[0].transpose(0, 1)], QH, KVH, True)[0]
+    assert_close_both(speculative_decode_attention(qs, k, v, causal=True)[0], refs, torch.bfloat16, n, "spec")
+
+
+def test_decode_chunk_boundaries_long_sequence():
+    """One long sequence splits into many chunks; lengths one below / at / above a multiple of the chunk size."""
+    from kernels.decode import decode_attention
+
+    gen = torch.Generator().manual_seed(31)
+    QH, KVH, D = 32, 8, 128
+    for n in (8191, 8192, 8193):
+        q = _rand(gen, (1, QH, D))
+        k = _rand(gen, (1, KVH, n, D))
+        v = _rand(gen, (1, KVH, n, D))
+        ref = sdpa_ref.decode_reference([q[0]], [k[0].transpose(0, 1)], [v[0].transpose(0, 1)], QH, KVH)[0]
+        assert_close_both(decode_attention(q, k, v)[0], ref, torch.bfloat16, n, f"n={n}")
