@@ -47,14 +47,25 @@ constexpr int kThreads = 576;
 constexpr int kProducerWarp = 16;
 constexpr int kMmaWarp = 17;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+// Of every 4 pairs of scores, this many are exponentiated on the FMA pipes (range reduction + cubic
+// polynomial, relative error 7.5e-5, far below the 16-bit rounding of P) instead of the MUFU unit,
+// which at 16 results per clock per SM is as scarce as the tensor pipe at head_dim 128.
+#ifndef B200ATTN_EXP_EMU_OF4
+#define B200ATTN_EXP_EMU_OF4 0
+#endif
+constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
 
 
 // Development aid (compiled out unless B200ATTN_TRACE is defined): CTA (0,0,0) stamps clock64 into the
 // workspace behind the header, one slot per (role, iteration, event).
 #ifdef B200ATTN_TRACE
 #define TRACE_AT(idx) do { if (trace_on) p.header[64 + (idx)] = static_cast<int>(clock64() - trace_t0); } while (0)
+// per-CTA summary (lane 0 of the MMA warp): global timer stamps in ns and counters
+#define TRACE_CTA(slot, val) do { if (lane == 0) p.header[64 + 8192 + blockIdx.x * 8 + (slot)] = static_cast<int>(val); } while (0)
+__device__ __forceinline__ unsigned long long trace_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
 #else
 #define TRACE_AT(idx) do { } while (0)
+#define TRACE_CTA(slot, val) do { } while (0)
 #endif
 
 // Everything one work item needs; decoded once by the scheduler warp.  An item is two 128-row query tiles
@@ -414,42 +425,34 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // (start address >> 4) plus small constants, so issuing one MMA costs the single thread a few adds.
     const uint64_t kdesc = make_smem_desc_sw128(smem_base, 16);                    // K-major operands (Q, K)
     const uint64_t vdesc = make_smem_desc_sw128(smem_base, Plan::kChunkBytes);     // MN-major operand (V)
-    const uint32_t k_hi = static_cast<uint32_t>(kdesc >> 32), v_hi = static_cast<uint32_t>(vdesc >> 32);
-    const uint32_t k_lo = static_cast<uint32_t>(kdesc), v_lo = static_cast<uint32_t>(vdesc);
     int ring_base = 0;            // ring entry of K_0 of the current item
     int tiles_done[kSlots] = {0, 0};  // score tiles issued per slot so far (barrier phases run across items)
+    bool pre_issued[kSlots] = {false, false};   // first score tile of the coming item already issued
     auto ring_full_wait = [&](int e) -> bool {
       return warp_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
     };
+    // The warp stays converged while it issues: every lane runs the descriptor arithmetic, one elected lane
+    // issues the tensor-core instructions and their commits.
+    const uint32_t lead = elect_one();
     auto issue_s = [&](int s, int e_k) {
       // S_s = Q_s K^T : K-major A and B, D/16 k-steps
-      if (lane == 0) {
-        const uint32_t qa_lo = k_lo + ((Plan::kQOff + s * Plan::kTileBytes) >> 4);
-        const uint32_t kb_lo = k_lo + ((Plan::kRingOff + (e_k % kRing) * Plan::kTileBytes) >> 4);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = ((kk >> 2) * Plan::kChunkBytes + (kk & 3) * 32) >> 4;
-          mma_ss_lohi(tmem_S[s], qa_lo + off, k_hi, kb_lo + off, k_hi, idesc_s, kk > 0);
-        }
-        mma_commit(smem_u32(&ctrl->s_full[s]));
-      }
-      __syncwarp();
+      const uint64_t qa = kdesc + static_cast<uint64_t>((Plan::kQOff + s * Plan::kTileBytes) >> 4);
+      const uint64_t kb = kdesc + static_cast<uint64_t>((Plan::kRingOff + (e_k % kRing) * Plan::kTileBytes) >> 4);
+      mma_ss_batch<D / 16>(tmem_S[s], qa, kb, idesc_s, 0u, lead);
+      mma_commit_lead(smem_u32(&ctrl->s_full[s]), lead);
     };
     auto issue_pv = [&](int s, int e_v, bool first) {
       // O_s (+)= P_s V : A = packed 16-bit P in TMEM, B = V, MN-major.  P of columns 0-63 sits in TMEM columns
       // 0-31 of the S tile and P of columns 64-127 in TMEM columns 64-95 (each warpgroup writes over its own half).
-      if (lane == 0) {
-        const uint32_t vb_lo = v_lo + ((Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes) >> 4);
-#pragma unroll
-        for (int kk = 0; kk < kBN / 16; ++kk) {
-          mma_ts_lohi(tmem_O[s], tmem_S[s] + (kk >> 2) * kHalf + (kk & 3) * 8, vb_lo + ((kk * 16 * 128) >> 4), v_hi, idesc_o,
-                      (!first || kk > 0) ? 1u : 0u);
-        }
-        mma_commit(smem_u32(&ctrl->o_done[s]));
-      }
-      __syncwarp();
+      const uint64_t vb = vdesc + static_cast<uint64_t>((Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes) >> 4);
+      mma_ts_batch8(tmem_O[s], tmem_S[s], vb, idesc_o, first ? 0u : 1u, lead);
+      mma_commit_lead(smem_u32(&ctrl->o_done[s]), lead);
     };
 
+#ifdef B200ATTN_TRACE
+    TRACE_CTA(0, trace_gtime() & 0x7fffffff);
+    int trace_items = 0, trace_iters = 0;
+#endif
     for (int k = 0; ok; ++k) {
       TRACE_AT(3328 + (k & 31) * 8 + 0);
       ok = warp_wait(smem_u32(&ctrl->sched_full[k & 1]), (k >> 1) & 1);
@@ -466,19 +469,41 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!ok) break;
         TRACE_AT(3328 + (k & 31) * 8 + 3);
         tc_fence_after();
-        for (int s = 0; s < kSlots; ++s) if (w.nkv[s] > 0) issue_s(s, ring_base);
+        // (slots whose first score tile was already issued while the previous item finished are skipped)
+        for (int s = 0; s < kSlots; ++s) if (w.nkv[s] > 0 && !pre_issued[s]) issue_s(s, ring_base);
         TRACE_AT(3328 + (k & 31) * 8 + 4);
-        if (lane == 0) {
-          mma_commit(smem_u32(&ctrl->kv_empty[ring_base % kRing]));
-          if (w.nkv_max == 1) mma_commit(smem_u32(&ctrl->q_empty));
-        }
-        __syncwarp();
-      } else if (lane == 0) {
-        mma_commit(smem_u32(&ctrl->q_empty));
+#ifdef B200ATTN_TRACE
+        if (k == 0) TRACE_CTA(1, trace_gtime() & 0x7fffffff);
+        ++trace_items; trace_iters += w.nkv_max;
+#endif
+        mma_commit_lead(smem_u32(&ctrl->kv_empty[ring_base % kRing]), lead);
+        if (w.nkv_max == 1) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
+      } else {
+        mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
       }
+      pre_issued[0] = pre_issued[1] = false;
       for (int j = 0; j < w.nkv_max && ok; ++j) {
         bool v_ready = false;
         const int e_v = ring_base + 2 * j + 1;
+        const bool last_iter = j + 1 == w.nkv_max;
+        // On the last tile of the item the first score tiles of the next item are issued right behind the final
+        // PVs, so the softmax warps find them complete when they return from the epilogue.  Everything waited
+        // for here (next item published, its Q and first K tile loaded) depends only on work this warp has
+        // already issued: Q may be replaced once the last score MMAs of this item, issued one tile ago, complete.
+        int next_state = 0;            // 0 = not looked at yet, 1 = ready, -1 = nothing to issue ahead
+        ItemWork wn;
+        auto prepare_next = [&]() -> bool {
+          if (next_state != 0) return true;
+          next_state = -1;
+          if (!warp_wait(smem_u32(&ctrl->sched_full[(k + 1) & 1]), ((k + 1) >> 1) & 1)) return false;
+          if (ctrl->sched_item[(k + 1) & 1] < 0) return true;
+          wn = ctrl->sched_work[(k + 1) & 1];
+          if (wn.nkv_max == 0) return true;
+          if (!warp_wait(smem_u32(&ctrl->q_full), (k + 1) & 1)) return false;
+          if (!ring_full_wait(ring_base + 2 * w.nkv_max)) return false;
+          next_state = 1;
+          return true;
+        };
         for (int s = 0; s < kSlots && ok; ++s) {
           if (j >= w.nkv[s]) continue;
           TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 0);
@@ -522,18 +547,33 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           ++tiles_done[s];
         }
         if (!ok) break;
-        if (lane == 0) {
-          mma_commit(smem_u32(&ctrl->kv_empty[e_v % kRing]));
-          if (j + 1 < w.nkv_max) mma_commit(smem_u32(&ctrl->kv_empty[(e_v + 1) % kRing]));
-          // the last score MMAs of the item have been issued: Q may be replaced once they complete
-          if (j + 2 == w.nkv_max) mma_commit(smem_u32(&ctrl->q_empty));
+        if (last_iter) {
+          // (behind the final PVs of both slots: the epilogues wait for those)
+          ok = prepare_next();
+          if (!ok) break;
+          if (next_state == 1) {
+            for (int s = 0; s < kSlots; ++s) {
+              if (pre_issued[s] || wn.nkv[s] == 0) continue;
+              tc_fence_after();
+              issue_s(s, ring_base + 2 * w.nkv_max);
+              pre_issued[s] = true;
+            }
+          }
         }
-        __syncwarp();
+        mma_commit_lead(smem_u32(&ctrl->kv_empty[e_v % kRing]), lead);
+        if (j + 1 < w.nkv_max) mma_commit_lead(smem_u32(&ctrl->kv_empty[(e_v + 1) % kRing]), lead);
+        // the last score MMAs of the item have been issued: Q may be replaced once they complete
+        if (j + 2 == w.nkv_max) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
       }
       ring_base += 2 * w.nkv_max;
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));
       __syncwarp();
     }
+#ifdef B200ATTN_TRACE
+    TRACE_CTA(2, trace_gtime() & 0x7fffffff);
+    TRACE_CTA(3, trace_items);
+    TRACE_CTA(4, trace_iters);
+#endif
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
   } else if (warp < kSoftmaxWarps) {
     // =========================== softmax warpgroups ===========================
@@ -644,9 +684,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             const uint64_t t2 = fma_f2(pack_f2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), sl2_2, negm_2);
-            float a, b;
-            unpack_f2(t2, a, b);
-            const float p0 = fast_exp2(a), p1 = fast_exp2(b);
+            float p0, p1;
+            if ((i & 3) < kExpEmuOf4) {
+              // 2^t = 2^n * 2^r with n = round(t), r in [-0.5, 0.5]; n is read off the magic-number sum
+              float a, b;
+              unpack_f2(t2, a, b);
+              const uint64_t tc = pack_f2(fmaxf(a, -126.f), fmaxf(b, -126.f));
+              const uint64_t tm = add_f2(tc, pack_f2(12582912.f, 12582912.f));
+              const uint64_t nf = add_f2(tm, pack_f2(-12582912.f, -12582912.f));
+              const uint64_t r = fma_f2(nf, pack_f2(-1.f, -1.f), tc);
+              uint64_t q = fma_f2(r, pack_f2(0.055171482f, 0.055171482f), pack_f2(0.2426109f, 0.2426109f));
+              q = fma_f2(q, r, pack_f2(0.69326097f, 0.69326097f));
+              q = fma_f2(q, r, pack_f2(0.99992812f, 0.99992812f));
+              float q0, q1, m0f, m1f;
+              unpack_f2(q, q0, q1);
+              unpack_f2(tm, m0f, m1f);
+              p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(m0f) << 23));
+              p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(m1f) << 23));
+            } else {
+              float a, b;
+              unpack_f2(t2, a, b);
+              p0 = fast_exp2(a);
+              p1 = fast_exp2(b);
+            }
             rs2 = add_f2(rs2, pack_f2(p0, p1));
             pk[i] = ElemTraits<T>::pack2(p0, p1);
           }
@@ -666,17 +726,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       // ---------------- epilogue of the item ----------------
       if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 0);
-      if (n > 0) {
-        ok = warp_wait(smem_u32(&ctrl->o_done[s]), (tile_cnt - 1) & 1);
-        if (!ok) break;
-      }
-      // total row sum = this thread's partial + its partner's
+      // total row sum = this thread's partial + its partner's (exchanged while the last PV is still running)
       ctrl->xchg[xchg_cnt & 1][s][half][row] = l;
       mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
       ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), xchg_cnt & 1);
       if (!ok) break;
       l += ctrl->xchg[xchg_cnt & 1][s][half ^ 1][row];
       ++xchg_cnt;
+      if (n > 0) {
+        ok = warp_wait(smem_u32(&ctrl->o_done[s]), (tile_cnt - 1) & 1);
+        if (!ok) break;
+      }
       tc_fence_after();
       if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 1);
       const bool slot_live = w.valid && m0s < w.len_q;
@@ -706,23 +766,38 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (lane == 0) mbar_arrive(smem_u32(&ctrl->o_free[s]));
         }
         if (row < rows_valid) {
+          // one thread writes 32 consecutive output columns of its row; 32-byte stores (one full sector per lane)
+          // when the output pointer allows, since the rows of a warp never share a 128-byte line
           if constexpr (std::is_same<OutT, float>::value) {
             float* out = static_cast<float*>(p.out) + off + c * 32;
+            if (p.out_align32) {
 #pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4)
-              *reinterpret_cast<float4*>(out + q4 * 4) =
-                  make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
-                              __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
+              for (int q8 = 0; q8 < 4; ++q8) {
+                uint32_t u[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) u[i] = __float_as_uint(__uint_as_float(ov[q8 * 8 + i]) * inv);
+                st_global_v8(out + q8 * 8, u);
+              }
+            } else {
+#pragma unroll
+              for (int q4 = 0; q4 < 8; ++q4)
+                *reinterpret_cast<float4*>(out + q4 * 4) =
+                    make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
+                                __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
+            }
           } else {
             T* out = static_cast<T*>(p.out) + off + c * 32;
+            uint32_t u[16];
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              uint4 u;
-              u.x = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 0]) * inv, __uint_as_float(ov[q4 * 8 + 1]) * inv);
-              u.y = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 2]) * inv, __uint_as_float(ov[q4 * 8 + 3]) * inv);
-              u.z = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 4]) * inv, __uint_as_float(ov[q4 * 8 + 5]) * inv);
-              u.w = ElemTraits<T>::pack2(__uint_as_float(ov[q4 * 8 + 6]) * inv, __uint_as_float(ov[q4 * 8 + 7]) * inv);
-              *reinterpret_cast<uint4*>(out + q4 * 8) = u;
+            for (int i = 0; i < 16; ++i)
+              u[i] = ElemTraits<T>::pack2(__uint_as_float(ov[2 * i]) * inv, __uint_as_float(ov[2 * i + 1]) * inv);
+            if (p.out_align32) {
+              st_global_v8(out, u);
+              st_global_v8(out + 16, u + 8);
+            } else {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4)
+                *reinterpret_cast<uint4*>(out + q4 * 8) = make_uint4(u[q4 * 4], u[q4 * 4 + 1], u[q4 * 4 + 2], u[q4 * 4 + 3]);
             }
           }
         }
@@ -815,6 +890,7 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
   p.num_pages = 0;
   p.is_causal = a.is_causal ? 1 : 0;
   p.head_pair = (p.group % 2 == 0) ? 1 : 0;
+  p.out_align32 = (reinterpret_cast<uintptr_t>(a.out) & 31) == 0 ? 1 : 0;
   const int item_rows = p.head_pair ? kBM : 2 * kBM;
   const int head_units = p.head_pair ? a.q_heads / 2 : a.q_heads;
   p.scale_log2 = a.sm_scale * 1.4426950408889634f;

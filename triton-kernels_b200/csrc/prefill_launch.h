@@ -30,6 +30,7 @@ struct PrefillParams {
   int box_rows;         // tokens per TMA box of a paged cache
   int num_pages;
   int is_causal;
+  int out_align32;      // the output pointer is 32-byte aligned: the epilogue may use 32-byte stores
   int head_pair;        // 1: the two slots of a work item are two q heads of one KV head over the same 128 rows
   float scale_log2;
 };

@@ -227,6 +227,81 @@ __device__ __forceinline__ void mma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, ui
       : "memory");
 }
 
+// 32-byte global store (address 32-byte aligned)
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t* v) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"l"(ptr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
+               "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Batched issue.  The whole (converged) warp executes these; only the lane whose `lead` is non-zero issues the
+// tensor-core instructions.  Keeping the warp converged lets the descriptor arithmetic run once per warp instead
+// of on a divergent single-lane path, which matters when the other warps of the SM sub-partition are busy: a
+// divergent issuer was measured to fall to a sixth of the tensor-core rate under an FMA-bound neighbour, the
+// converged form to about two thirds.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t r;
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\tselp.b32 %0, 1, 0, q;\n\t}\n" : "=r"(r));
+  return r;
+}
+
+#define B200ATTN_SS_STEP(OFF)                                                                   \
+  "add.s64 a1, %1, " #OFF ";\n\tadd.s64 b1, %2, " #OFF ";\n\t"                                  \
+  "@e tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, t;\n\t"
+
+// D/16 k-steps of a K-major x K-major product whose operands are 128-row, 128-byte-swizzled tiles stored as
+// 64-element column blocks of 16 KiB: k-step kk starts (kk / 4) * 16 KiB + (kk % 4) * 32 bytes into both tiles.
+template <int KSTEPS>
+__device__ __forceinline__ void mma_ss_batch(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate_first, uint32_t lead) {
+  static_assert(KSTEPS == 4 || KSTEPS == 8, "head dimension 64 or 128");
+  if constexpr (KSTEPS == 8) {
+    asm volatile(
+        "{\n\t.reg .pred p, t, e;\n\t.reg .b64 a1, b1;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, 0, 0;\n\tsetp.ne.b32 e, %5, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        B200ATTN_SS_STEP(2) B200ATTN_SS_STEP(4) B200ATTN_SS_STEP(6)
+        B200ATTN_SS_STEP(1024) B200ATTN_SS_STEP(1026) B200ATTN_SS_STEP(1028) B200ATTN_SS_STEP(1030)
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(lead) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p, t, e;\n\t.reg .b64 a1, b1;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, 0, 0;\n\tsetp.ne.b32 e, %5, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        B200ATTN_SS_STEP(2) B200ATTN_SS_STEP(4) B200ATTN_SS_STEP(6)
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(lead) : "memory");
+  }
+}
+#undef B200ATTN_SS_STEP
+
+#define B200ATTN_TS_STEP(AOFF, BOFF)                                                            \
+  "add.u32 a1, %1, " #AOFF ";\n\tadd.s64 b1, %2, " #BOFF ";\n\t"                                \
+  "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, t;\n\t"
+
+// Eight k-steps (128 keys) of O += P V: A is packed 16-bit P in tensor memory, keys 0-63 in columns [0,32) and
+// keys 64-127 in columns [64,96) of `a_tmem`; B is an MN-major 128-row V tile, 16 rows (2 KiB) per k-step.
+__device__ __forceinline__ void mma_ts_batch8(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate_first, uint32_t lead) {
+  asm volatile(
+      "{\n\t.reg .pred p, t, e;\n\t.reg .b32 a1;\n\t.reg .b64 b1;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, 0, 0;\n\tsetp.ne.b32 e, %5, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      B200ATTN_TS_STEP(8, 128) B200ATTN_TS_STEP(16, 256) B200ATTN_TS_STEP(24, 384)
+      B200ATTN_TS_STEP(64, 512) B200ATTN_TS_STEP(72, 640) B200ATTN_TS_STEP(80, 768) B200ATTN_TS_STEP(88, 896)
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(lead) : "memory");
+}
+#undef B200ATTN_TS_STEP
+
+// tcgen05.commit issued by the lane whose `lead` is non-zero (warp converged)
+__device__ __forceinline__ void mma_commit_lead(uint32_t bar, uint32_t lead) {
+  asm volatile(
+      "{\n\t.reg .pred e;\n\tsetp.ne.b32 e, %1, 0;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(bar), "r"(lead)
+      : "memory");
+}
+
 // mbarrier arrives once every tcgen05 operation this thread issued so far has completed
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
