@@ -141,6 +141,11 @@ int b200attn_abi_version(void);
 const char* b200attn_last_error(void);
 int b200attn_device_info(int device, b200attn_device_info_t* info);
 
+/*
+ * Workspace rules (all entry points): the caller zero-fills the workspace once after allocating it and then
+ * leaves its first 256 bytes (error word, scheduling counters that every launch returns to zero) alone; one
+ * workspace serves one stream at a time.
+ */
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args_t* args);
 size_t b200attn_decode_workspace_bytes(const b200attn_decode_args_t* args);
 

@@ -51,7 +51,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 // polynomial, relative error 7.5e-5, far below the 16-bit rounding of P) instead of the MUFU unit,
 // which at 16 results per clock per SM is as scarce as the tensor pipe at head_dim 128.
 #ifndef B200ATTN_EXP_EMU_OF4
-#define B200ATTN_EXP_EMU_OF4 0
+#define B200ATTN_EXP_EMU_OF4 1
 #endif
 constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
 
@@ -305,7 +305,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       int item = -1;
       if (lane == 0) {
-        item = atomicAdd(p.work_counter, 1);
+        // the first item of a CTA is its own index (the grid never exceeds the item count); later ones are drawn
+        item = k == 0 ? static_cast<int>(blockIdx.x) : static_cast<int>(gridDim.x) + atomicAdd(p.work_counter, 1);
         if (item >= p.total_items) item = -1;
       }
       item = __shfl_sync(0xffffffffu, item, 0);
@@ -413,6 +414,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // drain: wait (bounded) for the copies still in flight before the CTA may exit
       for (int e = max(ring_lo, ring_e - kRing); e < ring_e; ++e) mbar_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
     }
+    if (lane == 0) {
+      // This CTA draws no more items.  The last CTA to get here puts both counters back to zero for the next
+      // launch on this workspace (every other CTA's draws are ordered before its own increment by the fence).
+      __threadfence();
+      if (atomicAdd(p.work_counter + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+        atomicExch(p.work_counter, 0);
+        atomicExch(p.work_counter + 1, 0);
+      }
+    }
   } else if (warp == kMmaWarp) {
     // =========================== MMA issuer ===========================
     constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
@@ -486,8 +496,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         bool v_ready = false;
         const int e_v = ring_base + 2 * j + 1;
         const bool last_iter = j + 1 == w.nkv_max;
-        // On the last tile of the item the first score tiles of the next item are issued right behind the final
-        // PVs, so the softmax warps find them complete when they return from the epilogue.  Everything waited
+        // On the last tile of the item the first score tile of the next item is issued right behind each slot's
+        // final PV, so the softmax warps can carry straight on.  Everything waited
         // for here (next item published, its Q and first K tile loaded) depends only on work this warp has
         // already issued: Q may be replaced once the last score MMAs of this item, issued one tile ago, complete.
         int next_state = 0;            // 0 = not looked at yet, 1 = ready, -1 = nothing to issue ahead
@@ -542,13 +552,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (!ok) break;
             tc_fence_after();
             issue_s(s, e_v + 1);
+          } else if (last_iter) {
+            ok = prepare_next();
+            if (!ok) break;
+            if (next_state == 1 && wn.nkv[s] > 0) {
+              tc_fence_after();
+              issue_s(s, ring_base + 2 * w.nkv_max);
+              pre_issued[s] = true;
+            }
           }
           TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 3);
           ++tiles_done[s];
         }
         if (!ok) break;
         if (last_iter) {
-          // (behind the final PVs of both slots: the epilogues wait for those)
+          // a slot that ran out of tiles earlier in this item gets its head start here
           ok = prepare_next();
           if (!ok) break;
           if (next_state == 1) {
@@ -593,15 +611,207 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     int tile_cnt = 0;     // score tiles of this slot consumed so far (barrier phases run across items)
     int xchg_cnt = 0;     // exchanges done so far
     bool ok = true;
+    // The epilogue of an item is finished lazily: O is read out of tensor memory at the end of the first score
+    // tile of the slot's next item (its PV is the first thing that overwrites O) and the global stores are issued
+    // after that tile's P has been handed over, so they drain while the tensor cores work on it.
+    bool pend = false;        // an item's output is still in tensor memory
+    bool pend_acc = false;    // ... and it has an accumulator (false: the slot had no keys, the output is zero)
+    int pend_phase = 0;       // o_done phase of its last PV
+    int pend_rows = 0;        // rows of the tile that exist in the sequence
+    float pend_l = 0.f;       // row sum
+    long long pend_off = 0;   // element offset of this thread's first output column
+    constexpr bool kStoreLate = !std::is_same<OutT, float>::value;   // 16-bit output fits in registers meanwhile
+    auto store_row = [&](int c, const uint32_t (&ov)[32], float inv) {
+      // fp32 output: written straight from the accumulator chunk
+      float* out = static_cast<float*>(p.out) + pend_off + c * 32;
+      if (p.out_align32) {
+#pragma unroll
+        for (int q8 = 0; q8 < 4; ++q8) {
+          uint32_t u[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) u[i] = __float_as_uint(__uint_as_float(ov[q8 * 8 + i]) * inv);
+          st_global_v8(out + q8 * 8, u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
+        }
+      } else {
+#pragma unroll
+        for (int q4 = 0; q4 < 8; ++q4)
+          *reinterpret_cast<float4*>(out + q4 * 4) =
+              make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
+                          __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
+      }
+    };
+    // 4 x 4 transpose of two-word items across the four threads of a quad (lane bits 0-1): on return item m of
+    // thread q is what item q of thread m was.  x[2m], x[2m+1] are the words of item m.
+    auto quad_transpose = [&](uint32_t (&x)[8]) {
+      const bool b1 = (lane & 2) != 0, b0 = (lane & 1) != 0;
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+#pragma unroll
+        for (int wd = 0; wd < 2; ++wd) {
+          uint32_t& lo = x[2 * m + wd];
+          uint32_t& hi = x[2 * (m + 2) + wd];
+          const uint32_t recv = __shfl_xor_sync(0xffffffffu, b1 ? lo : hi, 2);
+          if (b1) lo = recv; else hi = recv;
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < 4; m += 2) {
+#pragma unroll
+        for (int wd = 0; wd < 2; ++wd) {
+          uint32_t& lo = x[2 * m + wd];
+          uint32_t& hi = x[2 * (m + 1) + wd];
+          const uint32_t recv = __shfl_xor_sync(0xffffffffu, b0 ? lo : hi, 1);
+          if (b0) lo = recv; else hi = recv;
+        }
+      }
+    };
+    // 16-bit output at head_dim 128: this thread's 64 columns of a row are exactly one 128-byte line, so the
+    // accumulator is read in the 16x256b layout (a quad holds 8 consecutive columns), transposed inside each quad
+    // and stored as full lines, 8 rows per store instruction instead of one 32-byte piece of 32 different lines.
+    constexpr bool kLineStores = kStoreLate && D == 128;
+    auto flush = [&](bool hand_over) -> bool {
+      if (pend_acc) {
+        if (!warp_wait(smem_u32(&ctrl->o_done[s]), pend_phase)) return false;
+      }
+      tc_fence_after();
+      const float inv = pend_l > 0.f ? 1.f / pend_l : 0.f;
+      if constexpr (kLineStores) {
+        uint32_t line[2][2][8];     // [16-row half][row r / row r + 8][32 bytes of the row's line]
+        const int rq = lane >> 2, q = lane & 3;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t v[32];
+          if (pend_acc) {
+            tmem_ld_16x256b_x8(tOh + (static_cast<uint32_t>(16 * h) << 16), v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          if (h == 1) {
+            // O has been read out: the MMA warp may start the next item's PV into it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->o_free[s]));
+          }
+          const float inv_a = __shfl_sync(0xffffffffu, inv, rq + 16 * h);
+          const float inv_b = __shfl_sync(0xffffffffu, inv, rq + 16 * h + 8);
+          uint32_t a[8], b[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            a[i] = ElemTraits<T>::pack2(__uint_as_float(v[4 * i]) * inv_a, __uint_as_float(v[4 * i + 1]) * inv_a);
+            b[i] = ElemTraits<T>::pack2(__uint_as_float(v[4 * i + 2]) * inv_b, __uint_as_float(v[4 * i + 3]) * inv_b);
+          }
+          // thread q of the quad holds word q of each 16-byte block i; it ends up with blocks 2q and 2q+1 whole
+          quad_transpose(a);
+          quad_transpose(b);
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            line[h][0][m] = a[2 * m];  line[h][0][4 + m] = a[2 * m + 1];
+            line[h][1][m] = b[2 * m];  line[h][1][4 + m] = b[2 * m + 1];
+          }
+        }
+        if (hand_over) {
+          // this tile's P goes to the MMA warp before the stores are issued
+          tc_fence_before();
+          mbar_arrive(smem_u32(&ctrl->p_ready[s]));
+        }
+        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 3);
+        const long long row_stride = p.layout == B200ATTN_RAGGED ? static_cast<long long>(p.q_heads) * D : D;
+        const int warp_row0 = (warp & 3) * 32;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int ab = 0; ab < 2; ++ab) {
+            const int r = warp_row0 + rq + 16 * h + 8 * ab;     // row of the slot this thread now stores a piece of
+            if (r < pend_rows) {
+              T* out = static_cast<T*>(p.out) + pend_off + (r - row) * row_stride + q * 16;
+              const uint32_t (&u)[8] = line[h][ab];
+              if (p.out_align32) {
+                st_global_v8(out, u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
+              } else {
+                *reinterpret_cast<uint4*>(out) = make_uint4(u[0], u[1], u[2], u[3]);
+                *reinterpret_cast<uint4*>(out + 8) = make_uint4(u[4], u[5], u[6], u[7]);
+              }
+            }
+          }
+        }
+        pend = false;
+        return true;
+      }
+      uint32_t outp[kStoreLate ? kOCols / 2 : 1];
+#pragma unroll
+      for (int c = 0; c < kOCols / 32; ++c) {
+        uint32_t ov[32];
+        if (pend_acc) {
+          tmem_ld32(tOh + c * 32, ov);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        if (c == kOCols / 32 - 1) {
+          // O has been read out: the MMA warp may start the next item's PV into it
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&ctrl->o_free[s]));
+        }
+        if constexpr (kStoreLate) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            outp[c * 16 + i] = ElemTraits<T>::pack2(__uint_as_float(ov[2 * i]) * inv, __uint_as_float(ov[2 * i + 1]) * inv);
+        } else {
+          if (row < pend_rows) store_row(c, ov, inv);
+        }
+      }
+      if (hand_over) {
+        // this tile's P goes to the MMA warp before the stores are issued
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctrl->p_ready[s]));
+      }
+      // one thread writes consecutive output columns of its row; 32-byte stores (one full sector per lane) when
+      // the output pointer allows, since the rows of a warp never share a 128-byte line
+      if constexpr (kStoreLate) {
+        if (row < pend_rows) {
+          T* out = static_cast<T*>(p.out) + pend_off;
+#pragma unroll
+          for (int c = 0; c < kOCols / 32; ++c) {
+            if (p.out_align32) {
+#pragma unroll
+              for (int h8 = 0; h8 < 2; ++h8) {
+                const int b = c * 16 + h8 * 8;
+                st_global_v8(out + c * 32 + h8 * 16, outp[b], outp[b + 1], outp[b + 2], outp[b + 3], outp[b + 4], outp[b + 5],
+                             outp[b + 6], outp[b + 7]);
+              }
+            } else {
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4)
+                *reinterpret_cast<uint4*>(out + c * 32 + q4 * 8) =
+                    make_uint4(outp[c * 16 + q4 * 4], outp[c * 16 + q4 * 4 + 1], outp[c * 16 + q4 * 4 + 2], outp[c * 16 + q4 * 4 + 3]);
+            }
+          }
+        }
+      }
+      pend = false;
+      return true;
+    };
     for (int k = 0; ok; ++k) {
       ok = warp_wait(smem_u32(&ctrl->sched_full[k & 1]), (k >> 1) & 1);
       if (!ok || *abort_flag) { ok = false; break; }
       const int item = ctrl->sched_item[k & 1];
       if (item < 0) break;
-      const ItemWork w = ctrl->sched_work[k & 1];
-      const int n = s == 0 ? w.nkv[0] : w.nkv[1];
-      const int m0s = s == 0 ? w.m0[0] : w.m0[1];
+      // (the few fields needed are read from shared memory where they are used, not held across the tile loop)
+      if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 7);
+      const ItemWork& w = ctrl->sched_work[k & 1];
+      const int n = w.nkv[s];
+      const int m0s = w.m0[s];
+      const int len_k = w.len_k;
       const int row_abs = m0s + row;                    // query index inside the sequence
+      if (pend && n == 0) {
+        // no score tile in this item to hang the previous item's epilogue on
+        ok = flush(false);
+        if (!ok) break;
+      }
       float m_used = -INFINITY;   // exponent reference currently baked into O and l
       float l = 0.f;              // partial row sum over this thread's columns
       for (int j = 0; j < n; ++j, ++tile_cnt) {
@@ -611,7 +821,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after();
         if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 1);
         // masking is needed only on the tile that holds the sequence end or the causal diagonal
-        int limit = w.len_k - 1 - j * kBN - half * kHalf;
+        int limit = len_k - 1 - j * kBN - half * kHalf;
         if (p.is_causal) limit = min(limit, row_abs - j * kBN - half * kHalf);
         const bool masked = limit < kHalf - 1;
         float mx;
@@ -719,93 +929,44 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         l += rs0 + rs1;
         if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 5);
         tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(smem_u32(&ctrl->p_ready[s]));
+        if (pend) {
+          // first tile of an item: the previous item's O must leave tensor memory before this tile's PV
+          ok = flush(true);
+          if (!ok) break;
+        } else {
+          tc_fence_before();
+          mbar_arrive(smem_u32(&ctrl->p_ready[s]));
+        }
         if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 6);
       }
       if (!ok) break;
-      // ---------------- epilogue of the item ----------------
+      // ---------------- the item's epilogue becomes pending ----------------
       if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 0);
-      // total row sum = this thread's partial + its partner's (exchanged while the last PV is still running)
+      // total row sum = this thread's partial + its partner's
       ctrl->xchg[xchg_cnt & 1][s][half][row] = l;
       mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
       ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), xchg_cnt & 1);
       if (!ok) break;
       l += ctrl->xchg[xchg_cnt & 1][s][half ^ 1][row];
       ++xchg_cnt;
-      if (n > 0) {
-        ok = warp_wait(smem_u32(&ctrl->o_done[s]), (tile_cnt - 1) & 1);
-        if (!ok) break;
-      }
-      tc_fence_after();
       if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 1);
-      const bool slot_live = w.valid && m0s < w.len_q;
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      const int rows_valid = slot_live ? min(kBM, w.len_q - m0s) : 0;
-      long long off;
-      const long long qrow0 = s == 0 ? w.q_row0[0] : w.q_row0[1];
-      const int qhead = s == 0 ? w.q_head[0] : w.q_head[1];
-      if (p.layout == B200ATTN_RAGGED) off = ((qrow0 + m0s + row) * p.q_heads + qhead) * D;
-      else off = (qrow0 + m0s + row) * D;
-      off += half * kOCols;
-      // every thread writes its own half row: 32 contiguous output columns per TMEM chunk
-#pragma unroll
-      for (int c = 0; c < kOCols / 32; ++c) {
-        uint32_t ov[32];
-        if (n > 0) {
-          tmem_ld32(tOh + c * 32, ov);
-          tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = 0u;
-        }
-        if (c == kOCols / 32 - 1) {
-          // O has been read out: the MMA warp may start the next item's PV into it
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&ctrl->o_free[s]));
-        }
-        if (row < rows_valid) {
-          // one thread writes 32 consecutive output columns of its row; 32-byte stores (one full sector per lane)
-          // when the output pointer allows, since the rows of a warp never share a 128-byte line
-          if constexpr (std::is_same<OutT, float>::value) {
-            float* out = static_cast<float*>(p.out) + off + c * 32;
-            if (p.out_align32) {
-#pragma unroll
-              for (int q8 = 0; q8 < 4; ++q8) {
-                uint32_t u[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) u[i] = __float_as_uint(__uint_as_float(ov[q8 * 8 + i]) * inv);
-                st_global_v8(out + q8 * 8, u);
-              }
-            } else {
-#pragma unroll
-              for (int q4 = 0; q4 < 8; ++q4)
-                *reinterpret_cast<float4*>(out + q4 * 4) =
-                    make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
-                                __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
-            }
-          } else {
-            T* out = static_cast<T*>(p.out) + off + c * 32;
-            uint32_t u[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i)
-              u[i] = ElemTraits<T>::pack2(__uint_as_float(ov[2 * i]) * inv, __uint_as_float(ov[2 * i + 1]) * inv);
-            if (p.out_align32) {
-              st_global_v8(out, u);
-              st_global_v8(out + 16, u + 8);
-            } else {
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4)
-                *reinterpret_cast<uint4*>(out + q4 * 8) = make_uint4(u[q4 * 4], u[q4 * 4 + 1], u[q4 * 4 + 2], u[q4 * 4 + 3]);
-            }
-          }
-        }
-      }
+      const int len_q = w.len_q;
+      const bool slot_live = w.valid && m0s < len_q;
+      const long long qrow0 = w.q_row0[s];
+      const int qhead = w.q_head[s];
+      pend = true;
+      pend_acc = n > 0;
+      pend_phase = (tile_cnt - 1) & 1;
+      pend_rows = slot_live ? min(kBM, len_q - m0s) : 0;
+      pend_l = l;
+      if (p.layout == B200ATTN_RAGGED) pend_off = ((qrow0 + m0s + row) * p.q_heads + qhead) * D;
+      else pend_off = (qrow0 + m0s + row) * D;
+      pend_off += half * kOCols;
       __syncwarp();
       if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 2);
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));
     }
+    if (ok && pend) ok = flush(false);
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
   }
 
@@ -927,9 +1088,8 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
   if (total_items > 0x7fffffff) { set_error("prefill: too many work items"); return B200ATTN_E_UNSUPPORTED; }
   p.total_items = static_cast<int>(total_items);
   grid = dim3(static_cast<unsigned>(std::min<long long>(total_items, sm_count)), 1, 1);
-  // the work counter of the persistent kernel starts from zero on every launch
-  cudaError_t me = cudaMemsetAsync(p.work_counter, 0, sizeof(int), stream);
-  if (me != cudaSuccess) return cuda_fail(me, "cudaMemsetAsync(work counter)");
+  // The two counters in the header (next item, CTAs finished) are zero here: the workspace starts zeroed and
+  // the last CTA of every launch puts them back.
 
   cudaError_t e;
 #define B200ATTN_LAUNCH_PREFILL(TYPE, DIM, OUT)                                                          \

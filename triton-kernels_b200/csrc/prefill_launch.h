@@ -15,7 +15,7 @@ struct PrefillParams {
   const int* k_table;
   const int* v_table;
   int* header;          // workspace header, word 0 = device error code
-  int* work_counter;    // workspace header word 8: next work item of the persistent kernel
+  int* work_counter;    // workspace header words 8, 9: items drawn beyond the first of each CTA; CTAs finished
   int total_items;
   long long table_stride;
   int layout;

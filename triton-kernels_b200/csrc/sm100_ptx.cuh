@@ -108,6 +108,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// 16 lanes x 64 consecutive 32-bit columns in the 16x256b register layout: thread t of the warp receives, for
+// every group i of 8 columns, r[4i], r[4i+1] = lane (base_lane + t / 4), columns 8i + 2 (t % 4) + {0, 1} and
+// r[4i+2], r[4i+3] = the same columns of lane (base_lane + t / 4 + 8).  Four neighbouring threads thus hold 8
+// consecutive columns of a row, which is what a coalesced row-major store needs.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -228,9 +244,10 @@ __device__ __forceinline__ void mma_ts_lohi(uint32_t d_tmem, uint32_t a_tmem, ui
 }
 
 // 32-byte global store (address 32-byte aligned)
-__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t* v) {
-  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"l"(ptr), "r"(v[0]), "r"(v[1]), "r"(v[2]),
-               "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+__device__ __forceinline__ void st_global_v8(void* ptr, uint32_t v0, uint32_t v1, uint32_t v2, uint32_t v3, uint32_t v4,
+                                             uint32_t v5, uint32_t v6, uint32_t v7) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"l"(ptr), "r"(v0), "r"(v1), "r"(v2), "r"(v3),
+               "r"(v4), "r"(v5), "r"(v6), "r"(v7)
                : "memory");
 }
 
