@@ -444,17 +444,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // The warp stays converged while it issues: every lane runs the descriptor arithmetic, one elected lane
     // issues the tensor-core instructions and their commits.
     const uint32_t lead = elect_one();
-    auto issue_s = [&](int s, int e_k) {
+    auto k_desc_of = [&](int e_k) -> uint64_t {
+      return kdesc + static_cast<uint64_t>((Plan::kRingOff + (e_k % kRing) * Plan::kTileBytes) >> 4);
+    };
+    auto issue_s = [&](int s, uint64_t kb) {
       // S_s = Q_s K^T : K-major A and B, D/16 k-steps
       const uint64_t qa = kdesc + static_cast<uint64_t>((Plan::kQOff + s * Plan::kTileBytes) >> 4);
-      const uint64_t kb = kdesc + static_cast<uint64_t>((Plan::kRingOff + (e_k % kRing) * Plan::kTileBytes) >> 4);
       mma_ss_batch<D / 16>(tmem_S[s], qa, kb, idesc_s, 0u, lead);
       mma_commit_lead(smem_u32(&ctrl->s_full[s]), lead);
     };
-    auto issue_pv = [&](int s, int e_v, bool first) {
+    auto issue_pv = [&](int s, uint64_t vb, bool first) {
       // O_s (+)= P_s V : A = packed 16-bit P in TMEM, B = V, MN-major.  P of columns 0-63 sits in TMEM columns
       // 0-31 of the S tile and P of columns 64-127 in TMEM columns 64-95 (each warpgroup writes over its own half).
-      const uint64_t vb = vdesc + static_cast<uint64_t>((Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes) >> 4);
       mma_ts_batch8(tmem_O[s], tmem_S[s], vb, idesc_o, first ? 0u : 1u, lead);
       mma_commit_lead(smem_u32(&ctrl->o_done[s]), lead);
     };
@@ -480,7 +481,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         TRACE_AT(3328 + (k & 31) * 8 + 3);
         tc_fence_after();
         // (slots whose first score tile was already issued while the previous item finished are skipped)
-        for (int s = 0; s < kSlots; ++s) if (w.nkv[s] > 0 && !pre_issued[s]) issue_s(s, ring_base);
+        for (int s = 0; s < kSlots; ++s) if (w.nkv[s] > 0 && !pre_issued[s]) issue_s(s, k_desc_of(ring_base));
         TRACE_AT(3328 + (k & 31) * 8 + 4);
 #ifdef B200ATTN_TRACE
         if (k == 0) TRACE_CTA(1, trace_gtime() & 0x7fffffff);
@@ -493,7 +494,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       pre_issued[0] = pre_issued[1] = false;
       for (int j = 0; j < w.nkv_max && ok; ++j) {
-        bool v_ready = false;
         const int e_v = ring_base + 2 * j + 1;
         const bool last_iter = j + 1 == w.nkv_max;
         // On the last tile of the item the first score tile of the next item is issued right behind each slot's
@@ -514,52 +514,58 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           next_state = 1;
           return true;
         };
+        // Everything that does not depend on the softmax warps is waited for and computed before their P is: V_j
+        // and K_{j+1} (in steady state loaded long ago), the operand descriptors, and on the last tile the next
+        // item.  Between a slot's P and its two batches of MMAs the warp then only runs the issue itself.
+        ok = ring_full_wait(e_v);
+        if (!ok) break;
+        {
+          const int valid = w.len_k - j * kBN;
+          if (valid < kBN) {
+            // keys past the sequence end carry P == 0 but their V rows may hold anything (stale
+            // shared memory, the next sequence, poisoned page tails): zero them so 0 * x stays 0
+            unsigned char* vbuf = smem + Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes;
+            const int first = valid > 0 ? valid : 0;
+            const int n16 = (kBN - first) * 8;  // 16-byte pieces per column block
+            for (int c = 0; c < Plan::kChunks; ++c) {
+              uint4* dst = reinterpret_cast<uint4*>(vbuf + c * Plan::kChunkBytes + first * 128);
+              for (int i = lane; i < n16; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+        }
+        int e_next = -1;              // ring entry of the K tile the score MMAs issued in this iteration read
+        if (!last_iter) {
+          e_next = e_v + 1;
+          ok = ring_full_wait(e_next);
+          if (!ok) break;
+        } else {
+          ok = prepare_next();
+          if (!ok) break;
+          if (next_state == 1) e_next = ring_base + 2 * w.nkv_max;
+        }
+        const uint64_t vb = vdesc + static_cast<uint64_t>((Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes) >> 4);
+        const uint64_t kb = kdesc + static_cast<uint64_t>((Plan::kRingOff + ((e_next < 0 ? 0 : e_next) % kRing) * Plan::kTileBytes) >> 4);
         for (int s = 0; s < kSlots && ok; ++s) {
           if (j >= w.nkv[s]) continue;
+          const bool s_next = last_iter ? (next_state == 1 && wn.nkv[s] > 0) : (j + 1 < w.nkv[s]);
+          if (j == 0 && k > 0) {
+            // the first PV of an item overwrites O: the epilogue of the previous item must have read it out
+            // (the softmax warps do that just before they hand over this tile's P)
+            ok = warp_wait(smem_u32(&ctrl->o_free[s]), (k - 1) & 1);
+            if (!ok) break;
+          }
           TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 0);
           ok = warp_wait(smem_u32(&ctrl->p_ready[s]), tiles_done[s] & 1);
           if (!ok) break;
           TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 1);
-          if (!v_ready) {
-            ok = ring_full_wait(e_v);
-            if (!ok) break;
-            v_ready = true;
-            const int valid = w.len_k - j * kBN;
-            if (valid < kBN) {
-              // keys past the sequence end carry P == 0 but their V rows may hold anything (stale
-              // shared memory, the next sequence, poisoned page tails): zero them so 0 * x stays 0
-              unsigned char* vbuf = smem + Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes;
-              const int first = valid > 0 ? valid : 0;
-              const int n16 = (kBN - first) * 8;  // 16-byte pieces per column block
-              for (int c = 0; c < Plan::kChunks; ++c) {
-                uint4* dst = reinterpret_cast<uint4*>(vbuf + c * Plan::kChunkBytes + first * 128);
-                for (int i = lane; i < n16; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-              }
-              fence_proxy_async_smem();
-              __syncwarp();
-            }
-          }
-          if (j == 0 && k > 0) {
-            // the first PV of an item overwrites O: the epilogue of the previous item must have read it out
-            ok = warp_wait(smem_u32(&ctrl->o_free[s]), (k - 1) & 1);
-            if (!ok) break;
-          }
           tc_fence_after();
-          issue_pv(s, e_v, j == 0);
+          issue_pv(s, vb, j == 0);
           TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 2);
-          if (j + 1 < w.nkv[s]) {
-            ok = ring_full_wait(e_v + 1);
-            if (!ok) break;
-            tc_fence_after();
-            issue_s(s, e_v + 1);
-          } else if (last_iter) {
-            ok = prepare_next();
-            if (!ok) break;
-            if (next_state == 1 && wn.nkv[s] > 0) {
-              tc_fence_after();
-              issue_s(s, ring_base + 2 * w.nkv_max);
-              pre_issued[s] = true;
-            }
+          if (s_next) {
+            issue_s(s, kb);
+            if (last_iter) pre_issued[s] = true;
           }
           TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 3);
           ++tiles_done[s];
@@ -573,7 +579,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int s = 0; s < kSlots; ++s) {
               if (pre_issued[s] || wn.nkv[s] == 0) continue;
               tc_fence_after();
-              issue_s(s, ring_base + 2 * w.nkv_max);
+              issue_s(s, kb);
               pre_issued[s] = true;
             }
           }
