@@ -784,20 +784,15 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     constexpr uint32_t idesc_o = make_idesc_f16(128, D, kFmt, 1);
     const uint64_t kdesc = make_smem_desc_sw128(smem_base, 16);
     const uint64_t vdesc = make_smem_desc_sw128(smem_base, CHUNK_BYTES);
-    const uint32_t k_hi = static_cast<uint32_t>(kdesc >> 32), v_hi = static_cast<uint32_t>(vdesc >> 32);
-    const uint32_t k_lo = static_cast<uint32_t>(kdesc), v_lo = static_cast<uint32_t>(vdesc);
     bool ok = ntiles == 0 || warp_wait(smem_u32(&ctrl->q_ready), 0);
+    // The warp stays converged while it issues (every lane runs the descriptor arithmetic, one elected lane issues
+    // the tensor-core instructions and their commits): a divergent single-lane issuer loses most of its issue slots
+    // to busy neighbouring warps.
+    const uint32_t lead = elect_one();
     auto issue_s = [&](int tile) {
-      if (lane == 0) {
-        const uint32_t kb_lo = k_lo + (((tile % kUmmaStages) * STAGE_BYTES) >> 4);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = ((kk >> 2) * CHUNK_BYTES + (kk & 3) * 32) >> 4;
-          mma_ts_lohi(tmem + kSCol, tmem + kk * 8, kb_lo + off, k_hi, idesc_s, kk > 0);
-        }
-        mma_commit(smem_u32(&ctrl->s_full));
-      }
-      __syncwarp();
+      const uint64_t kb = kdesc + static_cast<uint64_t>(((tile % kUmmaStages) * STAGE_BYTES) >> 4);
+      mma_ts_kmajor_batch<D / 16, (CHUNK_BYTES >> 4)>(tmem + kSCol, tmem, kb, idesc_s, 0u, lead);
+      mma_commit_lead(smem_u32(&ctrl->s_full), lead);
     };
     if (ok && ntiles > 0) {
       ok = warp_wait(smem_u32(&ctrl->full[0]), 0);
@@ -805,11 +800,16 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     }
     for (int tile = 0; tile < ntiles && ok; ++tile) {
       const int stage = tile % kUmmaStages;
-      ok = warp_wait(smem_u32(&ctrl->p_ready), tile & 1);
-      if (!ok) break;
+      // what does not depend on the softmax warps comes before the wait for their P: the next K tile (loaded long
+      // ago in steady state), the zero fill of V rows past the end, the operand descriptor
+      if (tile + 1 < ntiles) {
+        ok = warp_wait(smem_u32(&ctrl->full[(tile + 1) % kUmmaStages]), ((tile + 1) / kUmmaStages) & 1);
+        if (!ok) break;
+      }
       const int valid = len - (t_begin + tile * kTileN);
       if (valid < kTileN) {
         // keys past the sequence end carry P == 0 but their V rows may hold anything: zero them so 0 * x stays 0
+        // (the stage is complete: its K half was consumed by S(tile))
         unsigned char* vbuf = smem + stage * STAGE_BYTES + TILE_BYTES;
         const int first = valid > 0 ? valid : 0;
         const int n16 = (kTileN - first) * 8;
@@ -820,24 +820,15 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
         fence_proxy_async_smem();
         __syncwarp();
       }
+      const uint64_t vb = vdesc + static_cast<uint64_t>((stage * STAGE_BYTES + TILE_BYTES) >> 4);
+      ok = warp_wait(smem_u32(&ctrl->p_ready), tile & 1);
+      if (!ok) break;
       tc_fence_after();
-      if (lane == 0) {
-        const uint32_t vb_lo = v_lo + ((stage * STAGE_BYTES + TILE_BYTES) >> 4);
-#pragma unroll
-        for (int kk = 0; kk < kTileN / 16; ++kk)
-          mma_ts_lohi(tmem + kOCol, tmem + kSCol + kk * 8, vb_lo + ((kk * 16 * 128) >> 4), v_hi, idesc_o, (tile > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(smem_u32(&ctrl->o_done));
-      }
-      __syncwarp();
-      if (tile + 1 < ntiles) {
-        ok = warp_wait(smem_u32(&ctrl->full[(tile + 1) % kUmmaStages]), ((tile + 1) / kUmmaStages) & 1);
-        if (!ok) break;
-        tc_fence_after();
-        issue_s(tile + 1);
-      }
+      mma_ts_batch4(tmem + kOCol, tmem + kSCol, vb, idesc_o, tile > 0 ? 1u : 0u, lead);
+      mma_commit_lead(smem_u32(&ctrl->o_done), lead);
+      if (tile + 1 < ntiles) issue_s(tile + 1);
       // K_tile was read by S(tile) (complete: its P has come back) and V_tile by the PV just issued
-      if (lane == 0) mma_commit(smem_u32(&ctrl->empty[stage]));
-      __syncwarp();
+      mma_commit_lead(smem_u32(&ctrl->empty[stage]), lead);
     }
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
   } else if (warp < active_warps) {

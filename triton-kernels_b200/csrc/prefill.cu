@@ -3,22 +3,23 @@
 //
 // Replaces the reference's partial + merge launch pair (kernels/attention.py:430-746).
 //
-// One CTA owns two 128-row query tiles of one (sequence, q head) ("slots").
-// Warp roles (384 threads):
-//   warps 0-3  : softmax warpgroup of slot 0 (thread i owns query row i)
-//   warps 4-7  : softmax warpgroup of slot 1
-//   warp  8    : TMA producer (Q once, then K_j / V_j tiles of 128 keys through a 4-buffer ring;
-//                paged caches are fetched one page-sized box at a time from the block table)
-//   warp  9    : tcgen05.mma issuer (lane 0) and TMEM owner
+// Persistent kernel, one CTA per SM.  A work item is two 128-row query tiles ("slots") that share a KV head.
+// Warp roles (576 threads):
+//   warps 0-15 : four softmax warpgroups, (slot 0 | slot 1) x (score columns 0-63 | 64-127); thread i of a
+//                warpgroup owns query row i of its slot and 64 of the row's 128 scores
+//   warp  16   : scheduler + TMA producer (draws work items, loads Q, then K_j / V_j tiles of 128 keys through a
+//                4-buffer ring; paged caches are fetched one page-sized box at a time from the block table)
+//   warp  17   : tcgen05.mma issuer and TMEM owner; the warp stays converged, one elected lane issues
 // TMEM (512 columns): S0 | S1 | O0 | O1.  Per KV tile j and slot s:
 //   S_s = Q_s K_j^T   (SS MMA, 128x128xD)            -> commit s_full[s]
-//   softmax WG s reads S_s (one row per thread), masks, keeps a running max / sum in the exp2
-//   domain, rescales O_s in TMEM only when the max moved by more than 2^8, writes P_s as
-//   packed 16-bit into the first 64 columns of S_s                -> arrive p_ready[s]
+//   the slot's warpgroups read S_s, mask, keep a running max / sum in the exp2 domain (the two threads of a row
+//   agree on the max through shared memory), rescale O_s in TMEM only when the max moved by more than 2^8, and
+//   write P_s as packed 16-bit over part of S_s                      -> arrive p_ready[s]
 //   O_s += P_s V_j    (TS MMA, A from TMEM, V is the MN-major B operand) -> commit o_done[s]
-// The two slots are interleaved so that one slot's softmax overlaps the other's MMAs.
-// The epilogue normalises O by the row sum, stages it in the (now dead) Q buffer and
-// writes rows < seq_len_q with coalesced 16-byte stores.
+// The two slots are interleaved so that one slot's softmax overlaps the other's MMAs.  At the end of an item the
+// MMA warp issues the first score tile of the next item behind the last PVs, and the softmax warps finish the old
+// item's epilogue lazily: O is normalised and read out at the end of the next item's first tile and stored while
+// the tensor cores work on that tile.
 //
 // Every mbarrier wait is bounded; on expiry the role records DEV_ERR_WAIT_EXPIRED
 // in the workspace header and falls through to the common teardown (TMEM is freed).
@@ -535,6 +536,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             __syncwarp();
           }
         }
+        bool v_released = false;
         int e_next = -1;              // ring entry of the K tile the score MMAs issued in this iteration read
         if (!last_iter) {
           e_next = e_v + 1;
@@ -562,6 +564,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 1);
           tc_fence_after();
           issue_pv(s, vb, j == 0);
+          // V_j may be refilled once the PVs of every slot that reads it have completed: commit behind the last one
+          if (s == kSlots - 1 || j >= w.nkv[kSlots - 1]) { mma_commit_lead(smem_u32(&ctrl->kv_empty[e_v % kRing]), lead); v_released = true; }
           TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 2);
           if (s_next) {
             issue_s(s, kb);
@@ -584,7 +588,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
           }
         }
-        mma_commit_lead(smem_u32(&ctrl->kv_empty[e_v % kRing]), lead);
+        if (!v_released) mma_commit_lead(smem_u32(&ctrl->kv_empty[e_v % kRing]), lead);
         if (j + 1 < w.nkv_max) mma_commit_lead(smem_u32(&ctrl->kv_empty[(e_v + 1) % kRing]), lead);
         // the last score MMAs of the item have been issued: Q may be replaced once they complete
         if (j + 2 == w.nkv_max) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);

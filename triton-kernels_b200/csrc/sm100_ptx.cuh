@@ -311,6 +311,48 @@ __device__ __forceinline__ void mma_ts_batch8(uint32_t d_tmem, uint32_t a_tmem, 
 }
 #undef B200ATTN_TS_STEP
 
+#define B200ATTN_TSK_STEP(AOFF, BOPND)                                                          \
+  "add.u32 a1, %1, " #AOFF ";\n\tadd.s64 b1, %2, " BOPND ";\n\t"                                \
+  "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, t;\n\t"
+
+// KSTEPS k-steps of S = Q K^T with Q as packed 16-bit in tensor memory (8 columns per k-step) and K a K-major,
+// 128-byte-swizzled tile stored as 64-element column blocks of CHUNK16 * 16 bytes.
+template <int KSTEPS, int CHUNK16>
+__device__ __forceinline__ void mma_ts_kmajor_batch(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                    uint32_t accumulate_first, uint32_t lead) {
+  static_assert(KSTEPS == 4 || KSTEPS == 8, "head dimension 64 or 128");
+  if constexpr (KSTEPS == 8) {
+    asm volatile(
+        "{\n\t.reg .pred p, t, e;\n\t.reg .b32 a1;\n\t.reg .b64 b1;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, 0, 0;\n\tsetp.ne.b32 e, %5, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        B200ATTN_TSK_STEP(8, "2") B200ATTN_TSK_STEP(16, "4") B200ATTN_TSK_STEP(24, "6")
+        B200ATTN_TSK_STEP(32, "%6") B200ATTN_TSK_STEP(40, "%7") B200ATTN_TSK_STEP(48, "%8") B200ATTN_TSK_STEP(56, "%9")
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(lead),
+        "n"(CHUNK16), "n"(CHUNK16 + 2), "n"(CHUNK16 + 4), "n"(CHUNK16 + 6) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p, t, e;\n\t.reg .b32 a1;\n\t.reg .b64 b1;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, 0, 0;\n\tsetp.ne.b32 e, %5, 0;\n\t"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        B200ATTN_TSK_STEP(8, "2") B200ATTN_TSK_STEP(16, "4") B200ATTN_TSK_STEP(24, "6")
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(lead) : "memory");
+  }
+}
+
+// Four k-steps (64 keys) of O += P V: A is packed 16-bit P in 32 tensor-memory columns at `a_tmem`; B is 64 rows
+// of an MN-major V tile, 16 rows (2 KiB) per k-step.
+__device__ __forceinline__ void mma_ts_batch4(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate_first, uint32_t lead) {
+  asm volatile(
+      "{\n\t.reg .pred p, t, e;\n\t.reg .b32 a1;\n\t.reg .b64 b1;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, 0, 0;\n\tsetp.ne.b32 e, %5, 0;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      B200ATTN_TSK_STEP(8, "128") B200ATTN_TSK_STEP(16, "256") B200ATTN_TSK_STEP(24, "384")
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(lead) : "memory");
+}
+#undef B200ATTN_TSK_STEP
+
 // tcgen05.commit issued by the lane whose `lead` is non-zero (warp converged)
 __device__ __forceinline__ void mma_commit_lead(uint32_t bar, uint32_t lead) {
   asm volatile(
