@@ -437,8 +437,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint64_t kdesc = make_smem_desc_sw128(smem_base, 16);                    // K-major operands (Q, K)
     const uint64_t vdesc = make_smem_desc_sw128(smem_base, Plan::kChunkBytes);     // MN-major operand (V)
     int ring_base = 0;            // ring entry of K_0 of the current item
-    int tiles_done[kSlots] = {0, 0};  // score tiles issued per slot so far (barrier phases run across items)
-    bool pre_issued[kSlots] = {false, false};   // first score tile of the coming item already issued
+    // per-slot state as scalars (an array indexed by the slot would live in local memory)
+    int tiles_done0 = 0, tiles_done1 = 0;       // score tiles issued per slot so far (barrier phases run across items)
+    bool pre_issued0 = false, pre_issued1 = false;   // first score tile of the coming item already issued
     auto ring_full_wait = [&](int e) -> bool {
       return warp_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
     };
@@ -471,47 +472,51 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok || *abort_flag) { ok = false; break; }
       const int item = ctrl->sched_item[k & 1];
       if (item < 0) break;
-      const ItemWork w = ctrl->sched_work[k & 1];
+      const ItemWork& wr = ctrl->sched_work[k & 1];
+      const int nkv0 = wr.nkv[0], nkv1 = wr.nkv[1], nkv_max = wr.nkv_max, len_k = wr.len_k;
       TRACE_AT(3328 + (k & 31) * 8 + 1);
       ok = warp_wait(smem_u32(&ctrl->q_full), k & 1);
       if (!ok) break;
       TRACE_AT(3328 + (k & 31) * 8 + 2);
-      if (w.nkv_max > 0) {
+      if (nkv_max > 0) {
         ok = ring_full_wait(ring_base);
         if (!ok) break;
         TRACE_AT(3328 + (k & 31) * 8 + 3);
         tc_fence_after();
         // (slots whose first score tile was already issued while the previous item finished are skipped)
-        for (int s = 0; s < kSlots; ++s) if (w.nkv[s] > 0 && !pre_issued[s]) issue_s(s, k_desc_of(ring_base));
+        if (nkv0 > 0 && !pre_issued0) issue_s(0, k_desc_of(ring_base));
+        if (nkv1 > 0 && !pre_issued1) issue_s(1, k_desc_of(ring_base));
         TRACE_AT(3328 + (k & 31) * 8 + 4);
 #ifdef B200ATTN_TRACE
         if (k == 0) TRACE_CTA(1, trace_gtime() & 0x7fffffff);
-        ++trace_items; trace_iters += w.nkv_max;
+        ++trace_items; trace_iters += nkv_max;
 #endif
         mma_commit_lead(smem_u32(&ctrl->kv_empty[ring_base % kRing]), lead);
-        if (w.nkv_max == 1) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
+        if (nkv_max == 1) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
       } else {
         mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
       }
-      pre_issued[0] = pre_issued[1] = false;
-      for (int j = 0; j < w.nkv_max && ok; ++j) {
+      pre_issued0 = pre_issued1 = false;
+      for (int j = 0; j < nkv_max && ok; ++j) {
         const int e_v = ring_base + 2 * j + 1;
-        const bool last_iter = j + 1 == w.nkv_max;
+        const bool last_iter = j + 1 == nkv_max;
         // On the last tile of the item the first score tile of the next item is issued right behind each slot's
         // final PV, so the softmax warps can carry straight on.  Everything waited
         // for here (next item published, its Q and first K tile loaded) depends only on work this warp has
         // already issued: Q may be replaced once the last score MMAs of this item, issued one tile ago, complete.
         int next_state = 0;            // 0 = not looked at yet, 1 = ready, -1 = nothing to issue ahead
-        ItemWork wn;
+        int next_nkv0 = 0, next_nkv1 = 0;   // tiles per slot of the next item
         auto prepare_next = [&]() -> bool {
           if (next_state != 0) return true;
           next_state = -1;
           if (!warp_wait(smem_u32(&ctrl->sched_full[(k + 1) & 1]), ((k + 1) >> 1) & 1)) return false;
           if (ctrl->sched_item[(k + 1) & 1] < 0) return true;
-          wn = ctrl->sched_work[(k + 1) & 1];
+          const ItemWork& wn = ctrl->sched_work[(k + 1) & 1];
           if (wn.nkv_max == 0) return true;
+          next_nkv0 = wn.nkv[0];
+          next_nkv1 = wn.nkv[1];
           if (!warp_wait(smem_u32(&ctrl->q_full), (k + 1) & 1)) return false;
-          if (!ring_full_wait(ring_base + 2 * w.nkv_max)) return false;
+          if (!ring_full_wait(ring_base + 2 * nkv_max)) return false;
           next_state = 1;
           return true;
         };
@@ -521,7 +526,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ok = ring_full_wait(e_v);
         if (!ok) break;
         {
-          const int valid = w.len_k - j * kBN;
+          const int valid = len_k - j * kBN;
           if (valid < kBN) {
             // keys past the sequence end carry P == 0 but their V rows may hold anything (stale
             // shared memory, the next sequence, poisoned page tails): zero them so 0 * x stays 0
@@ -545,55 +550,52 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         } else {
           ok = prepare_next();
           if (!ok) break;
-          if (next_state == 1) e_next = ring_base + 2 * w.nkv_max;
+          if (next_state == 1) e_next = ring_base + 2 * nkv_max;
         }
         const uint64_t vb = vdesc + static_cast<uint64_t>((Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes) >> 4);
         const uint64_t kb = kdesc + static_cast<uint64_t>((Plan::kRingOff + ((e_next < 0 ? 0 : e_next) % kRing) * Plan::kTileBytes) >> 4);
-        for (int s = 0; s < kSlots && ok; ++s) {
-          if (j >= w.nkv[s]) continue;
-          const bool s_next = last_iter ? (next_state == 1 && wn.nkv[s] > 0) : (j + 1 < w.nkv[s]);
+        auto slot_step = [&](const int s, const int nkv_s, const int next_nkv_s, int& tiles_done, bool& pre_issued) -> bool {
+          if (j >= nkv_s) return true;
+          const bool s_next = last_iter ? (next_state == 1 && next_nkv_s > 0) : (j + 1 < nkv_s);
           if (j == 0 && k > 0) {
             // the first PV of an item overwrites O: the epilogue of the previous item must have read it out
             // (the softmax warps do that just before they hand over this tile's P)
-            ok = warp_wait(smem_u32(&ctrl->o_free[s]), (k - 1) & 1);
-            if (!ok) break;
+            if (!warp_wait(smem_u32(&ctrl->o_free[s]), (k - 1) & 1)) return false;
           }
-          TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 0);
-          ok = warp_wait(smem_u32(&ctrl->p_ready[s]), tiles_done[s] & 1);
-          if (!ok) break;
-          TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 1);
+          TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 0);
+          if (!warp_wait(smem_u32(&ctrl->p_ready[s]), tiles_done & 1)) return false;
+          TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 1);
           tc_fence_after();
           issue_pv(s, vb, j == 0);
           // V_j may be refilled once the PVs of every slot that reads it have completed: commit behind the last one
-          if (s == kSlots - 1 || j >= w.nkv[kSlots - 1]) { mma_commit_lead(smem_u32(&ctrl->kv_empty[e_v % kRing]), lead); v_released = true; }
-          TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 2);
+          if (s == kSlots - 1 || j >= nkv1) { mma_commit_lead(smem_u32(&ctrl->kv_empty[e_v % kRing]), lead); v_released = true; }
+          TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 2);
           if (s_next) {
             issue_s(s, kb);
-            if (last_iter) pre_issued[s] = true;
+            if (last_iter) pre_issued = true;
           }
-          TRACE_AT(2048 + ((tiles_done[0] + tiles_done[1]) & 127) * 4 + 3);
-          ++tiles_done[s];
-        }
+          TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 3);
+          ++tiles_done;
+          return true;
+        };
+        ok = slot_step(0, nkv0, next_nkv0, tiles_done0, pre_issued0);
+        if (ok) ok = slot_step(1, nkv1, next_nkv1, tiles_done1, pre_issued1);
         if (!ok) break;
         if (last_iter) {
           // a slot that ran out of tiles earlier in this item gets its head start here
           ok = prepare_next();
           if (!ok) break;
           if (next_state == 1) {
-            for (int s = 0; s < kSlots; ++s) {
-              if (pre_issued[s] || wn.nkv[s] == 0) continue;
-              tc_fence_after();
-              issue_s(s, kb);
-              pre_issued[s] = true;
-            }
+            if (!pre_issued0 && next_nkv0 > 0) { tc_fence_after(); issue_s(0, kb); pre_issued0 = true; }
+            if (!pre_issued1 && next_nkv1 > 0) { tc_fence_after(); issue_s(1, kb); pre_issued1 = true; }
           }
         }
         if (!v_released) mma_commit_lead(smem_u32(&ctrl->kv_empty[e_v % kRing]), lead);
-        if (j + 1 < w.nkv_max) mma_commit_lead(smem_u32(&ctrl->kv_empty[(e_v + 1) % kRing]), lead);
+        if (j + 1 < nkv_max) mma_commit_lead(smem_u32(&ctrl->kv_empty[(e_v + 1) % kRing]), lead);
         // the last score MMAs of the item have been issued: Q may be replaced once they complete
-        if (j + 2 == w.nkv_max) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
+        if (j + 2 == nkv_max) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
       }
-      ring_base += 2 * w.nkv_max;
+      ring_base += 2 * nkv_max;
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));
       __syncwarp();
     }
