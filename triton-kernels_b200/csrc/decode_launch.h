@@ -42,6 +42,7 @@ struct DecodeParams {
   int causal;
   int target_items;
   int min_chunk;
+  int equal_split;   // 1: a sequence's items are of equal size; 0: full chunks and one remainder
   int max_items;
   float scale_log2;  // sm_scale * log2(e)
 };

@@ -28,10 +28,12 @@ class DecodePlan:
     threads: int
 
 
-def decode_plan(sm_count: int, batch: int, q_heads: int, kv_heads: int, q_len: int) -> DecodePlan:
+def decode_plan(sm_count: int, batch: int, q_heads: int, kv_heads: int, q_len: int, fp32: bool = False) -> DecodePlan:
     group = q_heads // kv_heads
     rows = group * q_len
-    target = max(1, (sm_count * 2 * 4) // max(1, kv_heads))
+    # six (item, kv head) CTAs per SM for the tensor-core kernels (a whole number of waves at 2 or 3 resident CTAs
+    # per SM), eight for the fp32 kernel
+    target = max(1, (sm_count * (8 if fp32 else 6)) // max(1, kv_heads))
     by_rows = -(-(rows * 8) // DECODE_TILE_TOKENS) * DECODE_TILE_TOKENS
     min_chunk = max(128, by_rows)
     tiles = -(-rows // 16)
@@ -40,11 +42,20 @@ def decode_plan(sm_count: int, batch: int, q_heads: int, kv_heads: int, q_len: i
 
 
 def decode_chunk_tokens(plan: DecodePlan, lengths: Sequence[int]) -> int:
-    """Chunk size the device planner picks for these lengths."""
-    total = sum(max(0, int(n)) for n in lengths)
-    per = -(-total // plan.target_items)
-    per = -(-per // DECODE_TILE_TOKENS) * DECODE_TILE_TOKENS
-    return max(per, plan.min_chunk)
+    """Chunk size the device planner picks for these lengths: the smallest of 32 candidates between
+    total / target_items and twice that which splits the batch into at most target_items items."""
+    lens = [max(0, int(n)) for n in lengths]
+    total = sum(lens)
+    base = -(-total // plan.target_items)
+    base = -(-base // DECODE_TILE_TOKENS) * DECODE_TILE_TOKENS
+    base = max(base, plan.min_chunk)
+    chunk = base
+    for k in range(32):
+        chunk = base + (base * k) // 32
+        chunk = -(-chunk // DECODE_TILE_TOKENS) * DECODE_TILE_TOKENS
+        if sum(max(1, -(-n // chunk)) for n in lens) <= plan.target_items:
+            break
+    return chunk
 
 
 def decode_items(plan: DecodePlan, lengths: Sequence[int]) -> List[int]:
