@@ -20,6 +20,7 @@
  *   b200attn_*_workspace_bytes <- the torch.empty fp32 workspaces at
  *                        kernels/attention.py:852-864, kernels/decode.py:280-292,
  *                        kernels/speculative_decode.py:311-323
+ *   b200attn_softmax  <- kernels/softmax.py:152-236 softmax, :378-462 log_softmax
  *   b200attn_device_info <- torch.cuda.get_device_properties(...).multi_processor_count
  *                        at kernels/attention.py:836, kernels/decode.py:273
  */
@@ -206,6 +207,24 @@ typedef struct b200attn_paged_append_args_t {
 } b200attn_paged_append_args_t;
 
 int b200attn_paged_append(const b200attn_paged_append_args_t* args, void* cuda_stream);
+
+/*
+ * Softmax or log-softmax over the last dimension of a contiguous [rows, cols] tensor (any leading shape flattened
+ * into rows), fp32 arithmetic, same dtype out.  `out` may be `x` (in place).  No workspace.
+ * Replaces kernels/softmax.py:152-236 `softmax` (small :18-32, medium :35-66, partial / merge / finalize :69-150)
+ * and :378-462 `log_softmax` (:239-375).
+ */
+typedef struct b200attn_softmax_args_t {
+  const void* x;
+  void* out;
+  int64_t rows;
+  int64_t cols;
+  int32_t dtype;          /* B200ATTN_F16 / BF16 / F32 */
+  int32_t log_softmax;    /* 0: softmax, 1: log-softmax */
+  int32_t device;
+} b200attn_softmax_args_t;
+
+int b200attn_softmax(const b200attn_softmax_args_t* args, void* cuda_stream);
 
 /*
  * Reads (and clears) the error word a kernel of an earlier call may have set in

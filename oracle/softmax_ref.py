@@ -75,3 +75,27 @@ def lse_merge_f64(ms, ls, accs) -> np.ndarray:
     num = (a[:, :, None] * accs).sum(axis=0)
     den = (a * ls).sum(axis=0)
     return num / den[:, None]
+
+
+def row_softmax_f64(x, *, log: bool = False) -> np.ndarray:
+    """Softmax (or log-softmax) over the last axis in float64: the formula behind the reference's test oracle
+    ``torch.nn.functional.softmax`` / ``log_softmax`` (tests/test_softmax.py:47,95), written out as
+    ``exp(x - max) / sum(exp(x - max))`` and ``x - max - log(sum(exp(x - max)))`` (kernels/softmax.py:26-31,247-250)."""
+    x = np.asarray(x, dtype=np.float64)
+    m = np.max(x, axis=-1, keepdims=True)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        e = np.exp(x - m)
+        s = np.sum(e, axis=-1, keepdims=True)
+        return (x - m - np.log(s)) if log else e / s
+
+
+def row_softmax_split_f64(x, parts: int, *, log: bool = False) -> np.ndarray:
+    """The same result through per-slice (max, sum) pairs merged as the reference merges its programs
+    (kernels/softmax.py:114-127): what the cluster kernel computes, slice by slice."""
+    x = np.asarray(x, dtype=np.float64)
+    pieces = np.array_split(x, parts, axis=-1)
+    ms = [np.max(p, axis=-1, keepdims=True) for p in pieces]
+    ls = [np.sum(np.exp(p - m), axis=-1, keepdims=True) for p, m in zip(pieces, ms)]
+    g = np.max(np.concatenate(ms, axis=-1), axis=-1, keepdims=True)
+    total = sum(l * np.exp(m - g) for l, m in zip(ls, ms))
+    return (x - g - np.log(total)) if log else np.exp(x - g) / total

@@ -134,3 +134,24 @@ def test_c1_cpu_config_runs():
     f64 = softmax_ref.attention_f64(q.transpose(0, 1).numpy(), k.transpose(0, 1).numpy(), v.transpose(0, 1).numpy(),
                                     mask=softmax_ref.causal_top_left(512, 512))
     np.testing.assert_allclose(out.transpose(0, 1).numpy(), f64, atol=5e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("shape", [(7,), (5, 33), (3, 4, 129)])
+@pytest.mark.parametrize("log", [False, True])
+def test_row_softmax_oracle_matches_torch_and_split(shape, log):
+    """The row-softmax restatement against the reference tests' own oracle (torch's softmax / log_softmax) and
+    against the split-and-merge form the long-row kernels use."""
+    import numpy as np
+    from oracle import softmax_ref
+
+    x = torch.randn(shape, generator=torch.Generator().manual_seed(len(shape)), dtype=torch.float64) * 5
+    want = (torch.log_softmax if log else torch.softmax)(x, dim=-1).numpy()
+    got = softmax_ref.row_softmax_f64(x.numpy(), log=log)
+    np.testing.assert_allclose(got, want, rtol=1e-12, atol=1e-14)
+    split = softmax_ref.row_softmax_split_f64(x.numpy(), 3, log=log)
+    np.testing.assert_allclose(split, want, rtol=1e-12, atol=1e-13)
+    # known answers: a constant row is uniform, a dominant entry takes everything
+    u = softmax_ref.row_softmax_f64(np.full((4,), 2.5))
+    np.testing.assert_allclose(u, np.full((4,), 0.25))
+    d = softmax_ref.row_softmax_f64(np.array([0.0, 800.0, -3.0]))
+    np.testing.assert_allclose(d, np.array([0.0, 1.0, 0.0]), atol=1e-300)

@@ -6,6 +6,7 @@
 #include "common.cuh"
 #include "decode_launch.h"
 #include "paged_append_launch.h"
+#include "softmax_launch.h"
 #include "prefill_launch.h"
 
 namespace b200attn {
@@ -185,6 +186,20 @@ int b200attn_paged_append(const b200attn_paged_append_args_t* a, void* cuda_stre
   DeviceGuard guard;
   if ((rc = guard.enter(a->device))) return rc;
   return launch_paged_append(*a, info.sm_count, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int b200attn_softmax(const b200attn_softmax_args_t* a, void* cuda_stream) {
+  if (!a) { set_error("args is null"); return B200ATTN_E_INVALID; }
+  if (a->rows < 0 || a->cols < 0) { set_error("softmax: negative extent"); return B200ATTN_E_INVALID; }
+  if (a->rows == 0 || a->cols == 0) return B200ATTN_OK;
+  if (!a->x || !a->out) { set_error("softmax: null pointer"); return B200ATTN_E_INVALID; }
+  if (a->dtype != B200ATTN_F16 && a->dtype != B200ATTN_BF16 && a->dtype != B200ATTN_F32) { set_error("softmax: unknown dtype %d", a->dtype); return B200ATTN_E_UNSUPPORTED; }
+  b200attn_device_info_t info;
+  int rc;
+  if ((rc = check_arch(a->device, &info))) return rc;
+  DeviceGuard guard;
+  if ((rc = guard.enter(a->device))) return rc;
+  return launch_softmax(*a, info.sm_count, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int b200attn_check_workspace(void* workspace, void* cuda_stream, int32_t* code) {

@@ -1,0 +1,302 @@
+// Row softmax / log-softmax over the last dimension for sm_100a (HBM-bound: one read, one write).
+//
+// Replaces the reference's small / medium / partial + merge + finalize kernels (kernels/softmax.py:18-150 and
+// :239-375): there a row longer than one block is read twice (three launches when it is split over programs).
+// Here a row is staged once in shared memory and normalised from there:
+//   softmax_row_kernel     one CTA per row, the row (as its 16- or 32-bit elements) in up to 200 KiB of shared memory
+//   softmax_cluster_kernel a row longer than that is spread over a thread-block cluster of 2, 4 or 8 CTAs; the CTAs
+//                          exchange their (max, sum) pairs through distributed shared memory
+//   softmax_stream_kernel  rows beyond 8 x 200 KiB: one CTA per row, online (max, sum) pass, then a second read
+// All arithmetic is fp32 (expf / logf), like the reference's `.to(tl.float32)`.  `out` may alias `x`: a CTA writes a
+// row only after it has staged it (the streaming kernel reads element i right before it writes element i).
+#include <cooperative_groups.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+#include "softmax_launch.h"
+
+namespace cg = cooperative_groups;
+
+namespace b200attn {
+
+namespace {
+
+constexpr int kRowSmemBytes = 200 * 1024;   // row bytes one CTA stages
+constexpr int kMaxCluster = 8;              // portable cluster size
+
+__device__ __forceinline__ float warp_max(float v) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// block-wide reductions through a 32-float scratch array; every thread gets the result
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();                 // scratch may still be read from a previous reduction
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? scratch[lane] : -INFINITY;
+  return warp_max(r);
+}
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = lane < nw ? scratch[lane] : 0.f;
+  return warp_sum(r);
+}
+
+template <typename T> struct Vec16 { static constexpr int kElems = 16 / sizeof(T); };
+
+// (max, sum of exp(x - max)) of two parts
+__device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2) {
+  const float g = fmaxf(m, m2);
+  const float a = (m == -INFINITY) ? 0.f : expf(m - g);
+  const float b = (m2 == -INFINITY) ? 0.f : expf(m2 - g);
+  l = l * a + l2 * b;
+  m = g;
+}
+
+// Stage `n` elements of a row in shared memory (16-byte copies when VEC) and return this thread's running max.
+template <typename T, bool VEC>
+__device__ __forceinline__ float stage_row(const T* src, T* row, long long n) {
+  float mx = -INFINITY;
+  if constexpr (VEC) {
+    constexpr int E = Vec16<T>::kElems;
+    const long long nv = n / E;
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(row);
+    for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
+      const uint4 u = s4[i];       // (plain load: `out` may alias `x`)
+      d4[i] = u;
+      const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int k = 0; k < E; ++k) mx = fmaxf(mx, ElemTraits<T>::to_float(e[k]));
+    }
+  } else {
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) {
+      const T v = src[i];
+      row[i] = v;
+      mx = fmaxf(mx, ElemTraits<T>::to_float(v));
+    }
+  }
+  return mx;
+}
+
+template <typename T, bool VEC>
+__device__ __forceinline__ float row_exp_sum(const T* row, long long n, float m) {
+  float s = 0.f;
+  if (m == -INFINITY) return 0.f;
+  if constexpr (VEC) {
+    constexpr int E = Vec16<T>::kElems;
+    const long long nv = n / E;
+    const uint4* r4 = reinterpret_cast<const uint4*>(row);
+    for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
+      const uint4 u = r4[i];
+      const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int k = 0; k < E; ++k) s += expf(ElemTraits<T>::to_float(e[k]) - m);
+    }
+  } else {
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) s += expf(ElemTraits<T>::to_float(row[i]) - m);
+  }
+  return s;
+}
+
+// softmax: exp(x - m) / l;  log-softmax: (x - m) - log l  (in this order: m + log l would lose log l next to a
+// large m)
+template <typename T, bool LOG>
+__device__ __forceinline__ T finish(float x, float m, float k) {
+  if constexpr (LOG) return ElemTraits<T>::from_float((x - m) - k);
+  else return ElemTraits<T>::from_float(expf(x - m) * k);
+}
+
+template <typename T, bool LOG, bool VEC>
+__device__ __forceinline__ void write_row(const T* row, T* dst, long long n, float m, float k) {
+  if constexpr (VEC) {
+    constexpr int E = Vec16<T>::kElems;
+    const long long nv = n / E;
+    const uint4* r4 = reinterpret_cast<const uint4*>(row);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (long long i = threadIdx.x; i < nv; i += blockDim.x) {
+      uint4 u = r4[i];
+      T* e = reinterpret_cast<T*>(&u);
+#pragma unroll
+      for (int q = 0; q < E; ++q) e[q] = finish<T, LOG>(ElemTraits<T>::to_float(e[q]), m, k);
+      d4[i] = u;
+    }
+  } else {
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) dst[i] = finish<T, LOG>(ElemTraits<T>::to_float(row[i]), m, k);
+  }
+}
+
+// the constant the write pass needs: 1 / l for softmax, log l for log-softmax
+template <bool LOG>
+__device__ __forceinline__ float final_constant(float m, float l) {
+  (void)m;
+  if constexpr (LOG) return logf(l);
+  else return 1.f / l;
+}
+
+// ---------------------------------------------------------------------------
+// one CTA per row, the row in shared memory
+// ---------------------------------------------------------------------------
+template <typename T, bool LOG, bool VEC>
+__global__ void softmax_row_kernel(const T* x, T* out, long long rows, long long cols) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float scratch[32];
+  T* row = reinterpret_cast<T*>(smem_raw);
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* src = x + r * cols;
+    __syncthreads();               // the previous row has been written out of `row`
+    float m = stage_row<T, VEC>(src, row, cols);
+    m = block_max(m, scratch);     // (its barriers also publish the staged row)
+    const float l = block_sum(row_exp_sum<T, VEC>(row, cols, m), scratch);
+    write_row<T, LOG, VEC>(row, out + r * cols, cols, m, final_constant<LOG>(m, l));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// one cluster per row: every CTA stages a slice, (max, sum) pairs meet in distributed shared memory
+// ---------------------------------------------------------------------------
+template <typename T, bool LOG, bool VEC>
+__global__ void softmax_cluster_kernel(const T* x, T* out, long long rows, long long cols,
+                                       long long slice) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float scratch[32];
+  __shared__ float ml[2];          // this CTA's (max, sum), read by its peers
+  cg::cluster_group cluster = cg::this_cluster();
+  const unsigned rank = cluster.block_rank(), csize = cluster.num_blocks();
+  T* row = reinterpret_cast<T*>(smem_raw);
+  const long long c0 = std::min<long long>(cols, slice * rank);
+  const long long n = std::min<long long>(cols - c0, slice);
+  const long long nclusters = gridDim.x / csize;
+  for (long long r = blockIdx.x / csize; r < rows; r += nclusters) {
+    const T* src = x + r * cols + c0;
+    float m = stage_row<T, VEC>(src, row, n);
+    m = block_max(m, scratch);
+    const float l = block_sum(row_exp_sum<T, VEC>(row, n, m), scratch);
+    if (threadIdx.x == 0) { ml[0] = m; ml[1] = l; }
+    cluster.sync();                // every CTA's pair is in place
+    float gm = -INFINITY, gl = 0.f;
+    for (unsigned p = 0; p < csize; ++p) {
+      const float* peer = cluster.map_shared_rank(ml, p);
+      merge_ml(gm, gl, peer[0], peer[1]);
+    }
+    cluster.sync();                // all pairs have been read: they may be overwritten for the next row
+    write_row<T, LOG, VEC>(row, out + r * cols + c0, n, gm, final_constant<LOG>(gm, gl));
+    __syncthreads();               // `row` is free again
+  }
+}
+
+// ---------------------------------------------------------------------------
+// rows that do not fit a cluster: online (max, sum), then a second read
+// ---------------------------------------------------------------------------
+template <typename T, bool LOG>
+__global__ void softmax_stream_kernel(const T* x, T* out, long long rows, long long cols) {
+  __shared__ float scratch[32];
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* src = x + r * cols;
+    T* dst = out + r * cols;
+    float m = -INFINITY, l = 0.f;
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x) {
+      const float v = ElemTraits<T>::to_float(src[i]);
+      if (v > m) { l = (m == -INFINITY) ? 0.f : l * expf(m - v); m = v; }
+      if (v != -INFINITY) l += expf(v - m);
+    }
+    const float gm = block_max(m, scratch);
+    const float part = (m == -INFINITY) ? 0.f : l * expf(m - gm);
+    const float gl = block_sum(part, scratch);
+    const float k = final_constant<LOG>(gm, gl);
+    for (long long i = threadIdx.x; i < cols; i += blockDim.x)
+      dst[i] = finish<T, LOG>(ElemTraits<T>::to_float(src[i]), gm, k);
+  }
+}
+
+template <typename K>
+int set_smem_limit(K kernel, size_t bytes) {
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(softmax)");
+  return 0;
+}
+
+template <typename T, bool LOG, bool VEC>
+int launch_typed(const b200attn_softmax_args_t& a, int sm_count, cudaStream_t stream) {
+  const T* x = static_cast<const T*>(a.x);
+  T* out = static_cast<T*>(a.out);
+  const long long rows = a.rows, cols = a.cols;
+  const size_t row_bytes = static_cast<size_t>(cols) * sizeof(T);
+  if (row_bytes <= static_cast<size_t>(kRowSmemBytes)) {
+    // threads: enough for 16-byte pieces to keep every lane busy on short rows, 1024 on long ones
+    int threads = 64;
+    while (threads < 1024 && static_cast<long long>(threads) * 8 < cols) threads *= 2;
+    const size_t smem = (row_bytes + 15) & ~static_cast<size_t>(15);
+    int rc = set_smem_limit(softmax_row_kernel<T, LOG, VEC>, smem);
+    if (rc) return rc;
+    const long long max_grid = static_cast<long long>(sm_count) * 32;
+    const unsigned grid = static_cast<unsigned>(std::min<long long>(rows, max_grid));
+    softmax_row_kernel<T, LOG, VEC><<<grid, threads, smem, stream>>>(x, out, rows, cols);
+  } else if (row_bytes <= static_cast<size_t>(kRowSmemBytes) * kMaxCluster) {
+    int csize = 2;
+    while (static_cast<size_t>(kRowSmemBytes) * csize < row_bytes) csize *= 2;
+    constexpr int E = 16 / static_cast<int>(sizeof(T));
+    long long slice = (cols + csize - 1) / csize;
+    slice = ((slice + E - 1) / E) * E;                 // slices start on 16-byte boundaries of the row
+    const size_t smem = static_cast<size_t>(slice) * sizeof(T);
+    int rc = set_smem_limit(softmax_cluster_kernel<T, LOG, VEC>, smem);
+    if (rc) return rc;
+    const long long clusters = std::min<long long>(rows, std::max(1, sm_count / csize));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * csize), 1, 1);
+    cfg.blockDim = dim3(1024, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, softmax_cluster_kernel<T, LOG, VEC>, x, out, rows, cols, slice);
+    if (e != cudaSuccess) return cuda_fail(e, "softmax cluster kernel launch");
+  } else {
+    const unsigned grid = static_cast<unsigned>(std::min<long long>(rows, static_cast<long long>(sm_count) * 2));
+    softmax_stream_kernel<T, LOG><<<grid, 1024, 0, stream>>>(x, out, rows, cols);
+  }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "softmax kernel launch");
+  return B200ATTN_OK;
+}
+
+template <typename T>
+int launch_dtype(const b200attn_softmax_args_t& a, int sm_count, cudaStream_t stream) {
+  // 16-byte copies need every row to start on a 16-byte boundary
+  const bool vec = (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0 &&
+                   (static_cast<size_t>(a.cols) * sizeof(T)) % 16 == 0;
+  if (a.log_softmax) {
+    return vec ? launch_typed<T, true, true>(a, sm_count, stream) : launch_typed<T, true, false>(a, sm_count, stream);
+  }
+  return vec ? launch_typed<T, false, true>(a, sm_count, stream) : launch_typed<T, false, false>(a, sm_count, stream);
+}
+
+}  // namespace
+
+int launch_softmax(const b200attn_softmax_args_t& a, int sm_count, cudaStream_t stream) {
+  switch (a.dtype) {
+    case B200ATTN_F16: return launch_dtype<__half>(a, sm_count, stream);
+    case B200ATTN_BF16: return launch_dtype<__nv_bfloat16>(a, sm_count, stream);
+    case B200ATTN_F32: return launch_dtype<float>(a, sm_count, stream);
+    default: set_error("softmax: unknown dtype %d", a.dtype); return B200ATTN_E_UNSUPPORTED;
+  }
+}
+
+}  // namespace b200attn

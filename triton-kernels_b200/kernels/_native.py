@@ -33,6 +33,7 @@ EXPORTS = (
     "b200attn_decode",
     "b200attn_decode_static",
     "b200attn_paged_append",
+    "b200attn_softmax",
     "b200attn_check_workspace",
 )
 
@@ -126,6 +127,18 @@ class PagedAppendArgs(C.Structure):
     ]
 
 
+class SoftmaxArgs(C.Structure):
+    _fields_ = [
+        ("x", C.c_void_p),
+        ("out", C.c_void_p),
+        ("rows", C.c_int64),
+        ("cols", C.c_int64),
+        ("dtype", C.c_int32),
+        ("log_softmax", C.c_int32),
+        ("device", C.c_int32),
+    ]
+
+
 _lib: Optional[C.CDLL] = None
 _lib_lock = threading.Lock()
 
@@ -165,6 +178,8 @@ def lib() -> C.CDLL:
         handle.b200attn_decode_static.restype = C.c_int
         handle.b200attn_paged_append.argtypes = [C.POINTER(PagedAppendArgs), C.c_void_p]
         handle.b200attn_paged_append.restype = C.c_int
+        handle.b200attn_softmax.argtypes = [C.POINTER(SoftmaxArgs), C.c_void_p]
+        handle.b200attn_softmax.restype = C.c_int
         handle.b200attn_check_workspace.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
         handle.b200attn_check_workspace.restype = C.c_int
         got = handle.b200attn_abi_version()
