@@ -5,12 +5,15 @@ benchmarks/decode.py:11-43, benchmarks/speculative_decode.py:11-50 of the refere
             mha 8/8, gqa 8/2, mqa 8/1, fp16 / bf16, dense / ragged / paged, causal for self attention
   decode  : BATCH 16, HEAD_DIM 64, N in {16 ... 8192}, same topologies and layouts
   spec    : as decode with M in {2, 4, 6, 8, 10} draft tokens, causal and not
+  softmax : the shapes of benchmarks/benchmark_softmx.py:68-84 plus tensors far larger than L2; GB/s counts one read
+            and one write of the tensor (the reference's bytes_softmax, :21-22)
 
 Timing: CUDA events, median of `iters` calls after warm-up, L2 flushed between calls (the reference uses
 triton.testing.do_bench, which flushes L2 the same way).  Prints one line per cell: milliseconds and the derived
 TFLOP/s (prefill, visible score pairs only) or KV GB/s (decode).
 
-    PYTHONPATH=triton-kernels_b200 python -m benchmarks.sweeps [prefill|decode|spec] [--quick]
+    PYTHONPATH=triton-kernels_b200 python -m benchmarks.sweeps [prefill|decode|spec|softmax] [--quick]
+    PYTHONPATH=triton-kernels_b200 python -m benchmarks.sweeps softmax --rows 8192 --cols 8192 --dtype float32
 """
 from __future__ import annotations
 
@@ -19,7 +22,7 @@ import statistics
 
 import torch
 
-from kernels import decode_attention, flash_attention_v2, speculative_decode_attention
+from kernels import decode_attention, flash_attention_v2, log_softmax, softmax, speculative_decode_attention
 
 DEVICE = "cuda"
 BATCH = 16
@@ -130,10 +133,34 @@ def sweep_decode(quick, spec):
                             print(f"{layout:7s}{topo:5s}{str(dtype)[6:10]:6s}{m:3d}{str(causal):>7s}{n:6d}{t:9.4f}{gbs:10.1f}")
 
 
+SOFTMAX_SHAPES = [(1024,), (4096,), (64, 128), (128, 512), (512, 1024), (2048, 2048), (4096, 4096), (1, 32768),
+                  (2, 32768), (8, 32768), (16, 32768), (1, 65536), (2, 65536), (8, 65536), (1, 131072),
+                  # HBM-bound sizes (the grid above fits in L2)
+                  (8192, 8192), (16384, 16384), (65536, 2048), (1024, 131072), (64, 1048576)]
+
+
+def sweep_softmax(quick, only=None, dtypes=None):
+    print("softmax: op dtype rows cols ms GB/s")
+    shapes = [only] if only else (SOFTMAX_SHAPES[::3] if quick else SOFTMAX_SHAPES)
+    for dtype in dtypes or (torch.float16, torch.bfloat16, torch.float32):
+        for shape in shapes:
+            x = torch.randn(shape, device=DEVICE, dtype=dtype)
+            out = torch.empty_like(x)
+            for name, f in (("softmax", softmax), ("log_softmax", log_softmax)):
+                t = _time(lambda: f(x, out=out))
+                gbs = 2 * x.numel() * x.element_size() / t / 1e6
+                rows = x.numel() // x.shape[-1]
+                print(f"{name:12s}{str(dtype)[6:]:9s}{rows:8d}{x.shape[-1]:9d}{t:10.4f}{gbs:10.1f}")
+            del x, out
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("which", nargs="?", default="all", choices=["all", "prefill", "decode", "spec"])
+    ap.add_argument("which", nargs="?", default="all", choices=["all", "prefill", "decode", "spec", "softmax"])
     ap.add_argument("--quick", action="store_true", help="a thin slice of each grid")
+    ap.add_argument("--rows", type=int, default=0, help="softmax: one shape only")
+    ap.add_argument("--cols", type=int, default=0)
+    ap.add_argument("--dtype", default="", choices=["", "float16", "bfloat16", "float32"])
     a = ap.parse_args()
     if a.which in ("all", "prefill"):
         sweep_prefill(a.quick)
@@ -141,6 +168,9 @@ def main():
         sweep_decode(a.quick, spec=False)
     if a.which in ("all", "spec"):
         sweep_decode(a.quick, spec=True)
+    if a.which in ("all", "softmax"):
+        only = (a.rows, a.cols) if a.rows > 0 and a.cols > 0 else None
+        sweep_softmax(a.quick, only, [getattr(torch, a.dtype)] if a.dtype else None)
 
 
 if __name__ == "__main__":

@@ -2,7 +2,9 @@
 //
 // Replaces the reference's small / medium / partial + merge + finalize kernels (kernels/softmax.py:18-150 and
 // :239-375): there a row longer than one block is read twice (three launches when it is split over programs).
-// Here a row is staged once in shared memory and normalised from there:
+// Here a row is read once, kept on the SM and normalised from there:
+//   softmax_reg_kernel     one CTA per row, up to 32 elements per thread in registers (rows up to 32 768 elements whose
+//                          bytes are a multiple of 16)
 //   softmax_row_kernel     one CTA per row, the row (as its 16- or 32-bit elements) in up to 200 KiB of shared memory
 //   softmax_cluster_kernel a row longer than that is spread over a thread-block cluster of 2, 4 or 8 CTAs; the CTAs
 //                          exchange their (max, sum) pairs through distributed shared memory
@@ -147,6 +149,68 @@ __device__ __forceinline__ float final_constant(float m, float l) {
 }
 
 // ---------------------------------------------------------------------------
+// one CTA per row, the row in registers: thread t holds the 16-byte pieces t, t + blockDim, ... (VPT of them)
+// ---------------------------------------------------------------------------
+template <typename T> __device__ __forceinline__ float fast_or_exact_exp(float x) {
+  // 16-bit outputs round away far more than the approximate exponential loses; fp32 outputs need expf
+  if constexpr (sizeof(T) == 2) return __expf(x);
+  else return expf(x);
+}
+
+template <typename T, bool LOG, int VPT>
+__global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, long long rows, long long cols) {
+  constexpr int E = Vec16<T>::kElems;
+  __shared__ float scratch[32];
+  const int nv = static_cast<int>(cols / E);
+  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(x + r * cols);
+    uint4* d4 = reinterpret_cast<uint4*>(out + r * cols);
+    float f[VPT * E];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < nv) {
+        const uint4 u = s4[i];
+        const T* e = reinterpret_cast<const T*>(&u);
+#pragma unroll
+        for (int q = 0; q < E; ++q) { f[k * E + q] = ElemTraits<T>::to_float(e[q]); mx = fmaxf(mx, f[k * E + q]); }
+      } else {
+#pragma unroll
+        for (int q = 0; q < E; ++q) f[k * E + q] = -INFINITY;
+      }
+    }
+    const float m = block_max(mx, scratch);
+    float sum = 0.f;
+    if (m != -INFINITY) {
+#pragma unroll
+      for (int j = 0; j < VPT * E; ++j) {
+        const float ev = fast_or_exact_exp<T>(f[j] - m);      // exp(-inf) = 0 for the padding
+        sum += ev;
+        if constexpr (!LOG) f[j] = ev;
+      }
+    }
+    const float l = block_sum(sum, scratch);
+    const float kk = final_constant<LOG>(m, l);
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < nv) {
+        uint4 u;
+        T* e = reinterpret_cast<T*>(&u);
+#pragma unroll
+        for (int q = 0; q < E; ++q) {
+          const float v = f[k * E + q];
+          if constexpr (LOG) e[q] = ElemTraits<T>::from_float((v - m) - kk);
+          else e[q] = ElemTraits<T>::from_float(m == -INFINITY ? __int_as_float(0x7fc00000) : v * kk);
+        }
+        d4[i] = u;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // one CTA per row, the row in shared memory
 // ---------------------------------------------------------------------------
 template <typename T, bool LOG, bool VEC>
@@ -234,7 +298,25 @@ int launch_typed(const b200attn_softmax_args_t& a, int sm_count, cudaStream_t st
   T* out = static_cast<T*>(a.out);
   const long long rows = a.rows, cols = a.cols;
   const size_t row_bytes = static_cast<size_t>(cols) * sizeof(T);
-  if (row_bytes <= static_cast<size_t>(kRowSmemBytes)) {
+  constexpr int E = 16 / static_cast<int>(sizeof(T));
+  constexpr int kMaxVpt = 32 / E;                      // 32 elements per thread
+  if (VEC && cols / E <= 1024LL * kMaxVpt) {
+    const int nv = static_cast<int>(cols / E);
+    int threads = 64;
+    while (threads < 1024 && threads * 4 < nv) threads *= 2;
+    int vpt = 1;
+    while (threads * vpt < nv) vpt *= 2;
+    const long long max_grid = static_cast<long long>(sm_count) * (2048 / threads) * 4;
+    const unsigned grid = static_cast<unsigned>(std::min<long long>(rows, max_grid));
+    switch (vpt) {
+      case 1: softmax_reg_kernel<T, LOG, 1><<<grid, threads, 0, stream>>>(x, out, rows, cols); break;
+      case 2: softmax_reg_kernel<T, LOG, 2><<<grid, threads, 0, stream>>>(x, out, rows, cols); break;
+      case 4: softmax_reg_kernel<T, LOG, 4><<<grid, threads, 0, stream>>>(x, out, rows, cols); break;
+      default:
+        if constexpr (kMaxVpt >= 8) softmax_reg_kernel<T, LOG, 8><<<grid, threads, 0, stream>>>(x, out, rows, cols);
+        break;
+    }
+  } else if (row_bytes <= static_cast<size_t>(kRowSmemBytes)) {
     // threads: enough for 16-byte pieces to keep every lane busy on short rows, 1024 on long ones
     int threads = 64;
     while (threads < 1024 && static_cast<long long>(threads) * 8 < cols) threads *= 2;
@@ -247,7 +329,6 @@ int launch_typed(const b200attn_softmax_args_t& a, int sm_count, cudaStream_t st
   } else if (row_bytes <= static_cast<size_t>(kRowSmemBytes) * kMaxCluster) {
     int csize = 2;
     while (static_cast<size_t>(kRowSmemBytes) * csize < row_bytes) csize *= 2;
-    constexpr int E = 16 / static_cast<int>(sizeof(T));
     long long slice = (cols + csize - 1) / csize;
     slice = ((slice + E - 1) / E) * E;                 // slices start on 16-byte boundaries of the row
     const size_t smem = static_cast<size_t>(slice) * sizeof(T);
