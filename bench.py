@@ -13,7 +13,8 @@ A step is one call of the entry point on one batch of seeded synthetic inputs.
   value : algorithmic FLOPs (prefill) or KV bytes (decode) of all ranks / device time of the slowest
           rank, inputs resident in HBM, CUDA events on the launch stream, L2 flushed between steps.
   e2e   : the same quantity through the Python entry point with the per-step inputs in pinned host
-          memory: H2D copies, the call, and the D2H copy of the output are all inside the timed region.
+          memory: H2D copies, the call, and the D2H copy of the output are all inside the timed region
+          (upload, kernels and download on three streams, two sets of device input buffers).
 Multi-GPU runs are weak scaling: every rank runs the full single-GPU configuration on its own
 seeded inputs (global batch = N x the configuration's batch); there is no data-path collective.
 """
@@ -42,7 +43,7 @@ L2_FLUSH_BYTES = 512 << 20
 
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
 # summarised under profiles/prefill_kernel_c2_c3.md and profiles/decode_mma_kernel_c4_c5.md.
-NCU_TRAFFIC_BYTES = {"c2": 52.8e6, "c3": 775.6e6, "c4": 1140.3e6, "c5": 1803.3e6}
+NCU_TRAFFIC_BYTES = {"c2": 55.9e6, "c3": 777.8e6, "c4": 1137.7e6, "c5": 1788.3e6}
 # kernels of this library launched per call of the entry point (prefill: the persistent kernel;
 # decode: planner + split kernel with fused merge)
 LAUNCHES_PER_STEP = {"c2": 1, "c3": 1, "c4": 2, "c5": 2}
@@ -176,31 +177,66 @@ def time_resident(wl, steps, warmup, flush, world):
 
 
 def time_end_to_end(wl, steps, warmup, world):
-    """Inputs start in pinned host memory every step; the output ends in pinned host memory."""
+    """Every step copies its inputs from pinned host memory, calls the public entry point and copies the output back
+    to pinned host memory, all inside the timed region.  The three stages run on three streams with two sets of
+    device input buffers, the way a serving loop would: step i's upload overlaps step i-1's kernels and download
+    (PCIe is full duplex), ordered by events; nothing is skipped or cached."""
+    dev = next(iter(wl.tensors.values())).device
     host = {n: wl.tensors[n].cpu().pin_memory() for n in wl.host_inputs}
+    dev_sets = [{n: wl.tensors[n] for n in wl.host_inputs}, {n: torch.empty_like(wl.tensors[n]) for n in wl.host_inputs}]
     out0 = wl.run()
     out_host = torch.empty(out0.shape, dtype=out0.dtype).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in host.values())
     d2h = out_host.numel() * out_host.element_size()
+    s_comp = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    comp_done = [None, None]     # last compute event that read each input set
+    out_done = None              # the previous download (out_host is reused)
 
-    def step():
-        for n, t in host.items():
-            wl.tensors[n].copy_(t, non_blocking=True)
+    def step(i):
+        nonlocal out_done
+        cur = dev_sets[i & 1]
+        with torch.cuda.stream(s_in):
+            if comp_done[i & 1] is not None:
+                s_in.wait_event(comp_done[i & 1])          # the kernels that read this set two steps ago are done
+            for n, t in host.items():
+                cur[n].copy_(t, non_blocking=True)
+            uploaded = torch.cuda.Event()
+            uploaded.record(s_in)
+        s_comp.wait_event(uploaded)
+        for n in wl.host_inputs:
+            wl.tensors[n] = cur[n]
         out = wl.run()
-        out_host.copy_(out, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(s_comp)
+        comp_done[i & 1] = ev
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev)
+            if out_done is not None:
+                s_out.wait_event(out_done)
+            out.record_stream(s_out)
+            out_host.copy_(out, non_blocking=True)
+            out_done = torch.cuda.Event()
+            out_done.record(s_out)
 
-    for _ in range(max(1, warmup)):
-        step()
+    for i in range(max(2, warmup)):
+        step(i)
     torch.cuda.synchronize()
     barrier(world)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
+    e0.record(s_comp)
+    s_in.wait_event(e0)
+    s_out.wait_event(e0)
+    for i in range(steps):
+        step(i)
+    s_comp.wait_stream(s_in)
+    s_comp.wait_stream(s_out)
+    e1.record(s_comp)
     torch.cuda.synchronize()
     barrier(world)
+    for n in wl.host_inputs:
+        wl.tensors[n] = dev_sets[0][n]
     return e0.elapsed_time(e1) / steps, h2d, d2h
 
 
