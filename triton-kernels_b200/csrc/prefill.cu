@@ -5,16 +5,17 @@
 //
 // Persistent kernel, one CTA per SM.  A work item is two 128-row query tiles ("slots") that share a KV head.
 // Warp roles (576 threads):
-//   warps 0-15 : four softmax warpgroups, (slot 0 | slot 1) x (score columns 0-63 | 64-127); thread i of a
-//                warpgroup owns query row i of its slot and 64 of the row's 128 scores
+//   warps 0-15 : softmax; warp w serves slot w / 8, TMEM lane quadrant w % 4 and 16 of its 32 query rows.  Tensor
+//                memory is read in the 16x256b layout, which puts the 128 scores of a row into the four threads of
+//                a quad: row maxima and sums are two shuffles away, nothing is exchanged through shared memory
 //   warp  16   : scheduler + TMA producer (draws work items, loads Q, then K_j / V_j tiles of 128 keys through a
 //                4-buffer ring; paged caches are fetched one page-sized box at a time from the block table)
 //   warp  17   : tcgen05.mma issuer and TMEM owner; the warp stays converged, one elected lane issues
 // TMEM (512 columns): S0 | S1 | O0 | O1.  Per KV tile j and slot s:
 //   S_s = Q_s K_j^T   (SS MMA, 128x128xD)            -> commit s_full[s]
-//   the slot's warpgroups read S_s, mask, keep a running max / sum in the exp2 domain (the two threads of a row
-//   agree on the max through shared memory), rescale O_s in TMEM only when the max moved by more than 2^8, and
-//   write P_s as packed 16-bit over part of S_s                      -> arrive p_ready[s]
+//   the slot's warps read S_s, mask, keep a running max / sum per row in the exp2 domain, rescale O_s in TMEM only
+//   when the max moved by more than 2^8, and write P_s as packed 16-bit (16x128b layout) over the first 64 columns
+//   of S_s                                                            -> arrive p_ready[s]
 //   O_s += P_s V_j    (TS MMA, A from TMEM, V is the MN-major B operand) -> commit o_done[s]
 // The two slots are interleaved so that one slot's softmax overlaps the other's MMAs.  At the end of an item the
 // MMA warp issues the first score tile of the next item behind the last PVs, and the softmax warps finish the old
@@ -95,13 +96,11 @@ struct __align__(8) Control {
   uint64_t s_full[kSlots];
   uint64_t p_ready[kSlots];
   uint64_t o_done[kSlots];
-  uint64_t xchg_bar[kSlots];
   uint64_t o_free[kSlots];
   uint64_t sched_full[2];
   uint64_t sched_empty[2];
   int sched_item[2];
   ItemWork sched_work[2];   // decoded by the scheduler, read by every other warp
-  float xchg[2][kSlots][2][kBM];   // [tile parity][slot][column half][row]: row max / final row sum exchange
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -272,7 +271,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(smem_u32(&ctrl->s_full[s]), 1);
       mbar_init(smem_u32(&ctrl->p_ready[s]), 2 * kBM);
       mbar_init(smem_u32(&ctrl->o_done[s]), 1);
-      mbar_init(smem_u32(&ctrl->xchg_bar[s]), 2 * kBM);
       mbar_init(smem_u32(&ctrl->o_free[s]), 8);          // one arrival per softmax warp of the slot
     }
     for (int i = 0; i < 2; ++i) {
@@ -456,8 +454,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mma_commit_lead(smem_u32(&ctrl->s_full[s]), lead);
     };
     auto issue_pv = [&](int s, uint64_t vb, bool first) {
-      // O_s (+)= P_s V : A = packed 16-bit P in TMEM, B = V, MN-major.  P of columns 0-63 sits in TMEM columns
-      // 0-31 of the S tile and P of columns 64-127 in TMEM columns 64-95 (each warpgroup writes over its own half).
+      // O_s (+)= P_s V : A = packed 16-bit P in the first 64 TMEM columns of the S tile, B = V, MN-major
       mma_ts_batch8(tmem_O[s], tmem_S[s], vb, idesc_o, first ? 0u : 1u, lead);
       mma_commit_lead(smem_u32(&ctrl->o_done[s]), lead);
     };
@@ -606,22 +603,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #endif
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
   } else if (warp < kSoftmaxWarps) {
-    // =========================== softmax warpgroups ===========================
-    // Warpgroup g = warp / 4 serves slot (g & 1) and the column half (g >> 1) of its score tile: thread `row`
-    // of the warpgroup owns 64 of the 128 scores of query row `row`; the two threads of a row agree on the row
-    // max through shared memory (an mbarrier, so the wait is bounded) and keep separate partial row sums.
-    const int g = warp >> 2;
-    const int s = g & 1;
-    const int half = g >> 1;
-    const int row = (warp & 3) * 32 + lane;             // 0..127 inside the slot
-    const uint32_t lane_off = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tSh = tmem + s * kBN + lane_off + half * kHalf;
-    constexpr int kOCols = D / 2;                       // O columns rescaled / written out by this thread
-    const uint32_t tOh = tmem + 2 * kBN + s * D + lane_off + half * kOCols;
+    // =========================== softmax warps ===========================
+    // Warp w serves slot w / 8, the TMEM lane quadrant w % 4 (the only lanes it may touch) and, inside the quadrant,
+    // the sixteen query rows 16 h .. 16 h + 15 with h = (w / 4) % 2.  Tensor memory is read in the 16x256b layout:
+    // thread t holds the columns 8 i + 2 (t % 4) + {0, 1} (i = 0 .. 15) of row A = t / 4 and of row B = A + 8, so the
+    // 128 scores of a row live in the four threads of a quad and row maxima and sums are two shuffles away: no
+    // exchange through shared memory, no barrier inside a tile.
+    const int s = warp >> 3;
+    const int qd = warp & 3;
+    const int h = (warp >> 2) & 1;
+    const int q = lane & 3;
+    const int rowA = qd * 32 + h * 16 + (lane >> 2);    // 0..127 inside the slot; row B = row A + 8
+    const uint32_t lane_off = static_cast<uint32_t>(qd * 32 + h * 16) << 16;
+    const uint32_t tS = tmem + s * kBN + lane_off;
+    const uint32_t tO = tmem + 2 * kBN + s * D + lane_off;
     const float sl2 = p.scale_log2;
-    const bool tracer = (warp & 3) == 0 && half == 0;
+    const bool tracer = (warp & 7) == 0;
     int tile_cnt = 0;     // score tiles of this slot consumed so far (barrier phases run across items)
-    int xchg_cnt = 0;     // exchanges done so far
     bool ok = true;
     // The epilogue of an item is finished lazily: O is read out of tensor memory at the end of the first score
     // tile of the slot's next item (its PV is the first thing that overwrites O) and the global stores are issued
@@ -630,27 +628,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     bool pend_acc = false;    // ... and it has an accumulator (false: the slot had no keys, the output is zero)
     int pend_phase = 0;       // o_done phase of its last PV
     int pend_rows = 0;        // rows of the tile that exist in the sequence
-    float pend_l = 0.f;       // row sum
-    long long pend_off = 0;   // element offset of this thread's first output column
-    constexpr bool kStoreLate = !std::is_same<OutT, float>::value;   // 16-bit output fits in registers meanwhile
-    auto store_row = [&](int c, const uint32_t (&ov)[32], float inv) {
-      // fp32 output: written straight from the accumulator chunk
-      float* out = static_cast<float*>(p.out) + pend_off + c * 32;
-      if (p.out_align32) {
-#pragma unroll
-        for (int q8 = 0; q8 < 4; ++q8) {
-          uint32_t u[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) u[i] = __float_as_uint(__uint_as_float(ov[q8 * 8 + i]) * inv);
-          st_global_v8(out + q8 * 8, u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
-        }
-      } else {
-#pragma unroll
-        for (int q4 = 0; q4 < 8; ++q4)
-          *reinterpret_cast<float4*>(out + q4 * 4) =
-              make_float4(__uint_as_float(ov[q4 * 4 + 0]) * inv, __uint_as_float(ov[q4 * 4 + 1]) * inv,
-                          __uint_as_float(ov[q4 * 4 + 2]) * inv, __uint_as_float(ov[q4 * 4 + 3]) * inv);
-      }
+    float pend_la = 0.f, pend_lb = 0.f;   // row sums of rows A and B
+    long long pend_off = 0;   // element offset of row A's first output column
+    long long pend_stride = 0;   // elements between consecutive rows of the output
+    constexpr bool k16 = !std::is_same<OutT, float>::value;
+    auto quad_max = [](float v) {
+      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+      return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+    };
+    auto quad_sum = [](float v) {
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      return v + __shfl_xor_sync(0xffffffffu, v, 2);
     };
     // 4 x 4 transpose of two-word items across the four threads of a quad (lane bits 0-1): on return item m of
     // thread q is what item q of thread m was.  x[2m], x[2m+1] are the words of item m.
@@ -677,37 +665,43 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
     };
-    // 16-bit output at head_dim 128: this thread's 64 columns of a row are exactly one 128-byte line, so the
-    // accumulator is read in the 16x256b layout (a quad holds 8 consecutive columns), transposed inside each quad
-    // and stored as full lines, 8 rows per store instruction instead of one 32-byte piece of 32 different lines.
-    constexpr bool kLineStores = kStoreLate && D == 128;
     auto flush = [&](bool hand_over) -> bool {
       if (pend_acc) {
         if (!warp_wait(smem_u32(&ctrl->o_done[s]), pend_phase)) return false;
       }
       tc_fence_after();
-      const float inv = pend_l > 0.f ? 1.f / pend_l : 0.f;
-      if constexpr (kLineStores) {
-        uint32_t line[2][2][8];     // [16-row half][row r / row r + 8][32 bytes of the row's line]
-        const int rq = lane >> 2, q = lane & 3;
+      const float inv_a = pend_la > 0.f ? 1.f / pend_la : 0.f;
+      const float inv_b = pend_lb > 0.f ? 1.f / pend_lb : 0.f;
+      auto o_is_free = [&]() {
+        // O has been read out: the MMA warp may start the next item's PV into it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->o_free[s]));
+      };
+      auto hand = [&]() {
+        if (hand_over) {
+          // this tile's P goes to the MMA warp before the stores are issued
+          tc_fence_before();
+          mbar_arrive(smem_u32(&ctrl->p_ready[s]));
+        }
+      };
+      constexpr int kChunksO = D / 64;
+      if constexpr (k16) {
+        // 16-bit output: 64 columns of a row are one 128-byte line.  A quad holds 8 consecutive columns per group;
+        // transposed inside the quad, every thread owns 32 contiguous bytes and a store instruction writes 8 full
+        // lines instead of one piece of 32 different lines.
+        uint32_t line[kChunksO][2][8];     // [64-column chunk][row A / row B][32 bytes of the row's line]
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int c = 0; c < kChunksO; ++c) {
           uint32_t v[32];
           if (pend_acc) {
-            tmem_ld_16x256b_x8(tOh + (static_cast<uint32_t>(16 * h) << 16), v);
+            tmem_ld_16x256b_x8(tO + c * 64, v);
             tmem_wait_ld();
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = 0u;
           }
-          if (h == 1) {
-            // O has been read out: the MMA warp may start the next item's PV into it
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctrl->o_free[s]));
-          }
-          const float inv_a = __shfl_sync(0xffffffffu, inv, rq + 16 * h);
-          const float inv_b = __shfl_sync(0xffffffffu, inv, rq + 16 * h + 8);
+          if (c == kChunksO - 1) o_is_free();
           uint32_t a[8], b[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -719,26 +713,18 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           quad_transpose(b);
 #pragma unroll
           for (int m = 0; m < 4; ++m) {
-            line[h][0][m] = a[2 * m];  line[h][0][4 + m] = a[2 * m + 1];
-            line[h][1][m] = b[2 * m];  line[h][1][4 + m] = b[2 * m + 1];
+            line[c][0][m] = a[2 * m];  line[c][0][4 + m] = a[2 * m + 1];
+            line[c][1][m] = b[2 * m];  line[c][1][4 + m] = b[2 * m + 1];
           }
         }
-        if (hand_over) {
-          // this tile's P goes to the MMA warp before the stores are issued
-          tc_fence_before();
-          mbar_arrive(smem_u32(&ctrl->p_ready[s]));
-        }
-        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 3);
-        const long long row_stride = p.layout == B200ATTN_RAGGED ? static_cast<long long>(p.q_heads) * D : D;
-        const int warp_row0 = (warp & 3) * 32;
+        hand();
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int ab = 0; ab < 2; ++ab) {
+          if (rowA + 8 * ab < pend_rows) {
 #pragma unroll
-          for (int ab = 0; ab < 2; ++ab) {
-            const int r = warp_row0 + rq + 16 * h + 8 * ab;     // row of the slot this thread now stores a piece of
-            if (r < pend_rows) {
-              T* out = static_cast<T*>(p.out) + pend_off + (r - row) * row_stride + q * 16;
-              const uint32_t (&u)[8] = line[h][ab];
+            for (int c = 0; c < kChunksO; ++c) {
+              T* out = static_cast<T*>(p.out) + pend_off + ab * 8 * pend_stride + c * 64 + q * 16;
+              const uint32_t (&u)[8] = line[c][ab];
               if (p.out_align32) {
                 st_global_v8(out, u[0], u[1], u[2], u[3], u[4], u[5], u[6], u[7]);
               } else {
@@ -748,59 +734,27 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
           }
         }
-        pend = false;
-        return true;
-      }
-      uint32_t outp[kStoreLate ? kOCols / 2 : 1];
+      } else {
+        // fp32 output: a thread holds two consecutive columns per group, a quad 32 contiguous bytes of a row
 #pragma unroll
-      for (int c = 0; c < kOCols / 32; ++c) {
-        uint32_t ov[32];
-        if (pend_acc) {
-          tmem_ld32(tOh + c * 32, ov);
-          tmem_wait_ld();
-        } else {
+        for (int c = 0; c < kChunksO; ++c) {
+          uint32_t v[32];
+          if (pend_acc) {
+            tmem_ld_16x256b_x8(tO + c * 64, v);
+            tmem_wait_ld();
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = 0u;
-        }
-        if (c == kOCols / 32 - 1) {
-          // O has been read out: the MMA warp may start the next item's PV into it
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&ctrl->o_free[s]));
-        }
-        if constexpr (kStoreLate) {
+            for (int i = 0; i < 32; ++i) v[i] = 0u;
+          }
+          if (c == kChunksO - 1) { o_is_free(); hand(); }
+          float* out = static_cast<float*>(p.out) + pend_off + c * 64 + q * 2;
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            outp[c * 16 + i] = ElemTraits<T>::pack2(__uint_as_float(ov[2 * i]) * inv, __uint_as_float(ov[2 * i + 1]) * inv);
-        } else {
-          if (row < pend_rows) store_row(c, ov, inv);
-        }
-      }
-      if (hand_over) {
-        // this tile's P goes to the MMA warp before the stores are issued
-        tc_fence_before();
-        mbar_arrive(smem_u32(&ctrl->p_ready[s]));
-      }
-      // one thread writes consecutive output columns of its row; 32-byte stores (one full sector per lane) when
-      // the output pointer allows, since the rows of a warp never share a 128-byte line
-      if constexpr (kStoreLate) {
-        if (row < pend_rows) {
-          T* out = static_cast<T*>(p.out) + pend_off;
-#pragma unroll
-          for (int c = 0; c < kOCols / 32; ++c) {
-            if (p.out_align32) {
-#pragma unroll
-              for (int h8 = 0; h8 < 2; ++h8) {
-                const int b = c * 16 + h8 * 8;
-                st_global_v8(out + c * 32 + h8 * 16, outp[b], outp[b + 1], outp[b + 2], outp[b + 3], outp[b + 4], outp[b + 5],
-                             outp[b + 6], outp[b + 7]);
-              }
-            } else {
-#pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4)
-                *reinterpret_cast<uint4*>(out + c * 32 + q4 * 8) =
-                    make_uint4(outp[c * 16 + q4 * 4], outp[c * 16 + q4 * 4 + 1], outp[c * 16 + q4 * 4 + 2], outp[c * 16 + q4 * 4 + 3]);
-            }
+          for (int i = 0; i < 8; ++i) {
+            if (rowA < pend_rows)
+              *reinterpret_cast<float2*>(out + i * 8) = make_float2(__uint_as_float(v[4 * i]) * inv_a, __uint_as_float(v[4 * i + 1]) * inv_a);
+            if (rowA + 8 < pend_rows)
+              *reinterpret_cast<float2*>(out + 8 * pend_stride + i * 8) =
+                  make_float2(__uint_as_float(v[4 * i + 2]) * inv_b, __uint_as_float(v[4 * i + 3]) * inv_b);
           }
         }
       }
@@ -813,132 +767,151 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int item = ctrl->sched_item[k & 1];
       if (item < 0) break;
       // (the few fields needed are read from shared memory where they are used, not held across the tile loop)
-      if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 7);
       const ItemWork& w = ctrl->sched_work[k & 1];
       const int n = w.nkv[s];
       const int m0s = w.m0[s];
       const int len_k = w.len_k;
-      const int row_abs = m0s + row;                    // query index inside the sequence
+      const int row_abs = m0s + rowA;                   // query index of row A inside the sequence (row B: + 8)
       if (pend && n == 0) {
         // no score tile in this item to hang the previous item's epilogue on
         ok = flush(false);
         if (!ok) break;
       }
-      float m_used = -INFINITY;   // exponent reference currently baked into O and l
-      float l = 0.f;              // partial row sum over this thread's columns
+      float m_a = -INFINITY, m_b = -INFINITY;   // exponent references currently baked into O and l
+      float l_a = 0.f, l_b = 0.f;               // partial row sums over this thread's columns
       for (int j = 0; j < n; ++j, ++tile_cnt) {
         if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 0);
         ok = warp_wait(smem_u32(&ctrl->s_full[s]), tile_cnt & 1);
         if (!ok || *abort_flag) { ok = false; break; }
         tc_fence_after();
         if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 1);
-        // masking is needed only on the tile that holds the sequence end or the causal diagonal
-        int limit = len_k - 1 - j * kBN - half * kHalf;
-        if (p.is_causal) limit = min(limit, row_abs - j * kBN - half * kHalf);
-        const bool masked = limit < kHalf - 1;
-        float mx;
+        // masking is needed only on the tile that holds the sequence end or the causal diagonal; `lim` is the last
+        // visible column of the tile for the row
+        int lim_a = len_k - 1 - j * kBN, lim_b = lim_a;
+        if (p.is_causal) { lim_a = min(lim_a, row_abs - j * kBN); lim_b = min(lim_b, row_abs + 8 - j * kBN); }
+        const bool masked = min(lim_a, lim_b) < kBN - 1;
+        float mx_a, mx_b;
         {
-          // pass 1: the max of this thread's 64 scores (they are read again in pass 2; holding them across the
-          // exchange below would cost 64 registers per thread)
-          uint32_t ca[32], cb[32];
-          tmem_ld32(tSh, ca);
-          tmem_ld32(tSh + 32, cb);
+          // pass 1: row maxima (the scores are read again in pass 2: 64 registers cannot be held across it)
+          uint32_t v[64];
+          tmem_ld_16x256b_x16(tS, v);
           tmem_wait_ld();
           if (masked) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (i > limit) ca[i] = 0xff800000u;        // -inf
-              if (32 + i > limit) cb[i] = 0xff800000u;
+            for (int i = 0; i < 16; ++i) {
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int col = 8 * i + 2 * q + e;
+                if (col > lim_a) v[4 * i + e] = 0xff800000u;        // -inf
+                if (col > lim_b) v[4 * i + 2 + e] = 0xff800000u;
+              }
             }
           }
-          float ma = max3(__uint_as_float(ca[0]), __uint_as_float(ca[1]), __uint_as_float(ca[2]));
-          float mb = max3(__uint_as_float(cb[0]), __uint_as_float(cb[1]), __uint_as_float(cb[2]));
+          float a0 = fmaxf(__uint_as_float(v[0]), __uint_as_float(v[1]));
+          float b0 = fmaxf(__uint_as_float(v[2]), __uint_as_float(v[3]));
 #pragma unroll
-          for (int i = 3; i + 1 < 32; i += 2) {
-            ma = max3(ma, __uint_as_float(ca[i]), __uint_as_float(ca[i + 1]));
-            mb = max3(mb, __uint_as_float(cb[i]), __uint_as_float(cb[i + 1]));
+          for (int i = 1; i < 16; ++i) {
+            a0 = max3(a0, __uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]));
+            b0 = max3(b0, __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
           }
-          mx = max3(ma, mb, fmaxf(__uint_as_float(ca[31]), __uint_as_float(cb[31])));
+          mx_a = quad_max(a0);
+          mx_b = quad_max(b0);
         }
-        // exchange the half-row maxima
-        ctrl->xchg[xchg_cnt & 1][s][half][row] = mx;
-        mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
-        ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), xchg_cnt & 1);
-        if (!ok) break;
-        mx = fmaxf(mx, ctrl->xchg[xchg_cnt & 1][s][half ^ 1][row]);
-        ++xchg_cnt;
         if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 2);
-        const float m_new = fmaxf(m_used, mx * sl2);
-        const bool need = (m_new - m_used) > kRescaleThreshold;   // false for NaN / (-inf)-(-inf)
-        float alpha = 1.f;
-        if (need) { alpha = fast_exp2(m_used - m_new); m_used = m_new; l *= alpha; }
-        if (j > 0 && __any_sync(0xffffffffu, need)) {
+        const float mn_a = fmaxf(m_a, mx_a * sl2), mn_b = fmaxf(m_b, mx_b * sl2);
+        const bool need_a = (mn_a - m_a) > kRescaleThreshold;   // false for NaN / (-inf)-(-inf)
+        const bool need_b = (mn_b - m_b) > kRescaleThreshold;
+        float alpha_a = 1.f, alpha_b = 1.f;
+        if (need_a) { alpha_a = fast_exp2(m_a - mn_a); m_a = mn_a; l_a *= alpha_a; }
+        if (need_b) { alpha_b = fast_exp2(m_b - mn_b); m_b = mn_b; l_b *= alpha_b; }
+        if (j > 0 && __any_sync(0xffffffffu, need_a || need_b)) {
           // PV(j-1) has landed in O once S(j) is visible (the MMAs complete in issue order); waiting on its
           // barrier phase is then immediate, and skipping the wait on other tiles is harmless because the
-          // barrier can never run two phases ahead of this warpgroup
+          // barrier can never run two phases ahead of this warp
           ok = warp_wait(smem_u32(&ctrl->o_done[s]), (tile_cnt - 1) & 1);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll
-          for (int c = 0; c < kOCols / 32; ++c) {
+          for (int c = 0; c < D / 64; ++c) {
             uint32_t ov[32];
-            tmem_ld32(tOh + c * 32, ov);
+            tmem_ld_16x256b_x8(tO + c * 64, ov);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            tmem_st32(tOh + c * 32, ov);
+            for (int i = 0; i < 8; ++i) {
+              ov[4 * i] = __float_as_uint(__uint_as_float(ov[4 * i]) * alpha_a);
+              ov[4 * i + 1] = __float_as_uint(__uint_as_float(ov[4 * i + 1]) * alpha_a);
+              ov[4 * i + 2] = __float_as_uint(__uint_as_float(ov[4 * i + 2]) * alpha_b);
+              ov[4 * i + 3] = __float_as_uint(__uint_as_float(ov[4 * i + 3]) * alpha_b);
+            }
+            tmem_st_16x256b_x8(tO + c * 64, ov);
           }
         }
         if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 4);
-        const float m_eff = (m_used == -INFINITY) ? 0.f : m_used;
-        const float neg_m = -m_eff;
-        uint64_t rs2 = pack_f2(0.f, 0.f);
-        const uint64_t sl2_2 = pack_f2(sl2, sl2), negm_2 = pack_f2(neg_m, neg_m);
-        auto chunk_exp = [&](int c) {
+        const float neg_a = (m_a == -INFINITY) ? 0.f : -m_a, neg_b = (m_b == -INFINITY) ? 0.f : -m_b;
+        uint64_t rs_a = pack_f2(0.f, 0.f), rs_b = pack_f2(0.f, 0.f);
+        const uint64_t sl2_2 = pack_f2(sl2, sl2), nega_2 = pack_f2(neg_a, neg_a), negb_2 = pack_f2(neg_b, neg_b);
+        auto exp_pair = [&](uint32_t x0, uint32_t x1, uint64_t neg2, uint64_t& rs, bool emulate) -> uint32_t {
+          const uint64_t t2 = fma_f2(pack_f2(__uint_as_float(x0), __uint_as_float(x1)), sl2_2, neg2);
+          float p0, p1;
+          if (emulate) {
+            // 2^t = 2^n * 2^r with n = round(t), r in [-0.5, 0.5]; n is read off the magic-number sum
+            float a, b;
+            unpack_f2(t2, a, b);
+            const uint64_t tc = pack_f2(fmaxf(a, -126.f), fmaxf(b, -126.f));
+            const uint64_t tm = add_f2(tc, pack_f2(12582912.f, 12582912.f));
+            const uint64_t nf = add_f2(tm, pack_f2(-12582912.f, -12582912.f));
+            const uint64_t r = fma_f2(nf, pack_f2(-1.f, -1.f), tc);
+            uint64_t pq = fma_f2(r, pack_f2(0.055171482f, 0.055171482f), pack_f2(0.2426109f, 0.2426109f));
+            pq = fma_f2(pq, r, pack_f2(0.69326097f, 0.69326097f));
+            pq = fma_f2(pq, r, pack_f2(0.99992812f, 0.99992812f));
+            float q0, q1, m0f, m1f;
+            unpack_f2(pq, q0, q1);
+            unpack_f2(tm, m0f, m1f);
+            p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(m0f) << 23));
+            p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(m1f) << 23));
+          } else {
+            float a, b;
+            unpack_f2(t2, a, b);
+            p0 = fast_exp2(a);
+            p1 = fast_exp2(b);
+          }
+          rs = add_f2(rs, pack_f2(p0, p1));
+          return ElemTraits<T>::pack2(p0, p1);
+        };
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          // pass 2, 64 columns at a time: exponentials, row sums, P as packed 16-bit in the 16x128b layout (the pair
+          // of columns 8 i + 2 q + {0, 1} is packed column 4 i + q), written over score columns that are done with
           uint32_t v[32];
-          tmem_ld32(tSh + c * 32, v);
+          tmem_ld_16x256b_x8(tS + c * 64, v);
           tmem_wait_ld();
           if (masked) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) if (c * 32 + i > limit) v[i] = 0xff800000u;   // -inf
+            for (int i = 0; i < 8; ++i) {
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int col = c * 64 + 8 * i + 2 * q + e;
+                if (col > lim_a) v[4 * i + e] = 0xff800000u;        // -inf
+                if (col > lim_b) v[4 * i + 2 + e] = 0xff800000u;
+              }
+            }
           }
           uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const uint64_t t2 = fma_f2(pack_f2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), sl2_2, negm_2);
-            float p0, p1;
-            if ((i & 3) < kExpEmuOf4) {
-              // 2^t = 2^n * 2^r with n = round(t), r in [-0.5, 0.5]; n is read off the magic-number sum
-              float a, b;
-              unpack_f2(t2, a, b);
-              const uint64_t tc = pack_f2(fmaxf(a, -126.f), fmaxf(b, -126.f));
-              const uint64_t tm = add_f2(tc, pack_f2(12582912.f, 12582912.f));
-              const uint64_t nf = add_f2(tm, pack_f2(-12582912.f, -12582912.f));
-              const uint64_t r = fma_f2(nf, pack_f2(-1.f, -1.f), tc);
-              uint64_t q = fma_f2(r, pack_f2(0.055171482f, 0.055171482f), pack_f2(0.2426109f, 0.2426109f));
-              q = fma_f2(q, r, pack_f2(0.69326097f, 0.69326097f));
-              q = fma_f2(q, r, pack_f2(0.99992812f, 0.99992812f));
-              float q0, q1, m0f, m1f;
-              unpack_f2(q, q0, q1);
-              unpack_f2(tm, m0f, m1f);
-              p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(m0f) << 23));
-              p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(m1f) << 23));
-            } else {
-              float a, b;
-              unpack_f2(t2, a, b);
-              p0 = fast_exp2(a);
-              p1 = fast_exp2(b);
-            }
-            rs2 = add_f2(rs2, pack_f2(p0, p1));
-            pk[i] = ElemTraits<T>::pack2(p0, p1);
+          for (int i = 0; i < 8; ++i) {
+            const bool emu = (i & 3) < kExpEmuOf4;
+            pk[2 * i] = exp_pair(v[4 * i], v[4 * i + 1], nega_2, rs_a, emu);
+            pk[2 * i + 1] = exp_pair(v[4 * i + 2], v[4 * i + 3], negb_2, rs_b, emu);
           }
-          tmem_st16(tSh + c * 16, pk);
-        };
-        chunk_exp(0);
-        chunk_exp(1);
-        float rs0, rs1;
-        unpack_f2(rs2, rs0, rs1);
-        l += rs0 + rs1;
+          tmem_st_16x128b_x8(tS + c * 32, pk);
+        }
+        {
+          float r0, r1;
+          unpack_f2(rs_a, r0, r1);
+          l_a += r0 + r1;
+          unpack_f2(rs_b, r0, r1);
+          l_b += r0 + r1;
+        }
         if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 5);
         tmem_wait_st();
         if (pend) {
@@ -954,14 +927,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       // ---------------- the item's epilogue becomes pending ----------------
       if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 0);
-      // total row sum = this thread's partial + its partner's
-      ctrl->xchg[xchg_cnt & 1][s][half][row] = l;
-      mbar_arrive(smem_u32(&ctrl->xchg_bar[s]));
-      ok = warp_wait(smem_u32(&ctrl->xchg_bar[s]), xchg_cnt & 1);
-      if (!ok) break;
-      l += ctrl->xchg[xchg_cnt & 1][s][half ^ 1][row];
-      ++xchg_cnt;
-      if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 1);
       const int len_q = w.len_q;
       const bool slot_live = w.valid && m0s < len_q;
       const long long qrow0 = w.q_row0[s];
@@ -970,10 +935,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       pend_acc = n > 0;
       pend_phase = (tile_cnt - 1) & 1;
       pend_rows = slot_live ? min(kBM, len_q - m0s) : 0;
-      pend_l = l;
-      if (p.layout == B200ATTN_RAGGED) pend_off = ((qrow0 + m0s + row) * p.q_heads + qhead) * D;
-      else pend_off = (qrow0 + m0s + row) * D;
-      pend_off += half * kOCols;
+      pend_la = quad_sum(l_a);
+      pend_lb = quad_sum(l_b);
+      if (p.layout == B200ATTN_RAGGED) {
+        pend_stride = static_cast<long long>(p.q_heads) * D;
+        pend_off = ((qrow0 + m0s + rowA) * p.q_heads + qhead) * D;
+      } else {
+        pend_stride = D;
+        pend_off = (qrow0 + m0s + rowA) * D;
+      }
       __syncwarp();
       if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 2);
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));

@@ -34,17 +34,30 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
-// Bounded wait: gives up after ~2^31 clock cycles (about a second) and returns false.
+// Bounded wait: returns false when the phase has not completed after about a second.  The loop lives in one asm
+// block - a completed phase costs the caller two instructions, which matters for a warp that has to share its issue
+// slots with busy neighbours - and every failed try suspends the thread in hardware for up to the hinted time, so
+// the iteration limit (2^22 tries of up to 1 us each) bounds the wait: between a tenth of a second and a few seconds.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i) {
-      if (mbar_try_wait(bar, parity)) return true;
-    }
-    if (clock64() - t0 > (1ll << 31)) return false;
-  }
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .u32 n;\n\t"
+      "mov.u32 n, 0;\n\t"
+      "B200ATTN_WAIT_LOOP:\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "@p bra B200ATTN_WAIT_DONE;\n\t"
+      "add.u32 n, n, 1;\n\t"
+      "setp.lt.u32 p, n, 4194304;\n\t"
+      "@p bra B200ATTN_WAIT_LOOP;\n\t"
+      "mov.u32 %0, 0;\n\t"
+      "bra B200ATTN_WAIT_END;\n\t"
+      "B200ATTN_WAIT_DONE:\n\t"
+      "mov.u32 %0, 1;\n\t"
+      "B200ATTN_WAIT_END:\n\t}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
 }
 
 // ------------------------------ proxies / fences ----------------------------
@@ -122,6 +135,32 @@ __device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t (&r)
         "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr)
+      : "memory");
+}
+// More accesses in the 16-lane layouts.  16x256b (see tmem_ld_16x256b_x8): thread t holds, per group i of 8 columns,
+// lane t / 4, columns 8i + 2 (t % 4) + {0, 1} in r[4i], r[4i+1] and lane t / 4 + 8 in r[4i+2], r[4i+3].
+// 16x128b: thread t holds, per group i of 4 columns, lane t / 4, column 4i + t % 4 in r[2i] and lane t / 4 + 8 in
+// r[2i+1] - which is where the packed pair of the 16x256b columns 8i + 2 (t % 4) + {0, 1} belongs.
+__device__ __forceinline__ void tmem_ld_16x256b_x16(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x256b.x8.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -297,8 +336,7 @@ __device__ __forceinline__ void mma_ss_batch(uint32_t d_tmem, uint64_t a_desc, u
   "add.u32 a1, %1, " #AOFF ";\n\tadd.s64 b1, %2, " #BOFF ";\n\t"                                \
   "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, t;\n\t"
 
-// Eight k-steps (128 keys) of O += P V: A is packed 16-bit P in tensor memory, keys 0-63 in columns [0,32) and
-// keys 64-127 in columns [64,96) of `a_tmem`; B is an MN-major 128-row V tile, 16 rows (2 KiB) per k-step.
+// Eight k-steps (128 keys) of O += P V: A is packed 16-bit P in the 64 tensor-memory columns at `a_tmem`; B is an MN-major 128-row V tile, 16 rows (2 KiB) per k-step.
 __device__ __forceinline__ void mma_ts_batch8(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                               uint32_t accumulate_first, uint32_t lead) {
   asm volatile(
@@ -306,7 +344,7 @@ __device__ __forceinline__ void mma_ts_batch8(uint32_t d_tmem, uint32_t a_tmem, 
       "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, 0, 0;\n\tsetp.ne.b32 e, %5, 0;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
       B200ATTN_TS_STEP(8, 128) B200ATTN_TS_STEP(16, 256) B200ATTN_TS_STEP(24, 384)
-      B200ATTN_TS_STEP(64, 512) B200ATTN_TS_STEP(72, 640) B200ATTN_TS_STEP(80, 768) B200ATTN_TS_STEP(88, 896)
+      B200ATTN_TS_STEP(32, 512) B200ATTN_TS_STEP(40, 640) B200ATTN_TS_STEP(48, 768) B200ATTN_TS_STEP(56, 896)
       "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(lead) : "memory");
 }
 #undef B200ATTN_TS_STEP
