@@ -8,8 +8,9 @@
 //   warps 0-15 : softmax; warp w serves slot w / 8, TMEM lane quadrant w % 4 and 16 of its 32 query rows.  Tensor
 //                memory is read in the 16x256b layout, which puts the 128 scores of a row into the four threads of
 //                a quad: row maxima and sums are two shuffles away, nothing is exchanged through shared memory
-//   warp  16   : scheduler + TMA producer (draws work items, loads Q, then K_j / V_j tiles of 128 keys through a
-//                4-buffer ring; paged caches are fetched one page-sized box at a time from the block table)
+//   warp  16   : scheduler + TMA producer (draws work items, loads Q, then the K_j / V_j tiles of 128 keys in pairs
+//                {V_j, K_j+1} through two stages of two buffers; paged caches are fetched one page-sized box at a
+//                time from the block table)
 //   warp  17   : tcgen05.mma issuer and TMEM owner; the warp stays converged, one elected lane issues
 // TMEM (512 columns): S0 | S1 | O0 | O1.  Per KV tile j and slot s:
 //   S_s = Q_s K_j^T   (SS MMA, 128x128xD)            -> commit s_full[s]
@@ -43,7 +44,8 @@ constexpr int kBM = 128;           // query rows per slot
 constexpr int kBN = 128;           // keys per K/V tile
 constexpr int kHalf = 64;          // keys per softmax / MMA step
 constexpr int kSlots = 2;
-constexpr int kRing = 4;           // K/V ring buffers (K_j, V_j alternate)
+constexpr int kRing = 4;           // K/V tile buffers: two stages of one V buffer and one K buffer
+constexpr int kStages = 2;         // a stage holds the pair {V_j, K_j+1}: one barrier to wait for, one to release
 constexpr int kSoftmaxWarps = 16;  // 4 warpgroups: (slot 0 | slot 1) x (columns 0-63 | 64-127)
 constexpr int kThreads = 576;
 constexpr int kProducerWarp = 16;
@@ -91,8 +93,8 @@ struct ItemWork {
 struct __align__(8) Control {
   uint64_t q_full;
   uint64_t q_empty;
-  uint64_t kv_full[kRing];
-  uint64_t kv_empty[kRing];
+  uint64_t kv_full[kStages];     // pair {V_j, K_j+1} (or K_0 alone / V_last alone) has landed
+  uint64_t kv_empty[kStages];    // ... has been consumed by the MMAs
   uint64_t s_full[kSlots];
   uint64_t p_ready[kSlots];
   uint64_t o_done[kSlots];
@@ -266,7 +268,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (tid == 0) {
     mbar_init(smem_u32(&ctrl->q_full), 1);
     mbar_init(smem_u32(&ctrl->q_empty), 1);
-    for (int i = 0; i < kRing; ++i) { mbar_init(smem_u32(&ctrl->kv_full[i]), 1); mbar_init(smem_u32(&ctrl->kv_empty[i]), 1); }
+    for (int i = 0; i < kStages; ++i) { mbar_init(smem_u32(&ctrl->kv_full[i]), 1); mbar_init(smem_u32(&ctrl->kv_empty[i]), 1); }
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(smem_u32(&ctrl->s_full[s]), 1);
       mbar_init(smem_u32(&ctrl->p_ready[s]), 2 * kBM);
@@ -295,8 +297,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // =========================== scheduler + TMA producer ===========================
     if (lane == 0) { prefetch_tensormap(&tm_q); prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); }
     bool ok = true;
-    int ring_e = 0;       // K/V ring entries issued so far (K_j, V_j alternate), across items
-    int ring_lo = 0;      // first entry of the current item
+    int pair_e = 0;       // K/V pairs issued so far, across items
+    int pair_lo = 0;      // first pair of the current item
     for (int k = 0; ok; ++k) {
       if (k >= 2) {
         ok = warp_wait(smem_u32(&ctrl->sched_empty[k & 1]), ((k >> 1) - 1) & 1);
@@ -353,65 +355,79 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       TRACE_AT(3840 + (k & 31) * 2 + 0);
-      ring_lo = ring_e;
-      for (int e = 0; e < 2 * w.nkv_max && ok; ++e, ++ring_e) {
-        const int j = e >> 1;
-        const bool is_v = e & 1;
-        const int buf = ring_e % kRing;
-        const int use = ring_e / kRing;
+      // K/V tiles travel in pairs that share one barrier: pair 0 of an item is K_0 alone, pair j + 1 is {V_j, K_j+1}
+      // (the last one V alone).  Stage = pair % 2; its V buffer is ring buffer 2 * stage, its K buffer 2 * stage + 1.
+      pair_lo = pair_e;
+      const int npairs = w.nkv_max > 0 ? w.nkv_max + 1 : 0;
+      for (int pi = 0; pi < npairs && ok; ++pi, ++pair_e) {
+        const int stage = pair_e % kStages;
+        const int use = pair_e / kStages;
         if (use > 0) {
-          ok = warp_wait(smem_u32(&ctrl->kv_empty[buf]), (use - 1) & 1);
+          ok = warp_wait(smem_u32(&ctrl->kv_empty[stage]), (use - 1) & 1);
           if (!ok || *abort_flag) { ok = false; break; }
         }
-        const uint32_t dst = smem_base + Plan::kRingOff + buf * Plan::kTileBytes;
-        const uint32_t bar = smem_u32(&ctrl->kv_full[buf]);
-        const CUtensorMap* tm = is_v ? &tm_v : &tm_k;
+        const uint32_t bar = smem_u32(&ctrl->kv_full[stage]);
+        const bool has_v = pi >= 1, has_k = pi < w.nkv_max;
+        const int jv = pi - 1, jk = pi;               // tile indices of the V and the K of this pair
+        const uint32_t vdst = smem_base + Plan::kRingOff + (2 * stage) * Plan::kTileBytes;
+        const uint32_t kdst = vdst + Plan::kTileBytes;
         if (p.layout != B200ATTN_PAGED) {
           if (lane == 0) {
-            mbar_arrive_expect_tx(bar, Plan::kTileBytes);
-            for (int c = 0; c < Plan::kChunks; ++c)
-              tma_load_3d(dst + c * Plan::kChunkBytes, tm, bar, c * 64, w.kv_head_coord,
-                          static_cast<int>(w.kv_row0 + static_cast<long long>(j) * kBN));
+            mbar_arrive_expect_tx(bar, (has_v ? Plan::kTileBytes : 0) + (has_k ? Plan::kTileBytes : 0));
+            for (int c = 0; c < Plan::kChunks; ++c) {
+              if (has_v)
+                tma_load_3d(vdst + c * Plan::kChunkBytes, &tm_v, bar, c * 64, w.kv_head_coord,
+                            static_cast<int>(w.kv_row0 + static_cast<long long>(jv) * kBN));
+              if (has_k)
+                tma_load_3d(kdst + c * Plan::kChunkBytes, &tm_k, bar, c * 64, w.kv_head_coord,
+                            static_cast<int>(w.kv_row0 + static_cast<long long>(jk) * kBN));
+            }
           }
         } else {
-          // one box of `box_rows` tokens per lane per round; only pages that exist are fetched
-          const int* table = (is_v ? p.v_table : p.k_table) + static_cast<long long>(w.b) * p.table_stride;
+          // one box of `box_rows` tokens per lane per round and operand; only pages that exist are fetched
           const int boxes = kBN / p.box_rows;
-          int my_rows[4];
+          int rows_v[4], rows_k[4];
           int nmine = 0;
           int count = 0;
+          auto page_row = [&](const int* table, int t) -> int {
+            if (t >= w.len_k) return -1;
+            const int lp = t / p.page_size;
+            const int page = __ldg(table + lp);
+            // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
+            const bool bad = page < 0 || page >= p.num_pages;
+            if (bad) p.header[0] = DEV_ERR_PAGE_RANGE;
+            return p.num_pages > 0 ? (bad ? 0 : page) * p.page_size + (t - lp * p.page_size) : -1;
+          };
+          const int* vtab = p.v_table + static_cast<long long>(w.b) * p.table_stride;
+          const int* ktab = p.k_table + static_cast<long long>(w.b) * p.table_stride;
           for (int i = lane; i < boxes; i += 32) {
-            const int t = j * kBN + i * p.box_rows;
-            int row = -1;
-            if (t < w.len_k) {
-              const int lp = t / p.page_size;
-              const int page = __ldg(table + lp);
-              // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
-              const bool bad = page < 0 || page >= p.num_pages;
-              if (bad) p.header[0] = DEV_ERR_PAGE_RANGE;
-              if (p.num_pages > 0) row = (bad ? 0 : page) * p.page_size + (t - lp * p.page_size);
-            }
-            my_rows[nmine++] = row;
-            if (row >= 0) ++count;
+            const int rv = has_v ? page_row(vtab, jv * kBN + i * p.box_rows) : -1;
+            const int rk = has_k ? page_row(ktab, jk * kBN + i * p.box_rows) : -1;
+            rows_v[nmine] = rv;
+            rows_k[nmine] = rk;
+            ++nmine;
+            count += (rv >= 0) + (rk >= 0);
           }
           for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
           if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * p.box_rows * 128 * Plan::kChunks);
           __syncwarp();
           int kk = 0;
           for (int i = lane; i < boxes; i += 32, ++kk) {
-            const int row = my_rows[kk];
-            if (row < 0) continue;
-            for (int c = 0; c < Plan::kChunks; ++c)
-              tma_load_3d(dst + c * Plan::kChunkBytes + i * p.box_rows * 128, tm, bar, c * 64, w.kv_head_coord, row);
+            for (int c = 0; c < Plan::kChunks; ++c) {
+              if (rows_v[kk] >= 0)
+                tma_load_3d(vdst + c * Plan::kChunkBytes + i * p.box_rows * 128, &tm_v, bar, c * 64, w.kv_head_coord, rows_v[kk]);
+              if (rows_k[kk] >= 0)
+                tma_load_3d(kdst + c * Plan::kChunkBytes + i * p.box_rows * 128, &tm_k, bar, c * 64, w.kv_head_coord, rows_k[kk]);
+            }
           }
         }
-        TRACE_AT(3072 + (ring_e & 255));
+        TRACE_AT(3072 + (pair_e & 255));
       }
     }
     if (!ok) {
       if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
       // drain: wait (bounded) for the copies still in flight before the CTA may exit
-      for (int e = max(ring_lo, ring_e - kRing); e < ring_e; ++e) mbar_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
+      for (int e = max(pair_lo, pair_e - kStages); e < pair_e; ++e) mbar_wait(smem_u32(&ctrl->kv_full[e % kStages]), (e / kStages) & 1);
     }
     if (lane == 0) {
       // This CTA draws no more items.  The last CTA to get here puts both counters back to zero for the next
@@ -434,18 +450,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // (start address >> 4) plus small constants, so issuing one MMA costs the single thread a few adds.
     const uint64_t kdesc = make_smem_desc_sw128(smem_base, 16);                    // K-major operands (Q, K)
     const uint64_t vdesc = make_smem_desc_sw128(smem_base, Plan::kChunkBytes);     // MN-major operand (V)
-    int ring_base = 0;            // ring entry of K_0 of the current item
+    int pair_base = 0;            // pair that holds K_0 of the current item (pair j + 1 holds V_j and K_j+1)
     // per-slot state as scalars (an array indexed by the slot would live in local memory)
     int tiles_done0 = 0, tiles_done1 = 0;       // score tiles issued per slot so far (barrier phases run across items)
     bool pre_issued0 = false, pre_issued1 = false;   // first score tile of the coming item already issued
-    auto ring_full_wait = [&](int e) -> bool {
-      return warp_wait(smem_u32(&ctrl->kv_full[e % kRing]), (e / kRing) & 1);
+    auto pair_full_wait = [&](int pr) -> bool {
+      return warp_wait(smem_u32(&ctrl->kv_full[pr % kStages]), (pr / kStages) & 1);
     };
     // The warp stays converged while it issues: every lane runs the descriptor arithmetic, one elected lane
     // issues the tensor-core instructions and their commits.
     const uint32_t lead = elect_one();
-    auto k_desc_of = [&](int e_k) -> uint64_t {
-      return kdesc + static_cast<uint64_t>((Plan::kRingOff + (e_k % kRing) * Plan::kTileBytes) >> 4);
+    // operand descriptors of the K and the V buffer of a pair's stage
+    auto k_desc_of = [&](int pr) -> uint64_t {
+      return kdesc + static_cast<uint64_t>((Plan::kRingOff + (2 * (pr % kStages) + 1) * Plan::kTileBytes) >> 4);
+    };
+    auto v_desc_of = [&](int pr) -> uint64_t {
+      return vdesc + static_cast<uint64_t>((Plan::kRingOff + (2 * (pr % kStages)) * Plan::kTileBytes) >> 4);
     };
     auto issue_s = [&](int s, uint64_t kb) {
       // S_s = Q_s K^T : K-major A and B, D/16 k-steps
@@ -476,26 +496,26 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       TRACE_AT(3328 + (k & 31) * 8 + 2);
       if (nkv_max > 0) {
-        ok = ring_full_wait(ring_base);
+        ok = pair_full_wait(pair_base);
         if (!ok) break;
         TRACE_AT(3328 + (k & 31) * 8 + 3);
         tc_fence_after();
         // (slots whose first score tile was already issued while the previous item finished are skipped)
-        if (nkv0 > 0 && !pre_issued0) issue_s(0, k_desc_of(ring_base));
-        if (nkv1 > 0 && !pre_issued1) issue_s(1, k_desc_of(ring_base));
+        if (nkv0 > 0 && !pre_issued0) issue_s(0, k_desc_of(pair_base));
+        if (nkv1 > 0 && !pre_issued1) issue_s(1, k_desc_of(pair_base));
         TRACE_AT(3328 + (k & 31) * 8 + 4);
 #ifdef B200ATTN_TRACE
         if (k == 0) TRACE_CTA(1, trace_gtime() & 0x7fffffff);
         ++trace_items; trace_iters += nkv_max;
 #endif
-        mma_commit_lead(smem_u32(&ctrl->kv_empty[ring_base % kRing]), lead);
+        mma_commit_lead(smem_u32(&ctrl->kv_empty[pair_base % kStages]), lead);
         if (nkv_max == 1) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
       } else {
         mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
       }
       pre_issued0 = pre_issued1 = false;
       for (int j = 0; j < nkv_max && ok; ++j) {
-        const int e_v = ring_base + 2 * j + 1;
+        const int pr = pair_base + 1 + j;     // the pair {V_j, K_j+1}
         const bool last_iter = j + 1 == nkv_max;
         // On the last tile of the item the first score tile of the next item is issued right behind each slot's
         // final PV, so the softmax warps can carry straight on.  Everything waited
@@ -513,21 +533,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           next_nkv0 = wn.nkv[0];
           next_nkv1 = wn.nkv[1];
           if (!warp_wait(smem_u32(&ctrl->q_full), (k + 1) & 1)) return false;
-          if (!ring_full_wait(ring_base + 2 * nkv_max)) return false;
+          if (!pair_full_wait(pair_base + nkv_max + 1)) return false;
           next_state = 1;
           return true;
         };
-        // Everything that does not depend on the softmax warps is waited for and computed before their P is: V_j
-        // and K_{j+1} (in steady state loaded long ago), the operand descriptors, and on the last tile the next
-        // item.  Between a slot's P and its two batches of MMAs the warp then only runs the issue itself.
-        ok = ring_full_wait(e_v);
+        // Everything that does not depend on the softmax warps is waited for and computed before their P is: the
+        // pair {V_j, K_j+1} (one barrier; in steady state loaded long ago), the operand descriptors, and on the last
+        // tile the next item.  Between a slot's P and its two batches of MMAs the warp then only runs the issue.
+        ok = pair_full_wait(pr);
         if (!ok) break;
         {
           const int valid = len_k - j * kBN;
           if (valid < kBN) {
             // keys past the sequence end carry P == 0 but their V rows may hold anything (stale
             // shared memory, the next sequence, poisoned page tails): zero them so 0 * x stays 0
-            unsigned char* vbuf = smem + Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes;
+            unsigned char* vbuf = smem + Plan::kRingOff + (2 * (pr % kStages)) * Plan::kTileBytes;
             const int first = valid > 0 ? valid : 0;
             const int n16 = (kBN - first) * 8;  // 16-byte pieces per column block
             for (int c = 0; c < Plan::kChunks; ++c) {
@@ -538,19 +558,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             __syncwarp();
           }
         }
-        bool v_released = false;
-        int e_next = -1;              // ring entry of the K tile the score MMAs issued in this iteration read
-        if (!last_iter) {
-          e_next = e_v + 1;
-          ok = ring_full_wait(e_next);
-          if (!ok) break;
-        } else {
+        int pr_k = pr;                // pair whose K buffer the score MMAs issued in this iteration read
+        if (last_iter) {
           ok = prepare_next();
           if (!ok) break;
-          if (next_state == 1) e_next = ring_base + 2 * nkv_max;
+          pr_k = pair_base + nkv_max + 1;       // K_0 of the next item (read only when next_state == 1)
         }
-        const uint64_t vb = vdesc + static_cast<uint64_t>((Plan::kRingOff + (e_v % kRing) * Plan::kTileBytes) >> 4);
-        const uint64_t kb = kdesc + static_cast<uint64_t>((Plan::kRingOff + ((e_next < 0 ? 0 : e_next) % kRing) * Plan::kTileBytes) >> 4);
+        const uint64_t vb = v_desc_of(pr);
+        const uint64_t kb = k_desc_of(pr_k);
         auto slot_step = [&](const int s, const int nkv_s, const int next_nkv_s, int& tiles_done, bool& pre_issued) -> bool {
           if (j >= nkv_s) return true;
           const bool s_next = last_iter ? (next_state == 1 && next_nkv_s > 0) : (j + 1 < nkv_s);
@@ -564,8 +579,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 1);
           tc_fence_after();
           issue_pv(s, vb, j == 0);
-          // V_j may be refilled once the PVs of every slot that reads it have completed: commit behind the last one
-          if (s == kSlots - 1 || j >= nkv1) { mma_commit_lead(smem_u32(&ctrl->kv_empty[e_v % kRing]), lead); v_released = true; }
           TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 2);
           if (s_next) {
             issue_s(s, kb);
@@ -587,12 +600,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (!pre_issued1 && next_nkv1 > 0) { tc_fence_after(); issue_s(1, kb); pre_issued1 = true; }
           }
         }
-        if (!v_released) mma_commit_lead(smem_u32(&ctrl->kv_empty[e_v % kRing]), lead);
-        if (j + 1 < nkv_max) mma_commit_lead(smem_u32(&ctrl->kv_empty[(e_v + 1) % kRing]), lead);
+        // V_j and K_j+1 have been read by everything that will read them: one commit releases the stage
+        mma_commit_lead(smem_u32(&ctrl->kv_empty[pr % kStages]), lead);
         // the last score MMAs of the item have been issued: Q may be replaced once they complete
         if (j + 2 == nkv_max) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
       }
-      ring_base += 2 * nkv_max;
+      if (nkv_max > 0) pair_base += nkv_max + 1;
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));
       __syncwarp();
     }
