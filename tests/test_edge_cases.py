@@ -105,3 +105,45 @@ def test_decode_chunk_boundaries_long_sequence():
         v = _rand(gen, (1, KVH, n, D))
         ref = sdpa_ref.decode_reference([q[0]], [k[0].transpose(0, 1)], [v[0].transpose(0, 1)], QH, KVH)[0]
         assert_close_both(decode_attention(q, k, v)[0], ref, torch.bfloat16, n, f"n={n}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("layout", ["dense", "ragged"])
+def test_prefill_output_aligned_to_16_bytes_only(monkeypatch, dtype, layout):
+    """The C ABI asks for 16-byte alignment; the kernel's 32-byte stores are an option it may only take when the
+    output pointer allows.  The entry point's output allocation is replaced by one that starts 16 bytes past a
+    32-byte boundary."""
+    import kernels.attention as attn
+    from kernels.attention import flash_attention_v2
+
+    keep = []
+
+    def offset_empty_like(t):
+        raw = torch.empty(t.numel() * t.element_size() + 64, dtype=torch.uint8, device=t.device)
+        keep.append(raw)
+        start = (-raw.data_ptr()) % 32 + 16
+        out = raw[start:start + t.numel() * t.element_size()].view(t.dtype).view(t.shape)
+        assert out.data_ptr() % 32 == 16
+        return out
+
+    monkeypatch.setattr(attn.torch, "empty_like", offset_empty_like)
+    gen = torch.Generator().manual_seed(77)
+    QH, KVH, D, n = 8, 2, 128, 300
+    if layout == "dense":
+        q = _rand(gen, (1, QH, n, D), dtype)
+        k = _rand(gen, (1, KVH, n, D), dtype)
+        v = _rand(gen, (1, KVH, n, D), dtype)
+        out = flash_attention_v2(q, k, v, is_causal=True)
+        got = out[0].transpose(0, 1)
+        qs, ks, vs = q[0].transpose(0, 1), k[0].transpose(0, 1), v[0].transpose(0, 1)
+    else:
+        q = _rand(gen, (n, QH, D), dtype)
+        k = _rand(gen, (n, KVH, D), dtype)
+        v = _rand(gen, (n, KVH, D), dtype)
+        ip = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+        out = flash_attention_v2(q, k, v, is_causal=True, q_indptr=ip, kv_indptr=ip)
+        got, qs, ks, vs = out, q, k, v
+    assert out.data_ptr() % 32 == 16
+    ref = sdpa_ref.prefill_reference([qs], [ks], [vs], QH, KVH, True)[0]
+    from helpers import PREFILL_F32_STRICT
+    assert_close_both(got, ref, dtype, n, layout, strict=PREFILL_F32_STRICT if dtype == torch.float32 else None)
