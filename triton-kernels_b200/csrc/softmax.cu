@@ -58,6 +58,13 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 template <typename T> struct Vec16 { static constexpr int kElems = 16 / sizeof(T); };
 
+template <typename T> __device__ __forceinline__ float fast_or_exact_exp(float x) {
+  // 16-bit outputs round away far more than the approximate exponential loses; fp32 outputs need expf
+  if constexpr (sizeof(T) == 2) return __expf(x);
+  else return expf(x);
+}
+
+
 // (max, sum of exp(x - max)) of two parts
 __device__ __forceinline__ void merge_ml(float& m, float& l, float m2, float l2) {
   const float g = fmaxf(m, m2);
@@ -105,10 +112,10 @@ __device__ __forceinline__ float row_exp_sum(const T* row, long long n, float m)
       const uint4 u = r4[i];
       const T* e = reinterpret_cast<const T*>(&u);
 #pragma unroll
-      for (int k = 0; k < E; ++k) s += expf(ElemTraits<T>::to_float(e[k]) - m);
+      for (int k = 0; k < E; ++k) s += fast_or_exact_exp<T>(ElemTraits<T>::to_float(e[k]) - m);
     }
   } else {
-    for (long long i = threadIdx.x; i < n; i += blockDim.x) s += expf(ElemTraits<T>::to_float(row[i]) - m);
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) s += fast_or_exact_exp<T>(ElemTraits<T>::to_float(row[i]) - m);
   }
   return s;
 }
@@ -118,7 +125,7 @@ __device__ __forceinline__ float row_exp_sum(const T* row, long long n, float m)
 template <typename T, bool LOG>
 __device__ __forceinline__ T finish(float x, float m, float k) {
   if constexpr (LOG) return ElemTraits<T>::from_float((x - m) - k);
-  else return ElemTraits<T>::from_float(expf(x - m) * k);
+  else return ElemTraits<T>::from_float(fast_or_exact_exp<T>(x - m) * k);
 }
 
 template <typename T, bool LOG, bool VEC>
@@ -151,11 +158,6 @@ __device__ __forceinline__ float final_constant(float m, float l) {
 // ---------------------------------------------------------------------------
 // one CTA per row, the row in registers: thread t holds the 16-byte pieces t, t + blockDim, ... (VPT of them)
 // ---------------------------------------------------------------------------
-template <typename T> __device__ __forceinline__ float fast_or_exact_exp(float x) {
-  // 16-bit outputs round away far more than the approximate exponential loses; fp32 outputs need expf
-  if constexpr (sizeof(T) == 2) return __expf(x);
-  else return expf(x);
-}
 
 template <typename T, bool LOG, int VPT>
 __global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, long long rows, long long cols) {
@@ -327,14 +329,17 @@ int launch_typed(const b200attn_softmax_args_t& a, int sm_count, cudaStream_t st
     const unsigned grid = static_cast<unsigned>(std::min<long long>(rows, max_grid));
     softmax_row_kernel<T, LOG, VEC><<<grid, threads, smem, stream>>>(x, out, rows, cols);
   } else if (row_bytes <= static_cast<size_t>(kRowSmemBytes) * kMaxCluster) {
+    // more CTAs per row while a slice stays above 64 KiB (fp32) / 128 KiB (16-bit), measured: smaller CTAs share an SM
+    // and one's loads overlap another's stores
     int csize = 2;
-    while (static_cast<size_t>(kRowSmemBytes) * csize < row_bytes) csize *= 2;
+    while (csize < kMaxCluster && (static_cast<size_t>(kRowSmemBytes) * csize < row_bytes || row_bytes / csize > (sizeof(T) == 4 ? 64 : 128) * 1024)) csize *= 2;
     long long slice = (cols + csize - 1) / csize;
     slice = ((slice + E - 1) / E) * E;                 // slices start on 16-byte boundaries of the row
     const size_t smem = static_cast<size_t>(slice) * sizeof(T);
     int rc = set_smem_limit(softmax_cluster_kernel<T, LOG, VEC>, smem);
     if (rc) return rc;
-    const long long clusters = std::min<long long>(rows, std::max(1, sm_count / csize));
+    const int per_sm = std::max<int>(1, std::min<int>(2, static_cast<int>((220 * 1024) / (smem + 1024))));
+    const long long clusters = std::min<long long>(rows, std::max(1, sm_count * per_sm / csize));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(clusters * csize), 1, 1);
     cfg.blockDim = dim3(1024, 1, 1);
