@@ -3,24 +3,23 @@
 // One launch family replaces the reference's split kernel + merge kernel pairs
 // (kernels/decode.py:22-200, kernels/speculative_decode.py:22-226):
 //
-//   decode_plan_kernel : 1 CTA.  Reads the sequence lengths on the device (no
-//       host sync), picks the KV chunk size so that the whole batch becomes about
-//       `target_items` equally sized work items, and writes the per-sequence item
-//       prefix.  A work item is (sequence, KV chunk); the grid's y axis is the KV head.
-//   decode_mma_kernel  : one CTA per (item, kv_head).  All q rows that share the
-//       KV head (group size G x draft tokens M, <= 128 rows) are packed into
-//       16-row MMA tiles, so every K/V byte is read from HBM once per KV head
-//       (the reference re-reads it once per q head).  K/V tiles of 64 tokens
-//       stream through a 3-stage cp.async ring with 16-byte loads; paged
-//       layouts resolve the block table per row; rows past the sequence end
-//       are zero-filled, never dereferenced.  QK^T and PV run on bf16/fp16
-//       mma.sync with fp32 accumulation and an online softmax in the exp2 domain.
-//   decode_simt_kernel : the fp32-input variant, fp32 FMA arithmetic like the
-//       reference's decode kernel.
-//   Both end in emit_and_merge(): a CTA whose sequence has a single chunk writes
-//       the output directly; otherwise it writes an (m, l, acc) partial and takes
-//       a ticket, and the CTA that draws the last ticket of its (sequence, kv head)
-//       performs the log-sum-exp merge.  No CTA ever waits for another.
+//   decode_plan_kernel : 1 CTA.  Reads the sequence lengths on the device (no host sync), picks the KV chunk size
+//       (the smallest of 32 candidates that keeps the batch at or below `target_items` work items, a whole number of
+//       waves of resident CTAs), splits every sequence into equal items and writes one record per item in execution
+//       order, longest first.  A work item is (sequence, KV chunk); CTAs are (item, kv head), heads fastest.
+//   decode_mma_kernel  : up to 16 q rows per KV head.  All q rows that share the KV head (group size G x draft
+//       tokens M) are packed into 16-row MMA tiles, so every K/V byte is read from HBM once per KV head (the
+//       reference re-reads it once per q head).  A producer warp stages K/V tiles of 64 keys by TMA (one 4-D box per
+//       page and operand) through a 2- or 3-stage mbarrier ring; block-table entries outside the cache are reported
+//       and never dereferenced, V rows past the sequence end are zeroed in shared memory.  QK^T and PV run on
+//       bf16/fp16 mma.sync with fp32 accumulation and an online softmax in the exp2 domain.
+//   decode_umma_kernel : more than 16 q rows per KV head (speculative decode).  One 128-row tcgen05 tile: Q is
+//       written to tensor memory once per CTA, P once per 64-key tile, so both MMAs take their A operand from TMEM
+//       and shared memory is read once per K/V byte.  Same producer, planner and merge.
+//   decode_simt_kernel : the fp32-input variant, fp32 FMA arithmetic like the reference's decode kernel.
+//   All end in emit_and_merge(): a CTA whose sequence has a single chunk writes the output directly; otherwise it
+//       writes an (m, l, acc) partial and takes a ticket, and the CTA that draws the last ticket of its
+//       (sequence, kv head) performs the log-sum-exp merge.  No CTA ever waits for another.
 #include <algorithm>
 #include <mutex>
 #include <type_traits>
