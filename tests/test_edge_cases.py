@@ -147,3 +147,36 @@ def test_prefill_output_aligned_to_16_bytes_only(monkeypatch, dtype, layout):
     ref = sdpa_ref.prefill_reference([qs], [ks], [vs], QH, KVH, True)[0]
     from helpers import PREFILL_F32_STRICT
     assert_close_both(got, ref, dtype, n, layout, strict=PREFILL_F32_STRICT if dtype == torch.float32 else None)
+
+
+def test_two_streams_run_concurrently():
+    """Calls on different streams use different workspaces (one per stream) and may overlap on the GPU: the
+    persistent prefill kernel's work counters and the decode planner's tables must not be shared between them."""
+    from kernels.attention import flash_attention_v2
+    from kernels.decode import decode_attention
+
+    gen = torch.Generator().manual_seed(91)
+    QH, KVH, D = 8, 2, 128
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    work = []
+    for i, st in enumerate(streams):
+        n = 700 + 300 * i
+        q = _rand(gen, (2, QH, n, D))
+        k = _rand(gen, (2, KVH, n, D))
+        v = _rand(gen, (2, KVH, n, D))
+        qd = _rand(gen, (2, QH, D))
+        work.append((st, n, q, k, v, qd))
+    torch.cuda.synchronize()
+    outs = []
+    for rep in range(3):
+        outs = []
+        for st, n, q, k, v, qd in work:
+            with torch.cuda.stream(st):
+                outs.append((flash_attention_v2(q, k, v, is_causal=True), decode_attention(qd, k, v)))
+    torch.cuda.synchronize()
+    for (st, n, q, k, v, qd), (po, do) in zip(work, outs):
+        for b in range(2):
+            ref = sdpa_ref.prefill_reference([q[b].transpose(0, 1)], [k[b].transpose(0, 1)], [v[b].transpose(0, 1)], QH, KVH, True)[0]
+            assert_close_both(po[b].transpose(0, 1), ref, torch.bfloat16, n, "prefill")
+            refd = sdpa_ref.decode_reference([qd[b]], [k[b].transpose(0, 1)], [v[b].transpose(0, 1)], QH, KVH)[0]
+            assert_close_both(do[b], refd, torch.bfloat16, n, "decode")
