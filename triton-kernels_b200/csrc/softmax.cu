@@ -14,6 +14,7 @@
 #include <cooperative_groups.h>
 
 #include <algorithm>
+#include <type_traits>
 
 #include "common.cuh"
 #include "softmax_launch.h"
@@ -159,9 +160,29 @@ __device__ __forceinline__ float final_constant(float m, float l) {
 // one CTA per row, the row in registers: thread t holds the 16-byte pieces t, t + blockDim, ... (VPT of them)
 // ---------------------------------------------------------------------------
 
+// the elements of one 32-bit word of a 16-byte piece (two 16-bit values, or one float) <-> fp32
+template <typename T> __device__ __forceinline__ void word_to_floats(uint32_t w, float* f) {
+  if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+    f[0] = __uint_as_float(w << 16);                 // a bf16 is the upper half of the fp32 with the same value
+    f[1] = __uint_as_float(w & 0xffff0000u);
+  } else if constexpr (std::is_same<T, __half>::value) {
+    const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&w));
+    f[0] = t.x;
+    f[1] = t.y;
+  } else {
+    f[0] = __uint_as_float(w);
+  }
+}
+template <typename T> __device__ __forceinline__ uint32_t floats_to_word(const float* f) {
+  if constexpr (sizeof(T) == 2) return ElemTraits<T>::pack2(f[0], f[1]);
+  else return __float_as_uint(f[0]);
+}
+
 template <typename T, bool LOG, int VPT>
 __global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, long long rows, long long cols) {
   constexpr int E = Vec16<T>::kElems;
+  constexpr int W = E / 4;                           // elements per 32-bit word
+  constexpr float kLog2e = 1.4426950408889634f;
   __shared__ float scratch[32];
   const int nv = static_cast<int>(cols / E);
   for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -174,9 +195,11 @@ __global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, l
       const int i = threadIdx.x + k * blockDim.x;
       if (i < nv) {
         const uint4 u = s4[i];
-        const T* e = reinterpret_cast<const T*>(&u);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-        for (int q = 0; q < E; ++q) { f[k * E + q] = ElemTraits<T>::to_float(e[q]); mx = fmaxf(mx, f[k * E + q]); }
+        for (int q = 0; q < 4; ++q) word_to_floats<T>(w[q], &f[k * E + q * W]);
+#pragma unroll
+        for (int q = 0; q < E; ++q) mx = fmaxf(mx, f[k * E + q]);
       } else {
 #pragma unroll
         for (int q = 0; q < E; ++q) f[k * E + q] = -INFINITY;
@@ -185,9 +208,14 @@ __global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, l
     const float m = block_max(mx, scratch);
     float sum = 0.f;
     if (m != -INFINITY) {
+      const float neg_m_l2e = -m * kLog2e;
 #pragma unroll
       for (int j = 0; j < VPT * E; ++j) {
-        const float ev = fast_or_exact_exp<T>(f[j] - m);      // exp(-inf) = 0 for the padding
+        // 16-bit outputs round away far more than the approximate exponential loses: exp2(x log2e - m log2e), one
+        // FMA and one MUFU operation; fp32 outputs need expf.  exp(-inf) = 0 for the padding.
+        float ev;
+        if constexpr (sizeof(T) == 2) ev = fast_exp2(fmaf(f[j], kLog2e, neg_m_l2e));
+        else ev = expf(f[j] - m);
         sum += ev;
         if constexpr (!LOG) f[j] = ev;
       }
@@ -198,15 +226,19 @@ __global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, l
     for (int k = 0; k < VPT; ++k) {
       const int i = threadIdx.x + k * blockDim.x;
       if (i < nv) {
-        uint4 u;
-        T* e = reinterpret_cast<T*>(&u);
+        uint32_t w[4];
 #pragma unroll
-        for (int q = 0; q < E; ++q) {
-          const float v = f[k * E + q];
-          if constexpr (LOG) e[q] = ElemTraits<T>::from_float((v - m) - kk);
-          else e[q] = ElemTraits<T>::from_float(m == -INFINITY ? __int_as_float(0x7fc00000) : v * kk);
+        for (int q = 0; q < 4; ++q) {
+          float t[W];
+#pragma unroll
+          for (int e = 0; e < W; ++e) {
+            const float v = f[k * E + q * W + e];
+            if constexpr (LOG) t[e] = (v - m) - kk;
+            else t[e] = m == -INFINITY ? __int_as_float(0x7fc00000) : v * kk;
+          }
+          w[q] = floats_to_word<T>(t);
         }
-        d4[i] = u;
+        d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
   }
