@@ -64,6 +64,44 @@ def test_out_and_in_place(shape, dtype, log):
     _check(x, keep, log)
 
 
+# long rows: the pipelined kernel (one CTA up to 108 KiB, clusters of 2, 4, 8 up to 864 KiB; slice edges that do not
+# divide the row; more rows than resident CTAs, so every stage of the ring is reused), the register cluster kernel
+# beyond it (up to 1 MiB) and the lengths right at and right after each limit
+@pytest.mark.parametrize("log", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(3, 16388), (700, 20000), (3000, 4100), (3, 27648), (3, 27652), (300, 55296),
+                                   (2, 55304), (5, 65544), (2, 131080), (3, 200000), (2, 221184), (2, 221188),
+                                   (2, 262144), (2, 442368), (2, 442376), (2, 524288)])
+def test_long_rows(shape, dtype, log):
+    g = torch.Generator().manual_seed(shape[1] & 0xffff)
+    x = (torch.randn(shape, generator=g) * 3).to(dtype).to(DEV)
+    _check(_fn(log)(x), x, log)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cluster_slices_of_minus_inf(dtype):
+    """Whole slices of a clustered row are -inf: those CTAs contribute (max, sum) = (-inf, 0) and write zeros."""
+    from kernels import log_softmax, softmax
+
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((4, 131072), generator=g).to(dtype)
+    x[0, 40000:] = -float("inf")
+    x[1, :100000] = -float("inf")
+    x[2, 20000:110000] = -float("inf")
+    x[3, :] = -float("inf")
+    x = x.to(DEV)
+    s = softmax(x)
+    exp = _expected(x, False)
+    torch.testing.assert_close(s.cpu()[:3], exp[:3])
+    assert torch.isnan(s[3]).all()
+    assert float(s[0, 40000:].abs().max()) == 0.0 and float(s[1, :100000].abs().max()) == 0.0
+    ls = log_softmax(x).cpu()
+    lexp = _expected(x, True)
+    assert torch.equal(torch.isinf(ls[:3]), torch.isinf(lexp[:3]))
+    fin = torch.isfinite(lexp)
+    torch.testing.assert_close(ls[fin], lexp[fin])
+
+
 @pytest.mark.parametrize("log", [False, True])
 def test_against_numpy_restatement_fp32(log):
     g = torch.Generator().manual_seed(11)

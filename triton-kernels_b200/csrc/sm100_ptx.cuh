@@ -60,6 +60,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Asynchronous 8-byte store of (a, b) to the shared-memory address `slot` of CTA `cta_rank` of this cluster; the
+// receiver's mbarrier at `bar` (same offsets in every CTA) is credited with the 8 bytes when they have landed.
+__device__ __forceinline__ void st_async_pair(uint32_t slot, uint32_t bar, uint32_t cta_rank, float a, float b) {
+  asm volatile(
+      "{\n\t.reg .u32 rs, rb;\n\t"
+      "mapa.shared::cluster.u32 rs, %0, %2;\n\t"
+      "mapa.shared::cluster.u32 rb, %1, %2;\n\t"
+      "st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v2.f32 [rs], {%3, %4}, [rb];\n\t}\n"
+      ::"r"(slot), "r"(bar), "r"(cta_rank), "f"(a), "f"(b)
+      : "memory");
+}
+
+// Untiled bulk copy global -> this CTA's shared memory; both addresses 16-byte aligned, `bytes` a multiple of 16.
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
 // ------------------------------ proxies / fences ----------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");

@@ -2,21 +2,30 @@
 //
 // Replaces the reference's small / medium / partial + merge + finalize kernels (kernels/softmax.py:18-150 and
 // :239-375): there a row longer than one block is read twice (three launches when it is split over programs).
-// Here a row is read once, kept on the SM and normalised from there:
-//   softmax_reg_kernel     one CTA per row, up to 32 elements per thread in registers (rows up to 32 768 elements whose
-//                          bytes are a multiple of 16)
-//   softmax_row_kernel     one CTA per row, the row (as its 16- or 32-bit elements) in up to 200 KiB of shared memory
-//   softmax_cluster_kernel a row longer than that is spread over a thread-block cluster of 2, 4 or 8 CTAs; the CTAs
-//                          exchange their (max, sum) pairs through distributed shared memory
-//   softmax_stream_kernel  rows beyond 8 x 200 KiB: one CTA per row, online (max, sum) pass, then a second read
-// All arithmetic is fp32 (expf / logf), like the reference's `.to(tl.float32)`.  `out` may alias `x`: a CTA writes a
-// row only after it has staged it (the streaming kernel reads element i right before it writes element i).
+// Here a row is read once, kept on the SM and normalised from there.  Rows whose bytes are a multiple of 16:
+//   softmax_reg_kernel     up to 16 384 fp32 / 16-bit elements: one CTA per row, the row in registers
+//   softmax_pipe_kernel    up to 864 KiB: a CTA, or a cluster of 2, 4 or 8 CTAs, per row; slices of up to 108 KiB arrive
+//                          by bulk copies into a ring of 2 to 8 shared-memory stages, so the next rows load while
+//                          this one is reduced and written
+//   softmax_regc_kernel    up to 1 MiB: the row in the registers of a cluster of eight CTAs
+//   softmax_cluster_kernel up to 1.6 MB: 200 KiB per CTA in shared memory, cluster of eight
+// Any other row:
+//   softmax_row_kernel     up to 200 KiB: one CTA per row, the row in shared memory
+//   softmax_cluster_kernel up to 1.6 MB (as above)
+//   softmax_stream_kernel  beyond: one CTA per row, online (max, sum) pass, then a second read
+// Clusters exchange their (max, sum) pairs through distributed shared memory; the pipelined and register kernels do it
+// with asynchronous remote stores that count on the receiver's mbarrier, because a cluster-wide barrier also waits
+// for the previous row's global stores.
+// All arithmetic is fp32 (expf / logf; for 16-bit types one FMA and one ex2 per exponential), like the reference's
+// `.to(tl.float32)`.  `out` may alias `x`: a row is written only after all of it has been staged (the streaming kernel
+// reads element i right before it writes element i), and rows staged ahead of time are other rows.
 #include <cooperative_groups.h>
 
 #include <algorithm>
 #include <type_traits>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 #include "softmax_launch.h"
 
 namespace cg = cooperative_groups;
@@ -27,6 +36,8 @@ namespace {
 
 constexpr int kRowSmemBytes = 200 * 1024;   // row bytes one CTA stages
 constexpr int kMaxCluster = 8;              // portable cluster size
+constexpr int kPipeSliceBytes = 108 * 1024; // longest slice of a row per CTA of the pipelined kernel (two are staged)
+constexpr int kPipeStages = 8;              // shorter slices: as many stages as fit 216 KiB, up to this many
 
 __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -178,14 +189,40 @@ template <typename T> __device__ __forceinline__ uint32_t floats_to_word(const f
   else return __float_as_uint(f[0]);
 }
 
-template <typename T, bool LOG, int VPT>
-__global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, long long rows, long long cols) {
+// CL: the row is spread over the CTAs of a thread-block cluster (CTA `rank` holds the pieces rank * slice ...); each
+// CTA normalises against its own maximum first, the (max, sum) pairs meet in distributed shared memory, and the
+// correction exp(own max - row max) / row sum goes into the constant of the store loop.  The pairs are double
+// buffered by row parity, so one cluster barrier per row is enough.
+template <typename T, bool LOG, int VPT, bool CL>
+__device__ __forceinline__ void softmax_reg_body(const T* x, T* out, long long rows, long long cols) {
   constexpr int E = Vec16<T>::kElems;
   constexpr int W = E / 4;                           // elements per 32-bit word
   constexpr float kLog2e = 1.4426950408889634f;
   __shared__ float scratch[32];
-  const int nv = static_cast<int>(cols / E);
-  for (long long r = blockIdx.x; r < rows; r += gridDim.x) {
+  __shared__ __align__(8) float2 pairs[2][kMaxCluster];   // CL: every CTA's (max, sum) of the even / odd row in work
+  __shared__ __align__(8) uint64_t pair_bar[2];           // CL: completes when all pairs of that row have landed
+  int nv = static_cast<int>(cols / E);
+  unsigned csize = 1;
+  int rank = 0;
+  if constexpr (CL) {
+    cg::cluster_group cluster = cg::this_cluster();
+    rank = static_cast<int>(cluster.block_rank());
+    csize = cluster.num_blocks();
+    if (threadIdx.x == 0) {
+      ptx::mbar_init(smem_u32(&pair_bar[0]), 1);
+      ptx::mbar_init(smem_u32(&pair_bar[1]), 1);
+      ptx::mbar_fence_init();
+    }
+    cluster.sync();                                  // once: every peer's barriers exist before anyone sends
+    const int slice = (nv + static_cast<int>(csize) - 1) / static_cast<int>(csize);
+    x += static_cast<long long>(slice) * rank * E;   // this CTA's pieces start here within every row
+    out += static_cast<long long>(slice) * rank * E;
+    nv = max(0, min(slice, nv - slice * rank));
+  }
+  const unsigned row_step = gridDim.x / csize;
+  unsigned iter = 0;                                 // rows this CTA has worked on
+  for (long long r = blockIdx.x / csize; r < rows; r += row_step, ++iter) {
+    const unsigned parity = iter & 1u;
     const uint4* s4 = reinterpret_cast<const uint4*>(x + r * cols);
     uint4* d4 = reinterpret_cast<uint4*>(out + r * cols);
     float f[VPT * E];
@@ -219,9 +256,35 @@ __global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, l
         sum += ev;
         if constexpr (!LOG) f[j] = ev;
       }
+    } else if constexpr (CL && !LOG) {
+      // this CTA's part is all -inf but the row may not be: its outputs are zeros
+#pragma unroll
+      for (int j = 0; j < VPT * E; ++j) f[j] = 0.f;
     }
-    const float l = block_sum(sum, scratch);
-    const float kk = final_constant<LOG>(m, l);
+    float l = block_sum(sum, scratch);
+    float own = 1.f;                                 // CL: exp(own max - row max)
+    float m_row = m;
+    if constexpr (CL) {
+      // Thread 0 posts this CTA's pair into every CTA's `pairs` (its own included) with asynchronous remote stores
+      // that count bytes on the receiver's barrier: no cluster-wide barrier, no fence that would wait for the
+      // previous row's global stores.  Slot reuse is safe: a peer can send row r + 2 only after it has seen this
+      // CTA's pair of row r + 1, which thread 0 sends after all threads here have read the pairs of row r.
+      const uint32_t bar = smem_u32(&pair_bar[parity]);
+      if (threadIdx.x == 0) {
+        ptx::mbar_arrive_expect_tx(bar, csize * 8u);
+        const uint32_t slot = smem_u32(&pairs[parity][rank]);
+        for (unsigned p = 0; p < csize; ++p) ptx::st_async_pair(slot, bar, p, m, l);
+      }
+      const bool landed = ptx::mbar_wait(bar, (iter >> 1) & 1u);
+      float gm = -INFINITY, gl = 0.f;
+      for (unsigned p = 0; p < csize; ++p) merge_ml(gm, gl, pairs[parity][p].x, pairs[parity][p].y);
+      if (!landed) gl = __int_as_float(0x7fc00000);  // bounded wait ran out: the row comes out as NaN, never a hang
+      own = (m == -INFINITY) ? 0.f : expf(m - gm);
+      m_row = gm;
+      l = gl;
+    }
+    float kk = final_constant<LOG>(m_row, l);
+    if constexpr (CL && !LOG) kk *= own;
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
       const int i = threadIdx.x + k * blockDim.x;
@@ -233,8 +296,8 @@ __global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, l
 #pragma unroll
           for (int e = 0; e < W; ++e) {
             const float v = f[k * E + q * W + e];
-            if constexpr (LOG) t[e] = (v - m) - kk;
-            else t[e] = m == -INFINITY ? __int_as_float(0x7fc00000) : v * kk;
+            if constexpr (LOG) t[e] = (v - m_row) - kk;
+            else t[e] = m_row == -INFINITY ? __int_as_float(0x7fc00000) : v * kk;
           }
           w[q] = floats_to_word<T>(t);
         }
@@ -242,6 +305,19 @@ __global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, l
       }
     }
   }
+  // (a CTA may leave right away: it has received every pair sent to it, and its own last pairs have been received
+  // by peers that are still waiting for them or already past that wait)
+}
+
+template <typename T, bool LOG, int VPT>
+__global__ void __launch_bounds__(1024) softmax_reg_kernel(const T* x, T* out, long long rows, long long cols) {
+  softmax_reg_body<T, LOG, VPT, false>(x, out, rows, cols);
+}
+// two CTAs per SM while a thread holds 16 elements
+template <typename T, bool LOG, int VPT>
+__global__ void __launch_bounds__(1024, VPT * (16 / sizeof(T)) <= 16 ? 2 : 1)
+softmax_regc_kernel(const T* x, T* out, long long rows, long long cols) {
+  softmax_reg_body<T, LOG, VPT, true>(x, out, rows, cols);
 }
 
 // ---------------------------------------------------------------------------
@@ -296,6 +372,154 @@ __global__ void softmax_cluster_kernel(const T* x, T* out, long long rows, long 
 }
 
 // ---------------------------------------------------------------------------
+// long rows, pipelined: a CTA (alone, or as one of a cluster of 2, 4 or 8 that share a row) keeps two slices in shared
+// memory; the bulk copy of the next row's slice runs while the current one is reduced and written out, so loads are
+// in flight all the time.  Clusters exchange (max, sum) pairs like softmax_regc_kernel does.
+// ---------------------------------------------------------------------------
+template <typename T, bool LOG>
+__global__ void __launch_bounds__(1024, 1)
+softmax_pipe_kernel(const T* x, T* out, long long rows, long long cols, int slice /* 16-byte pieces per CTA */,
+                    int csize, int stages /* slices staged, 2..kPipeStages */) {
+  constexpr int E = Vec16<T>::kElems;
+  constexpr int W = E / 4;
+  constexpr float kLog2e = 1.4426950408889634f;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float scratch[32];
+  __shared__ __align__(8) float2 pairs[2][kMaxCluster];
+  __shared__ __align__(8) uint64_t pair_bar[2];
+  __shared__ __align__(8) uint64_t full_bar[kPipeStages];
+  const int rank = csize > 1 ? static_cast<int>(cg::this_cluster().block_rank()) : 0;
+  const int nv_row = static_cast<int>(cols / E);
+  const int nv = max(0, min(slice, nv_row - slice * rank));
+  const uint32_t bytes = static_cast<uint32_t>(nv) * 16u;
+  x += static_cast<long long>(slice) * rank * E;
+  out += static_cast<long long>(slice) * rank * E;
+  uint4* const base = reinterpret_cast<uint4*>(smem_raw);   // stage s at base + s * slice
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) ptx::mbar_init(smem_u32(&pair_bar[i]), 1);
+    for (int i = 0; i < kPipeStages; ++i) ptx::mbar_init(smem_u32(&full_bar[i]), 1);
+    ptx::mbar_fence_init();
+  }
+  if (csize > 1) cg::this_cluster().sync(); else __syncthreads();
+  const unsigned row_step = gridDim.x / csize;
+  const long long r0 = blockIdx.x / csize;
+  if (threadIdx.x == 0 && nv > 0) {
+    for (int s = 0; s < stages - 1; ++s) {
+      const long long r = r0 + static_cast<long long>(s) * row_step;
+      if (r >= rows) break;
+      ptx::mbar_arrive_expect_tx(smem_u32(&full_bar[s]), bytes);
+      ptx::bulk_load(smem_u32(base + static_cast<size_t>(s) * slice), x + r * cols, bytes, smem_u32(&full_bar[s]));
+    }
+  }
+  unsigned iter = 0;
+  int b = 0;                                         // stage of this iteration
+  unsigned phase = 0;                                // and the parity its barrier completes with
+  bool ok = true;
+  for (long long r = r0; r < rows; r += row_step, ++iter) {
+    if (threadIdx.x == 0 && nv > 0) {
+      // refill the stage the previous iteration used: it was read for the last time before the barrier that ended
+      // that iteration
+      const long long rn = r + static_cast<long long>(stages - 1) * row_step;
+      if (rn < rows) {
+        const int bn = b == 0 ? stages - 1 : b - 1;
+        ptx::fence_proxy_async_smem();
+        ptx::mbar_arrive_expect_tx(smem_u32(&full_bar[bn]), bytes);
+        ptx::bulk_load(smem_u32(base + static_cast<size_t>(bn) * slice), x + rn * cols, bytes, smem_u32(&full_bar[bn]));
+      }
+    }
+    if (nv > 0) ok = ptx::mbar_wait(smem_u32(&full_bar[b]), phase) && ok;
+    uint4* row = base + static_cast<size_t>(b) * slice;
+    float mx = -INFINITY;
+#pragma unroll 2
+    for (int i = threadIdx.x; i < nv; i += 1024) {
+      const uint4 u = row[i];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[W];
+        word_to_floats<T>(w[q], f);
+#pragma unroll
+        for (int e = 0; e < W; ++e) mx = fmaxf(mx, f[e]);
+      }
+    }
+    const float m = block_max(mx, scratch);
+    float sum = 0.f;
+    if (m != -INFINITY) {
+      const float neg_m_l2e = -m * kLog2e;
+#pragma unroll 2
+      for (int i = threadIdx.x; i < nv; i += 1024) {
+        const uint4 u = row[i];
+        uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float f[W];
+          word_to_floats<T>(w[q], f);
+#pragma unroll
+          for (int e = 0; e < W; ++e) {
+            if constexpr (sizeof(T) == 2) {
+              sum += fast_exp2(fmaf(f[e], kLog2e, neg_m_l2e));
+            } else {
+              const float ev = expf(f[e] - m);
+              sum += ev;
+              if constexpr (!LOG) w[q] = __float_as_uint(ev);   // fp32 softmax keeps exp(x - m) in place
+            }
+          }
+        }
+        if constexpr (sizeof(T) == 4 && !LOG) row[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+    float l = block_sum(sum, scratch);
+    float m_row = m, own = 1.f;
+    if (csize > 1) {
+      const unsigned parity = iter & 1u;
+      const uint32_t bar = smem_u32(&pair_bar[parity]);
+      if (threadIdx.x == 0) {
+        ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(csize) * 8u);
+        const uint32_t slot = smem_u32(&pairs[parity][rank]);
+        for (int p = 0; p < csize; ++p) ptx::st_async_pair(slot, bar, p, m, l);
+      }
+      ok = ptx::mbar_wait(bar, (iter >> 1) & 1u) && ok;
+      float gm = -INFINITY, gl = 0.f;
+      for (int p = 0; p < csize; ++p) merge_ml(gm, gl, pairs[parity][p].x, pairs[parity][p].y);
+      own = (m == -INFINITY) ? 0.f : expf(m - gm);
+      m_row = gm;
+      l = gl;
+    }
+    if (!ok) l = __int_as_float(0x7fc00000);         // a bounded wait ran out: NaN rows, never a hang
+    float kk = final_constant<LOG>(m_row, l);
+    if constexpr (!LOG && sizeof(T) == 4) kk *= own;
+    const float neg_mrow_l2e = -m_row * kLog2e;
+    const bool nan_row = m_row == -INFINITY;
+    uint4* d4 = reinterpret_cast<uint4*>(out + r * cols);
+#pragma unroll 2
+    for (int i = threadIdx.x; i < nv; i += 1024) {
+      const uint4 u = row[i];
+      uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[W];
+        word_to_floats<T>(w[q], f);
+#pragma unroll
+        for (int e = 0; e < W; ++e) {
+          if constexpr (LOG) {
+            f[e] = (f[e] - m_row) - kk;
+          } else if constexpr (sizeof(T) == 2) {
+            f[e] = nan_row ? __int_as_float(0x7fc00000) : fast_exp2(fmaf(f[e], kLog2e, neg_mrow_l2e)) * kk;
+          } else {
+            // (a slice of -inf only still holds -inf, not exp: its outputs are zeros unless the whole row is -inf)
+            f[e] = nan_row ? __int_as_float(0x7fc00000) : (m == -INFINITY ? 0.f : f[e] * kk);
+          }
+        }
+        w[q] = floats_to_word<T>(f);
+      }
+      d4[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __syncthreads();                                 // `row` may be refilled
+    if (++b == stages) { b = 0; phase ^= 1u; }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // rows that do not fit a cluster: online (max, sum), then a second read
 // ---------------------------------------------------------------------------
 template <typename T, bool LOG>
@@ -334,7 +558,8 @@ int launch_typed(const b200attn_softmax_args_t& a, int sm_count, cudaStream_t st
   const size_t row_bytes = static_cast<size_t>(cols) * sizeof(T);
   constexpr int E = 16 / static_cast<int>(sizeof(T));
   constexpr int kMaxVpt = 32 / E;                      // 32 elements per thread
-  if (VEC && cols / E <= 1024LL * kMaxVpt) {
+  constexpr int kPrefVpt = 16 / E;                     // 16 elements per thread: 32 registers, two 1024-thread CTAs per SM
+  if (VEC && cols / E <= 1024LL * kPrefVpt) {
     const int nv = static_cast<int>(cols / E);
     int threads = 64;
     while (threads < 1024 && threads * 4 < nv) threads *= 2;
@@ -346,10 +571,81 @@ int launch_typed(const b200attn_softmax_args_t& a, int sm_count, cudaStream_t st
       case 1: softmax_reg_kernel<T, LOG, 1><<<grid, threads, 0, stream>>>(x, out, rows, cols); break;
       case 2: softmax_reg_kernel<T, LOG, 2><<<grid, threads, 0, stream>>>(x, out, rows, cols); break;
       case 4: softmax_reg_kernel<T, LOG, 4><<<grid, threads, 0, stream>>>(x, out, rows, cols); break;
-      default:
-        if constexpr (kMaxVpt >= 8) softmax_reg_kernel<T, LOG, 8><<<grid, threads, 0, stream>>>(x, out, rows, cols);
-        break;
+      default: break;                                 // (not reached: vpt <= kPrefVpt <= 4)
     }
+  } else if (VEC && row_bytes <= static_cast<size_t>(kPipeSliceBytes) * kMaxCluster) {
+    // measured against the alternatives below on every length from 24 576 elements up: the pipelined kernel wins
+    const long long nv = cols / E;
+    int csize = 1;
+    while ((nv + csize - 1) / csize * 16 > kPipeSliceBytes) csize *= 2;
+    const int slice = static_cast<int>((nv + csize - 1) / csize);
+    const int stages = std::max(2, std::min<int>(kPipeStages, 2 * kPipeSliceBytes / (slice * 16)));
+    const size_t smem = static_cast<size_t>(slice) * 16 * stages;
+    auto kernel = softmax_pipe_kernel<T, LOG>;
+    int rc = set_smem_limit(kernel, smem);
+    if (rc) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(1024, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = csize > 1 ? 1 : 0;
+    // the grid is exactly what the GPU holds at once (each CTA or cluster loops over rows)
+    thread_local int key_csize = 0, resident = 0;
+    thread_local size_t key_smem = 0;
+    if (key_csize != csize || key_smem != smem) {
+      int n = 0;
+      if (csize > 1) {
+        cfg.gridDim = dim3(static_cast<unsigned>(sm_count / csize * csize), 1, 1);
+        cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveClusters(softmax)");
+      } else {
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 1024, smem);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveBlocksPerMultiprocessor(softmax)");
+        n *= sm_count;
+      }
+      resident = std::max(1, n);
+      key_csize = csize;
+      key_smem = smem;
+    }
+    const long long clusters = std::min<long long>(rows, resident);
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * csize), 1, 1);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, x, out, rows, cols, slice, csize, stages);
+    if (e != cudaSuccess) return cuda_fail(e, "softmax pipelined kernel launch");
+  } else if (VEC && cols / E <= 1024LL * kMaxVpt * kMaxCluster) {
+    // up to 1 MiB: the row in the registers of eight CTAs, 32 elements per thread
+    const int csize = kMaxCluster;
+    auto kernel = softmax_regc_kernel<T, LOG, kMaxVpt>;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(1024, 1, 1);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // the grid is exactly the clusters the GPU holds at once (each loops over rows); asked of the driver once.  The
+    // answer depends on the device model only, and only B200 is accepted.
+    static int cached = 0;
+    if (cached == 0) {
+      cfg.gridDim = dim3(static_cast<unsigned>(sm_count / csize * csize), 1, 1);
+      int n = 0;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaOccupancyMaxActiveClusters(softmax)");
+      cached = std::max(1, n);
+    }
+    const long long clusters = std::min<long long>(rows, cached);
+    cfg.gridDim = dim3(static_cast<unsigned>(clusters * csize), 1, 1);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, x, out, rows, cols);
+    if (e != cudaSuccess) return cuda_fail(e, "softmax register cluster kernel launch");
   } else if (row_bytes <= static_cast<size_t>(kRowSmemBytes)) {
     // threads: enough for 16-byte pieces to keep every lane busy on short rows, 1024 on long ones
     int threads = 64;
