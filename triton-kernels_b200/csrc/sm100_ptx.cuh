@@ -1,6 +1,7 @@
-// Inline-PTX wrappers for the Blackwell (sm_100a) features the prefill kernel uses:
-// mbarrier, TMA tiled loads, tensor memory (TMEM) allocation / load / store and
-// tcgen05.mma with shared-memory descriptors.  Every copy targets this CTA only (no clusters).
+// Inline-PTX wrappers for the Blackwell (sm_100a) features the kernels use: mbarrier, TMA tiled loads and untiled bulk
+// loads, tensor memory (TMEM) allocation / load / store, tcgen05.mma with shared-memory descriptors.  Every copy lands
+// in the issuing CTA's own shared memory; the only cluster traffic is st_async_pair (8-byte remote stores between the
+// CTAs of a softmax cluster).
 #pragma once
 
 #include <cuda.h>
