@@ -132,6 +132,23 @@ def test_extreme_values(dtype):
     assert torch.isnan(n).all()
 
 
+@pytest.mark.parametrize("log", [False, True])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(4, 4096), (3, 16384), (2, 40000), (2, 131072), (2, 524288)])
+def test_large_magnitudes_on_the_vector_paths(shape, dtype, log):
+    """Values of huge magnitude with ties at the maximum, on every 16-byte path: the difference x - max has to be taken
+    before anything is scaled, or the exponent's rounding error (proportional to |max|) ruins the result."""
+    big = 3e4 if dtype == torch.float16 else 1e30
+    g = torch.Generator().manual_seed(shape[1])
+    levels = torch.tensor([0.0, 0.5 * big, big, -big])
+    x = levels[torch.randint(0, 4, shape, generator=g)].to(dtype).to(DEV)
+    got = _fn(log)(x)
+    exp = _expected(x, log)
+    assert torch.equal(torch.isinf(got).cpu(), torch.isinf(exp)) and not torch.isnan(got).any()
+    fin = torch.isfinite(exp)
+    torch.testing.assert_close(got.cpu()[fin], exp[fin])
+
+
 def test_rows_sum_to_one_at_scale():
     """Size-independent property on a tensor far beyond what the CPU oracle is run on: rows sum to 1, entries are
     in [0, 1], exp(log_softmax) equals softmax, softmax is invariant under a per-row shift."""

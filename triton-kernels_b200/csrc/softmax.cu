@@ -245,13 +245,13 @@ __device__ __forceinline__ void softmax_reg_body(const T* x, T* out, long long r
     const float m = block_max(mx, scratch);
     float sum = 0.f;
     if (m != -INFINITY) {
-      const float neg_m_l2e = -m * kLog2e;
 #pragma unroll
       for (int j = 0; j < VPT * E; ++j) {
-        // 16-bit outputs round away far more than the approximate exponential loses: exp2(x log2e - m log2e), one
-        // FMA and one MUFU operation; fp32 outputs need expf.  exp(-inf) = 0 for the padding.
+        // 16-bit outputs round away far more than the approximate exponential loses: exp2((x - m) log2e), the
+        // difference first (it is exact for x near m, whatever the magnitude of m); fp32 outputs need expf.
+        // exp(-inf) = 0 for the padding.
         float ev;
-        if constexpr (sizeof(T) == 2) ev = fast_exp2(fmaf(f[j], kLog2e, neg_m_l2e));
+        if constexpr (sizeof(T) == 2) ev = fast_exp2((f[j] - m) * kLog2e);
         else ev = expf(f[j] - m);
         sum += ev;
         if constexpr (!LOG) f[j] = ev;
@@ -430,22 +430,35 @@ softmax_pipe_kernel(const T* x, T* out, long long rows, long long cols, int slic
     if (nv > 0) ok = ptx::mbar_wait(smem_u32(&full_bar[b]), phase) && ok;
     uint4* row = base + static_cast<size_t>(b) * slice;
     float mx = -INFINITY;
+    if constexpr (sizeof(T) == 2) {
+      // the maximum of 16-bit values is exact in 16 bits: one packed instruction per two elements, unpacked once
+      using T2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+      const uint32_t ninf2 = std::is_same<T, __half>::value ? 0xfc00fc00u : 0xff80ff80u;
+      uint32_t acc = ninf2;
 #pragma unroll 2
-    for (int i = threadIdx.x; i < nv; i += 1024) {
-      const uint4 u = row[i];
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+      for (int i = threadIdx.x; i < nv; i += 1024) {
+        const uint4 u = row[i];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        float f[W];
-        word_to_floats<T>(w[q], f);
-#pragma unroll
-        for (int e = 0; e < W; ++e) mx = fmaxf(mx, f[e]);
+        for (int q = 0; q < 4; ++q) {
+          const T2 t = __hmax2(*reinterpret_cast<const T2*>(&acc), *reinterpret_cast<const T2*>(&w[q]));
+          acc = *reinterpret_cast<const uint32_t*>(&t);
+        }
+      }
+      float f[2];
+      word_to_floats<T>(acc, f);
+      mx = fmaxf(f[0], f[1]);
+    } else {
+#pragma unroll 2
+      for (int i = threadIdx.x; i < nv; i += 1024) {
+        const uint4 u = row[i];
+        mx = fmaxf(mx, fmaxf(fmaxf(__uint_as_float(u.x), __uint_as_float(u.y)),
+                             fmaxf(__uint_as_float(u.z), __uint_as_float(u.w))));
       }
     }
     const float m = block_max(mx, scratch);
     float sum = 0.f;
     if (m != -INFINITY) {
-      const float neg_m_l2e = -m * kLog2e;
 #pragma unroll 2
       for (int i = threadIdx.x; i < nv; i += 1024) {
         const uint4 u = row[i];
@@ -457,7 +470,7 @@ softmax_pipe_kernel(const T* x, T* out, long long rows, long long cols, int slic
 #pragma unroll
           for (int e = 0; e < W; ++e) {
             if constexpr (sizeof(T) == 2) {
-              sum += fast_exp2(fmaf(f[e], kLog2e, neg_m_l2e));
+              sum += fast_exp2((f[e] - m) * kLog2e);
             } else {
               const float ev = expf(f[e] - m);
               sum += ev;
@@ -488,7 +501,9 @@ softmax_pipe_kernel(const T* x, T* out, long long rows, long long cols, int slic
     if (!ok) l = __int_as_float(0x7fc00000);         // a bounded wait ran out: NaN rows, never a hang
     float kk = final_constant<LOG>(m_row, l);
     if constexpr (!LOG && sizeof(T) == 4) kk *= own;
-    const float neg_mrow_l2e = -m_row * kLog2e;
+    // 16-bit softmax: exp(x - m) / l = exp2((x - m) log2e - log2 l), the division folded into the exponent (l >= 1
+    // whenever the row has a finite maximum)
+    const float neg_log2_l = LOG ? 0.f : -__log2f(l);
     const bool nan_row = m_row == -INFINITY;
     uint4* d4 = reinterpret_cast<uint4*>(out + r * cols);
 #pragma unroll 2
@@ -504,7 +519,7 @@ softmax_pipe_kernel(const T* x, T* out, long long rows, long long cols, int slic
           if constexpr (LOG) {
             f[e] = (f[e] - m_row) - kk;
           } else if constexpr (sizeof(T) == 2) {
-            f[e] = nan_row ? __int_as_float(0x7fc00000) : fast_exp2(fmaf(f[e], kLog2e, neg_mrow_l2e)) * kk;
+            f[e] = nan_row ? __int_as_float(0x7fc00000) : fast_exp2(fmaf(f[e] - m_row, kLog2e, neg_log2_l));
           } else {
             // (a slice of -inf only still holds -inf, not exp: its outputs are zeros unless the whole row is -inf)
             f[e] = nan_row ? __int_as_float(0x7fc00000) : (m == -INFINITY ? 0.f : f[e] * kk);
