@@ -68,6 +68,22 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return warp_sum(r);
 }
 
+// the same without the leading barrier: the caller guarantees a barrier between the last read of `scratch` and this call
+__device__ __forceinline__ float block_max_nolead(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  return warp_max(lane < nw ? scratch[lane] : -INFINITY);
+}
+__device__ __forceinline__ float block_sum_nolead(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  return warp_sum(lane < nw ? scratch[lane] : 0.f);
+}
+
 template <typename T> struct Vec16 { static constexpr int kElems = 16 / sizeof(T); };
 
 template <typename T> __device__ __forceinline__ float fast_or_exact_exp(float x) {
@@ -384,7 +400,8 @@ softmax_pipe_kernel(const T* x, T* out, long long rows, long long cols, int slic
   constexpr int W = E / 4;
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  __shared__ float scratch[32];
+  __shared__ float scratch[2][32];                   // [0] for the maxima, [1] for the sums: each is rewritten only
+                                                     // after the barrier that ends the row
   __shared__ __align__(8) float2 pairs[2][kMaxCluster];
   __shared__ __align__(8) uint64_t pair_bar[2];
   __shared__ __align__(8) uint64_t full_bar[kPipeStages];
@@ -456,7 +473,7 @@ softmax_pipe_kernel(const T* x, T* out, long long rows, long long cols, int slic
                              fmaxf(__uint_as_float(u.z), __uint_as_float(u.w))));
       }
     }
-    const float m = block_max(mx, scratch);
+    const float m = block_max_nolead(mx, scratch[0]);
     float sum = 0.f;
     if (m != -INFINITY) {
 #pragma unroll 2
@@ -472,7 +489,9 @@ softmax_pipe_kernel(const T* x, T* out, long long rows, long long cols, int slic
             if constexpr (sizeof(T) == 2) {
               sum += fast_exp2((f[e] - m) * kLog2e);
             } else {
-              const float ev = expf(f[e] - m);
+              // ex2.approx is within 2^-22 relative, the scaled difference within 2^-24 of its own magnitude: inside
+              // the fp32 tolerance, and what the reference's tl.exp compiles to
+              const float ev = fast_exp2((f[e] - m) * kLog2e);
               sum += ev;
               if constexpr (!LOG) w[q] = __float_as_uint(ev);   // fp32 softmax keeps exp(x - m) in place
             }
@@ -481,7 +500,7 @@ softmax_pipe_kernel(const T* x, T* out, long long rows, long long cols, int slic
         if constexpr (sizeof(T) == 4 && !LOG) row[i] = make_uint4(w[0], w[1], w[2], w[3]);
       }
     }
-    float l = block_sum(sum, scratch);
+    float l = block_sum_nolead(sum, scratch[1]);
     float m_row = m, own = 1.f;
     if (csize > 1) {
       const unsigned parity = iter & 1u;
