@@ -16,8 +16,8 @@
 // Clusters exchange their (max, sum) pairs through distributed shared memory; the pipelined and register kernels do it
 // with asynchronous remote stores that count on the receiver's mbarrier, because a cluster-wide barrier also waits
 // for the previous row's global stores.
-// All arithmetic is fp32 (expf / logf; for 16-bit types one FMA and one ex2 per exponential), like the reference's
-// `.to(tl.float32)`.  `out` may alias `x`: a row is written only after all of it has been staged (the streaming kernel
+// All arithmetic is fp32, like the reference's `.to(tl.float32)`: expf for fp32 rows in registers, ex2.approx of
+// (x - max) * log2(e) for 16-bit types and for fp32 rows in the pipelined kernel (tl.exp compiles to the same).  `out` may alias `x`: a row is written only after all of it has been staged (the streaming kernel
 // reads element i right before it writes element i), and rows staged ahead of time are other rows.
 #include <cooperative_groups.h>
 
