@@ -149,6 +149,31 @@ def test_large_magnitudes_on_the_vector_paths(shape, dtype, log):
     torch.testing.assert_close(got.cpu()[fin], exp[fin])
 
 
+def test_seeded_sweep_around_the_kernel_limits():
+    """Seeded random cases at and next to every row length where the launcher changes kernel, cluster size or stage
+    count, some with a tail of -inf, against the float64 oracle."""
+    import random
+
+    rnd = random.Random(1)
+    edges = [4096, 8192, 16384, 16388, 24576, 27648, 27652, 32768, 55296, 55300, 65536, 110592, 110600, 131072, 221184,
+             221188, 262144, 262148, 442368, 442376, 524288, 524296]
+    for _ in range(80):
+        dtype = rnd.choice(DTYPES)
+        cols = max(1, rnd.choice(edges) + rnd.choice([0, 0, -8, 8, -4, 4, -1, 1, rnd.randint(-3000, 3000)]))
+        rows = max(1, min(rnd.choice([1, 2, 3, 7, 37, 150]), 2_000_000 // cols))
+        log = rnd.random() < 0.5
+        g = torch.Generator().manual_seed(cols)
+        x = (torch.randn((rows, cols), generator=g) * rnd.choice([0.5, 3.0, 20.0])).to(dtype)
+        if rnd.random() < 0.3:
+            x[:, rnd.randint(0, cols - 1):] = -float("inf")
+        x = x.to(DEV)
+        got = _fn(log)(x).cpu()
+        exp = _expected(x, log)
+        assert torch.equal(torch.isinf(got), torch.isinf(exp)) and not torch.isnan(got).any(), (dtype, rows, cols, log)
+        fin = torch.isfinite(exp)
+        torch.testing.assert_close(got[fin], exp[fin], msg=lambda m: f"{dtype} {rows}x{cols} log={log}: {m}")
+
+
 def test_rows_sum_to_one_at_scale():
     """Size-independent property on a tensor far beyond what the CPU oracle is run on: rows sum to 1, entries are
     in [0, 1], exp(log_softmax) equals softmax, softmax is invariant under a per-row shift."""
