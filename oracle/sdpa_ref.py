@@ -10,11 +10,15 @@ softmax(QK^T/sqrt(D))V in fp64 numpy so the oracle does not hinge on a torch
 version, and ``tests/test_oracle.py`` pins one against the other and against
 the committed golden vectors.
 
-Parity status: the reference holds no golden vectors, no seeds and no
-known-answer literals for this path, and its kernels cannot run without a GPU,
-so the pins are (1) SDPA == the fp64 restatement, (2) analytic known-answer
-cases, (3) golden vectors generated here from SDPA with the committed script
-``tests/golden/make_golden.py``.
+Parity status: pinned to the reference's own oracle functions.  The reference holds no
+stored vectors, seeds or known-answer literals for this path and its kernels cannot run
+without a GPU, but its tests' ``get_reference_outputs`` / ``allocate_paged_cache`` /
+tolerance functions are pure torch and run on CPU.  ``tests/golden/make_golden.py`` imports
+them from a reference checkout and records their outputs on seeded inputs;
+``tests/test_oracle.py`` checks this restatement against those fixtures, against the fp64
+restatement and against analytic known answers.  On a GPU the reference's three test
+modules themselves run unmodified against the package (``oracle/stage_reference_tests.py``,
+``tests/test_zr_reference_suite.py``).
 
 Only ``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline / reference
 arm of ``bench.py`` may import this module.  The product path never does.

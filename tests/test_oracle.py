@@ -112,9 +112,13 @@ def test_packers_roundtrip():
 
 
 def test_golden_vectors():
-    """Committed fixtures (tests/golden/make_golden.py) must reproduce from the oracle."""
+    """The committed fixtures hold outputs of the REFERENCE's own oracle functions (its tests'
+    get_reference_outputs, imported from the reference checkout by tests/golden/make_golden.py);
+    the restatement in oracle/sdpa_ref.py must reproduce them."""
     blob = torch.load(GOLDEN)
-    assert len(blob["cases"]) >= 6
+    assert blob["source"] == "reference tests' get_reference_outputs"
+    kinds = [c["kind"] for c in blob["cases"]]
+    assert kinds.count("prefill") >= 3 and kinds.count("decode") >= 2 and kinds.count("spec") >= 3
     for case in blob["cases"]:
         kind = case["kind"]
         if kind == "prefill":
@@ -122,8 +126,30 @@ def test_golden_vectors():
         elif kind == "decode":
             out = sdpa_ref.decode_reference([case["q"]], [case["k"]], [case["v"]], case["qh"], case["kvh"])[0]
         else:
-            out = sdpa_ref.spec_decode_reference([case["q"]], [case["k"]], [case["v"]], case["qh"], case["kvh"], case["causal"])[0]
+            k, v = case["k"], case["v"]
+            if case["causal"]:
+                # the reference oracle appends the draft K/V itself (tests/test_speculative_decode.py:84-94);
+                # the restatement takes what the kernel sees: K/V with the drafts already at the tail
+                k, v = torch.cat([k, case["dk"]]), torch.cat([v, case["dv"]])
+            out = sdpa_ref.spec_decode_reference([case["q"]], [k], [v], case["qh"], case["kvh"], case["causal"])[0]
+        assert out.dtype == case["out"].dtype == torch.float32 and out.shape == case["out"].shape
         torch.testing.assert_close(out, case["out"], atol=1e-5, rtol=1e-5)
+
+
+def test_golden_paged_fixture_and_tolerances():
+    """pack_paged with its defaults is the reference fixture's scatter (tests/test_attention.py:101-134,
+    tests/test_decode.py:93-130, tests/test_speculative_decode.py:129-166) bit for bit, and
+    attn_tolerances is the reference's rule (tests/test_attention.py:27-30)."""
+    blob = torch.load(GOLDEN)
+    assert len(blob["paged"]) == 3
+    for fx in blob["paged"]:
+        cache, table, lens = sdpa_ref.pack_paged(fx["seqs"], 16)
+        assert lens.tolist() == fx["lens"]
+        assert torch.equal(cache, fx["cache"]) and torch.equal(table, fx["table"])
+    assert len(blob["tolerances"]) == 15
+    for t in blob["tolerances"]:
+        got = sdpa_ref.attn_tolerances(t["dtype"], t["n"])
+        assert got == dict(atol=t["atol"], rtol=t["rtol"])
 
 
 def test_c1_cpu_config_runs():
