@@ -14,9 +14,15 @@ A step is one call of the entry point on one batch of seeded synthetic inputs.
           rank, inputs resident in HBM, CUDA events on the launch stream, L2 flushed between steps.
   e2e   : the same quantity through the Python entry point with the per-step inputs in pinned host
           memory: H2D copies, the call, and the D2H copy of the output are all inside the timed region
-          (upload, kernels and download on three streams, two sets of device input buffers).
-Multi-GPU runs are weak scaling: every rank runs the full single-GPU configuration on its own
-seeded inputs (global batch = N x the configuration's batch); there is no data-path collective.
+          (upload, kernels and download on three streams, two sets of device input buffers).  Every step
+          is timed by its own event pair; the figure is the median step, with min / max, the PCIe link and
+          the achieved copy rates beside it.
+Multi-GPU runs: the headline `value` is weak scaling (every rank runs the full single-GPU configuration
+on its own seeded inputs, global batch = N x the configuration's batch, no data-path collective).  At
+N > 1 every workload also carries a "strong" entry: ONE problem cut the way the configuration names
+(dense prefill by batch x KV-head units, ragged prefill by balanced token cost, paged decode by batch,
+speculative decode by KV head), timed as max over ranks, and - once, outside the timed region - the
+shards are all-gathered over NCCL and compared with the same problem computed on rank 0's GPU.
 """
 from __future__ import annotations
 
@@ -41,8 +47,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0}
 L2_FLUSH_BYTES = 512 << 20
 
-# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/prefill_kernel_c2_c3.md and profiles/decode_mma_kernel_c4_c5.md.
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum), one ncu capture per kernel and workload.
 NCU_TRAFFIC_BYTES = {"c2": 54.1e6, "c3": 778.6e6, "c4": 1137.7e6, "c5": 1788.3e6}
 # kernels of this library launched per call of the entry point (prefill: the persistent kernel;
 # decode: planner + split kernel with fused merge)
@@ -224,43 +229,75 @@ def time_end_to_end(wl, steps, warmup, world):
     torch.cuda.synchronize()
     barrier(world)
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(s_comp)
-    s_in.wait_event(e0)
-    s_out.wait_event(e0)
+    # one event per step, recorded behind the step's download: the interval between two of them is what one more
+    # step costs the pipeline (upload, kernels and download of neighbouring steps overlap)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    s_out.wait_stream(s_comp)
+    marks[0].record(s_out)
+    s_in.wait_event(marks[0])
+    s_comp.wait_event(marks[0])
     for i in range(steps):
         step(i)
-    s_comp.wait_stream(s_in)
-    s_comp.wait_stream(s_out)
-    e1.record(s_comp)
+        marks[i + 1].record(s_out)
     torch.cuda.synchronize()
     barrier(world)
     for n in wl.host_inputs:
         wl.tensors[n] = dev_sets[0][n]
-    return e0.elapsed_time(e1) / steps, h2d, d2h
+    intervals = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
+    return intervals, h2d, d2h
 
 
-def measure(name, device, rank, world, steps, warmup, seed, peaks, flush, e2e_steps):
+def pcie_link(index):
+    """Current PCIe link of the GPU (read-only query), e.g. {"gen": 5, "width": 16}."""
+    try:
+        out = subprocess.run(["nvidia-smi", "--query-gpu=pcie.link.gen.current,pcie.link.width.current",
+                              "--format=csv,noheader,nounits", "-i", str(index)], capture_output=True, text=True,
+                             timeout=20).stdout.strip().splitlines()[0]
+        gen, width = [int(x.strip()) for x in out.split(",")]
+        # usable payload rate per direction, GB/s: 128b/130b encoding from gen 3 on, ~1 GB/s per lane at gen 3
+        rate = {1: 0.25, 2: 0.5, 3: 0.985, 4: 1.969, 5: 3.938, 6: 7.56}.get(gen, 0.0) * width
+        return {"gen": gen, "width": width, "nominal_gbs_per_direction": round(rate, 1)}
+    except Exception:  # noqa: BLE001 - the query is informational
+        return None
+
+
+def summarize_e2e(intervals, h2d, d2h, work_all, scale, unit, world, device, link):
+    """Median / min / max of the per-step intervals (max over ranks of each), achieved copy rates, and what bounds it."""
+    med = dist_max(statistics.median(intervals), world, device)
+    lo = dist_max(min(intervals), world, device)
+    hi = dist_max(max(intervals), world, device)
+    mean = dist_max(sum(intervals) / len(intervals), world, device)
+    res = {"value": work_all * scale / (med * 1e-3), "unit": unit, "ms_per_step": med, "ms_min": lo, "ms_max": hi,
+           "ms_mean": mean, "steps": len(intervals), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+           "h2d_gbs": h2d / (med * 1e-3) * 1e-9, "d2h_gbs": d2h / (med * 1e-3) * 1e-9, "pcie": link}
+    return res
+
+
+def measure(name, device, rank, world, steps, warmup, seed, peaks, flush, e2e_steps, link):
     wl = build_workload(name, device, rank, world, seed)
     times = time_resident(wl, steps, warmup, flush, world)
     ms = sum(times) / len(times)
     ms_max = dist_max(ms, world, device)
     work = wl.flops if wl.kind == "prefill" else wl.kv_bytes
     work_all = dist_sum(work, world, device)
-    e2e_ms, h2d, d2h = time_end_to_end(wl, e2e_steps, 2, world)
-    e2e_ms_max = dist_max(e2e_ms, world, device)
     if wl.kind == "prefill":
         unit, scale, bound, peak_key = "TFLOP/s", 1e-12, "tensor", "bf16_tflops"
     else:
         unit, scale, bound, peak_key = "GB/s", 1e-9, "hbm", "hbm_gbs"
+    intervals, h2d, d2h = time_end_to_end(wl, e2e_steps, 5, world)
+    e2e = summarize_e2e(intervals, h2d, d2h, work_all, scale, unit, world, device, link)
+    # what the end-to-end step cannot beat: the larger copy direction over the link, or the kernel itself
+    if link and link.get("nominal_gbs_per_direction"):
+        copy_ms = max(h2d, d2h) / (link["nominal_gbs_per_direction"] * 1e9) * 1e3
+        e2e["bound"] = {"copy_ms_at_link_rate": copy_ms, "kernel_ms": ms,
+                        "limiter": "pcie copies" if copy_ms > ms else "kernel"}
     value = work_all * scale / (ms_max * 1e-3)
     achieved = work * scale / (ms * 1e-3)          # this rank's kernel
     peak = peaks[peak_key]
     res = {
         "workload": wl.name, "value": value, "unit": unit, "ms_per_step": ms_max,
         "ms_min": min(times), "ms_median": statistics.median(times),
-        "e2e": {"value": work_all * scale / (e2e_ms_max * 1e-3), "unit": unit, "ms_per_step": e2e_ms_max,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": e2e,
         "roofline": {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
                      "frac_of_nominal": achieved / NOMINAL[peak_key], "peak_source": peaks["source"],
                      "traffic": NCU_TRAFFIC_BYTES[name]},
@@ -268,6 +305,65 @@ def measure(name, device, rank, world, steps, warmup, seed, peaks, flush, e2e_st
         "algorithmic_work_per_step": work, "meta": {k: v for k, v in wl.meta.items() if k != "lengths"},
     }
     del wl
+    torch.cuda.empty_cache()
+    if world > 1:
+        res["strong"] = measure_strong(name, device, rank, world, steps, warmup, seed, peaks, flush, scale, unit, peak_key)
+    return res
+
+
+def measure_strong(name, device, rank, world, steps, warmup, seed, peaks, flush, scale, unit, peak_key):
+    """ONE problem cut across the ranks the way the configuration names; max over ranks; plus, outside the timed
+    region, the all-gather of the shards over NCCL compared with the whole problem computed on rank 0's GPU."""
+    import torch.distributed as dist
+
+    from benchmarks import workloads as W
+    from sharding import all_gather_outputs, all_gather_ragged
+
+    shard, full, assemble = W.STRONG[name](device, seed, rank, world)
+    work_full = full.flops if full.kind == "prefill" else full.kv_bytes
+    work_mine = shard.flops if shard.kind == "prefill" else shard.kv_bytes
+    # --- the check: gather the shards and compare with the whole problem on one GPU
+    out = shard.run()
+    torch.cuda.synchronize()
+    gather = all_gather_ragged if name == "c3" else all_gather_outputs
+    parts = gather(out)                     # warm-up of the collective
+    torch.cuda.synchronize()
+    barrier(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    parts = gather(out)
+    e1.record()
+    torch.cuda.synchronize()
+    gather_us = dist_max(e0.elapsed_time(e1) * 1e3, world, device)
+    check = None
+    if rank == 0:
+        whole = full.run()
+        got = assemble(parts)
+        torch.cuda.synchronize()
+        diff = (got.float() - whole.float()).abs().max().item() if whole.numel() else 0.0
+        check = {"sharded_equals_single": bool(torch.equal(got, whole)), "max_abs_diff": diff,
+                 "gather_us": gather_us, "gathered_bytes": got.numel() * got.element_size()}
+        del whole, got
+    del parts, out
+    # only the shard stays resident for the timing (rank 0 held the whole problem for the check)
+    shard_names = set(id(t) for t in shard.tensors.values())
+    for k in list(full.tensors):
+        if id(full.tensors[k]) not in shard_names:
+            full.tensors[k] = None
+    del full
+    torch.cuda.empty_cache()
+    times = time_resident(shard, steps, warmup, flush, world)
+    ms = sum(times) / len(times)
+    ms_max = dist_max(ms, world, device)
+    ms_min_rank = -dist_max(-ms, world, device)
+    res = {"value": work_full * scale / (ms_max * 1e-3), "unit": unit, "ms_per_step": ms_max,
+           "ms_fastest_rank": ms_min_rank, "frac_per_gpu": work_full * scale / (ms_max * 1e-3) / world / peaks[peak_key],
+           "work_share_of_slowest": dist_max(work_mine, world, device) / work_full,
+           "parallelism": {"c2": "batch x KV-head units, contiguous", "c3": "sequences by balanced causal cost (LPT)",
+                           "c4": "batch, contiguous", "c5": "KV heads, contiguous"}[name]}
+    if check is not None:
+        res["check"] = check
+    del shard
     torch.cuda.empty_cache()
     return res
 
@@ -382,11 +478,12 @@ def main():
     if sampler:
         sampler.start()
     order = [args.workload] + ([] if args.only else [n for n in ("c2", "c3", "c4", "c5") if n != args.workload])
+    link = pcie_link(local_rank)
     results = {}
     for i, name in enumerate(order):
         steps = args.steps if i == 0 else max(5, min(args.steps, 10))
         results[name] = measure(name, device, rank, world, steps, args.warmup, args.seed, peaks, flush,
-                                e2e_steps=max(3, min(steps, 10)))
+                                e2e_steps=30 if name != "c3" else 20, link=link)
     clocks = sampler.stop() if sampler else None
     torch.cuda.synchronize()
     _native.check_device_errors()
@@ -399,14 +496,16 @@ def main():
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
             "config": {"workload": main_res["workload"], "l2": "flushed between timed steps (512 MiB memset)",
-                       "timing": "CUDA events per step on the launch stream, mean over steps, max over ranks",
+                       "timing": "CUDA events per step on the launch stream, mean over steps, max over ranks; "
+                                 "e2e: median of per-step event intervals",
                        "parallelism": f"independent replicas x{world} (batch-sharded, no collective)",
                        **main_res["meta"]},
-            "e2e": {k: main_res["e2e"][k] for k in ("value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step")},
+            "e2e": main_res["e2e"],
             "gpu_launches": main_res["gpu_launches"],
             "roofline": main_res["roofline"],
             "clocks": clocks,
-            "workloads": {n: {k: r[k] for k in ("workload", "value", "unit", "ms_per_step", "ms_min", "e2e", "roofline")}
+            "workloads": {n: {k: r[k] for k in ("workload", "value", "unit", "ms_per_step", "ms_min", "e2e", "roofline",
+                                                "strong") if k in r}
                           for n, r in results.items()},
         }
         if world == 1:

@@ -164,17 +164,39 @@ int b200attn_decode(const b200attn_decode_args_t* args, void* cuda_stream);
  *
  *  - Problems whose scratch need (b200attn_decode_workspace_bytes) exceeds 8 MiB are refused with
  *    B200ATTN_E_WORKSPACE; use b200attn_decode for those.
- *  - The first call on each device looks up the array's device address (one driver query, no
- *    allocation); make that first call before starting any stream capture.
+ *  - The first call on each device loads the library's device code on that GPU (which is what reserves
+ *    the 8 MiB there) and looks up the array's device address; it takes device memory and it may fail
+ *    once a framework has frozen its allocator or is capturing a stream.  Make that first call at
+ *    start-up, before any stream capture; b200attn_decode_static_check on the device does the same
+ *    set-up and is a convenient way to pay for it early.  Later calls allocate nothing.
  *  - All calls on a device share the one array.  Calls must not overlap on the GPU (two streams,
  *    two threads): they would overwrite each other's partials.  Back-to-back calls on one stream
  *    are fine; nothing needs clearing in between.
- *  - Device-side error codes (block-table entry out of range) are not reported through this entry
- *    point; such entries are still skipped, never dereferenced.
+ *  - Device-side error codes (1 bounded wait expired, 2 block-table entry out of range, 3 planner
+ *    overflow) land in word 0 of the array, where the caller cannot see them: read them with
+ *    b200attn_decode_static_check.  The word is sticky until that call clears it.  A CTA whose
+ *    wait expired writes NaN rows, so the failure also shows in the output; out-of-range block-table
+ *    entries are skipped, never dereferenced.
  *
  * This function has no counterpart in the reference.
  */
 int b200attn_decode_static(const b200attn_decode_args_t* args, void* cuda_stream);
+
+/*
+ * Reads and clears the device error word of b200attn_decode_static's built-in array on `device`
+ * (one 4-byte copy on `cuda_stream`, which it synchronises; allocates nothing).  Returns 0, or
+ * B200ATTN_E_DEVICE with the code in *code.  No counterpart in the reference.
+ */
+int b200attn_decode_static_check(int device, void* cuda_stream, int32_t* code);
+
+/*
+ * Self-test of the bounded waits: launches one warp that waits on a barrier nothing completes, with the
+ * kernels' own wait loop limited to `tries` attempts (1..2^20; the kernels use 2^22), so that it gives up
+ * after a fraction of a second, records code 1 in word 0 of `workspace` (>= 256 bytes, zeroed) and
+ * returns.  b200attn_check_workspace then reports B200ATTN_E_DEVICE / code 1 and the context stays
+ * usable.  No counterpart in the reference.
+ */
+int b200attn_selftest_wait_expiry(int device, void* workspace, uint32_t tries, void* cuda_stream);
 
 /*
  * Paged KV-cache append: copies the new rows of every sequence into the pages its block table names.
@@ -227,9 +249,10 @@ typedef struct b200attn_softmax_args_t {
 int b200attn_softmax(const b200attn_softmax_args_t* args, void* cuda_stream);
 
 /*
- * Reads (and clears) the error word a kernel of an earlier call may have set in
- * `workspace` (bounded wait expired, page index out of range).  Synchronises
- * `cuda_stream`.  Returns 0, or B200ATTN_E_DEVICE with the code in *code.
+ * Reads the error word a kernel of an earlier call may have set in `workspace` (bounded wait expired,
+ * page index out of range, planner overflow).  Synchronises `cuda_stream`.  Returns 0, or
+ * B200ATTN_E_DEVICE with the code in *code; in that case the 256-byte header is zeroed again, so that
+ * the workspace can be used for the next call.
  */
 int b200attn_check_workspace(void* workspace, void* cuda_stream, int32_t* code);
 

@@ -180,3 +180,31 @@ def test_two_streams_run_concurrently():
             assert_close_both(po[b].transpose(0, 1), ref, torch.bfloat16, n, "prefill")
             refd = sdpa_ref.decode_reference([qd[b]], [k[b].transpose(0, 1)], [v[b].transpose(0, 1)], QH, KVH)[0]
             assert_close_both(do[b], refd, torch.bfloat16, n, "decode")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("causal", [False, True])
+def test_prefill_outlier_keys_move_the_exponent_reference(dtype, causal):
+    """Keys whose score towers over everything seen so far, planted in the first and in the second 64 keys of a
+    128-key tile and in later tiles: the running exponent reference has to jump (by far more than the 2^8 the
+    kernel tolerates before it rescales), including between the two halves of one tile, where the first half's P
+    is already in tensor memory when the jump comes."""
+    from kernels import flash_attention_v2
+
+    gen = torch.Generator().manual_seed(77)
+    s, d, qh, kvh = 400, 128, 4, 2
+    q = torch.randn((1, qh, s, d), generator=gen)
+    k = torch.randn((1, kvh, s, d), generator=gen)
+    v = torch.randn((1, kvh, s, d), generator=gen)
+    # key t is made parallel to query row r of the first q head of its group, scaled so that the score is ~ +25..+40
+    # (log2 domain: 36..58 above a typical score); rows before and after see it or not depending on the mask
+    for t, r, gain in [(5, 390, 2.2), (70, 200, 2.6), (100, 300, 3.0), (127, 127, 2.4), (130, 350, 2.8), (200, 399, 3.3),
+                       (330, 340, 2.9)]:
+        for h in range(kvh):
+            k[0, h, t] = q[0, h * (qh // kvh), r] * gain / q[0, h * (qh // kvh), r].norm() * (d ** 0.5)
+    q, k, v = q.to(dtype).to(DEV), k.to(dtype).to(DEV), v.to(dtype).to(DEV)
+    out = flash_attention_v2(q, k, v, is_causal=causal)
+    ref = sdpa_ref.prefill_reference([q[0].transpose(0, 1)], [k[0].transpose(0, 1)], [v[0].transpose(0, 1)], qh, kvh, causal)[0]
+    assert torch.isfinite(out.float()).all()
+    assert_close_both(out[0].transpose(0, 1), ref, dtype, s, "outlier keys")

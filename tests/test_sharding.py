@@ -103,3 +103,57 @@ def _failing_worker(rank, world, port):
         raise RuntimeError("injected host-side failure before the collective")
     t = torch.zeros(4)
     dist.all_reduce(t)   # rank 0 must not hang forever: the group times out or the peer's exit is noticed
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("name", ["c2", "c3", "c4", "c5"])
+def test_strong_shards_reassemble_to_the_whole_problem(name, world):
+    """The strong-scaling cut of every benchmark configuration (benchmarks/workloads.STRONG), at a small size on
+    CPU with the oracle playing the kernel: the shards' outputs, put back together by `assemble`, are the whole
+    problem's output, and the shards' algorithmic work adds up to the whole."""
+    from benchmarks import workloads as W
+    from oracle import sdpa_ref
+
+    cpu = torch.device("cpu")
+    cfg = {"c2": dict(batch=2, q_heads=16, kv_heads=8, seq=24, head_dim=16, dtype=torch.float32),
+           "c3": dict(n_seqs=9, lo=3, hi=40, q_heads=8, kv_heads=2, head_dim=16, dtype=torch.float32),
+           "c4": dict(batch=16, lo=5, hi=70, q_heads=8, kv_heads=2, head_dim=16, dtype=torch.float32),
+           "c5": dict(batch=4, drafts=3, lo=5, hi=50, q_heads=16, kv_heads=8, head_dim=16, dtype=torch.float32)}[name]
+
+    def oracle_run(wl):
+        t, m = wl.tensors, wl.meta
+        if name == "c2":
+            b, qh = t["q"].shape[0], t["q"].shape[1]
+            kvh = t["k"].shape[1]
+            outs = sdpa_ref.prefill_reference([t["q"][i].transpose(0, 1) for i in range(b)],
+                                              [t["k"][i].transpose(0, 1) for i in range(b)],
+                                              [t["v"][i].transpose(0, 1) for i in range(b)], qh, kvh, True)
+            return torch.stack([o.transpose(0, 1) for o in outs]) if outs else t["q"][:0]
+        if name == "c3":
+            ip = t["indptr"].tolist()
+            seq = lambda x: [x[ip[i]:ip[i + 1]] for i in range(len(ip) - 1)]
+            outs = sdpa_ref.prefill_reference(seq(t["q"]), seq(t["k"]), seq(t["v"]), t["q"].shape[1], t["k"].shape[1], True)
+            return torch.cat(outs) if outs else t["q"][:0]
+        lens = t["lens"].tolist()
+        ks = [W.gather_paged(t["k_cache"], t["k_table"][i], lens[i], m["page_size"]) for i in range(len(lens))]
+        vs = [W.gather_paged(t["v_cache"], t["v_table"][i], lens[i], m["page_size"]) for i in range(len(lens))]
+        qh, kvh = t["q"].shape[1], t["k_cache"].shape[1]
+        if name == "c4":
+            outs = sdpa_ref.decode_reference([t["q"][i] for i in range(len(lens))], ks, vs, qh, kvh)
+        else:
+            outs = sdpa_ref.spec_decode_reference([t["q"][i] for i in range(len(lens))], ks, vs, qh, kvh, True)
+        return torch.stack(outs) if outs else t["q"][:0]
+
+    parts, flops, kvb = [], 0.0, 0.0
+    for rank in range(world):
+        shard, full, assemble = W.STRONG[name](cpu, 3, rank, world, **cfg)
+        parts.append(oracle_run(shard))
+        flops += shard.flops
+        kvb += shard.kv_bytes
+    got = assemble(parts)
+    want = oracle_run(full)
+    assert got.shape == want.shape
+    torch.testing.assert_close(got.float(), want.float(), atol=1e-6, rtol=1e-6)
+    assert abs(flops - full.flops) <= 1e-9 * full.flops
+    if name in ("c4", "c5"):
+        assert abs(kvb - full.kv_bytes) <= 1e-9 * full.kv_bytes

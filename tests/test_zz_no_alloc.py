@@ -94,6 +94,60 @@ def test_static_scratch_decode_matches_workspace_decode_twice():
         torch.testing.assert_close(b_static[i].float().cpu(), refs[i].cpu(), atol=2e-2, rtol=2e-2)
 
 
+def _static_only(prob, causal):
+    """One b200attn_decode_static call on pre-allocated tensors; returns the output."""
+    from kernels import _native
+
+    out = torch.zeros_like(prob[0])
+    a = _args(*prob, out, causal)
+    _native.check(_native.lib().b200attn_decode_static(C.byref(a), C.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                  "b200attn_decode_static")
+    return out
+
+
+def test_static_scratch_call_takes_no_device_memory():
+    """The property the entry point exists for: once the first call on the device has loaded the module and
+    looked up the array, a call neither allocates through torch nor changes the device's free memory."""
+    from kernels import _native
+
+    prob = _problem(5, [3000, 1500, 700])
+    _static_only(prob, False)                      # first call on this device in this process, or a repeat
+    out = torch.zeros_like(prob[0])
+    a = _args(*prob, out, False)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    allocated, reserved, free = torch.cuda.memory_allocated(), torch.cuda.memory_reserved(), torch.cuda.mem_get_info()[0]
+    _native.check(_native.lib().b200attn_decode_static(C.byref(a), stream), "b200attn_decode_static")
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() == allocated and torch.cuda.memory_reserved() == reserved
+    assert torch.cuda.mem_get_info()[0] == free
+    code = C.c_int32(-1)
+    assert _native.lib().b200attn_decode_static_check(torch.cuda.current_device(), stream, C.byref(code)) == 0
+    assert code.value == 0
+    assert torch.cuda.mem_get_info()[0] == free
+
+
+@pytest.mark.parametrize("case", ["tcgen05_rows_18", "fp32"])
+def test_static_scratch_other_kernels_match_workspace_decode(case):
+    """The shared array under the two other decode kernels: the tcgen05 kernel (more than 16 q rows per KV head) and
+    the fp32 kernel; each twice in a row with different problems."""
+    from kernels import _native
+
+    for seed, lens in [(11, [4000, 90, 1300]), (12, [2500, 2600])]:
+        if case == "fp32":
+            prob, causal = _problem(seed, lens, qh=8, kvh=2, m=2, dtype=torch.float32), True
+        else:
+            prob, causal = _problem(seed, lens, qh=12, kvh=2, m=3), True     # 6 x 3 = 18 rows per KV head
+            a = _args(*prob, torch.zeros_like(prob[0]), causal)
+            assert _native.lib().b200attn_decode_workspace_bytes(C.byref(a)) <= (8 << 20)
+        ws_out, static_out = _run_both(prob, causal)
+        assert torch.isfinite(static_out.float()).all()
+        assert torch.equal(static_out, ws_out)
+    code = C.c_int32(-1)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert _native.lib().b200attn_decode_static_check(torch.cuda.current_device(), stream, C.byref(code)) == 0
+
+
 def test_static_scratch_rejects_problems_beyond_its_size():
     from kernels import _native
 

@@ -202,3 +202,122 @@ def c5_paged_spec_decode(device, seed: int = 0, *, batch: int = 32, drafts: int 
                 head_dim=head_dim, pages=n_pages, tokens=sum(lens)),
         flops, kv_bytes, ["q", "lens", "k_table", "v_table"],
     )
+
+
+# ---------------------------------------------------------------------------
+# Strong scaling: ONE problem (the configuration as named, generated from the seed alone, the same on every rank)
+# cut into the shards the configuration names.  Every builder returns
+#   (shard workload of this rank, the whole problem as a workload, assemble(list of per-rank outputs) -> whole output)
+# so that a caller can compare the gathered shards with the same problem computed on one GPU.
+# ---------------------------------------------------------------------------
+def _clone_workload(full: Workload, run, tensors, flops, kv_bytes, meta_extra) -> Workload:
+    return Workload(full.name, full.kind, run, tensors, dict(full.meta, **meta_extra), flops, kv_bytes,
+                    list(full.host_inputs))
+
+
+def c2_strong(device, seed: int, rank: int, world: int, **cfg):
+    """Dense prefill cut into (batch, KV head) units; a rank owns a contiguous run of them in batch-major order and
+    holds the q heads of its KV heads only, stacked along the batch axis."""
+    from kernels.attention import flash_attention_v2
+    from sharding.planner import batch_head_units
+
+    full = c2_dense_prefill(device, seed, **cfg)
+    m = full.meta
+    group = m["q_heads"] // m["kv_heads"]
+    units = batch_head_units(m["batch"], m["kv_heads"], world, rank)
+    q, k, v = full.tensors["q"], full.tensors["k"], full.tensors["v"]
+    t = dict(q=torch.stack([q[b, h * group:(h + 1) * group] for b, h in units]),
+             k=torch.stack([k[b, h:h + 1] for b, h in units]), v=torch.stack([v[b, h:h + 1] for b, h in units]))
+    frac = len(units) / (m["batch"] * m["kv_heads"])
+    shard = _clone_workload(full, lambda: flash_attention_v2(t["q"], t["k"], t["v"], is_causal=True), t,
+                            full.flops * frac, full.kv_bytes * frac, dict(units=len(units)))
+
+    def assemble(parts):
+        return torch.cat(parts).reshape(m["batch"], m["q_heads"], m["seq"], m["head_dim"])
+
+    return shard, full, assemble
+
+
+def c3_strong(device, seed: int, rank: int, world: int, **cfg):
+    """Ragged prefill: whole sequences dealt to ranks by balanced causal cost (longest first, greedy)."""
+    from kernels.attention import flash_attention_v2
+
+    full = c3_ragged_prefill(device, seed, **cfg)
+    lens = full.meta["lengths"]
+    bins = balance_sequences(lens, world, causal_prefill=True)
+    starts = [0]
+    for n in lens:
+        starts.append(starts[-1] + n)
+    mine = bins[rank]
+    d, qh = full.meta["head_dim"], full.meta["q_heads"]
+
+    def pick(x):
+        if not mine:
+            return x[:0].clone()
+        return torch.cat([x[starts[i]:starts[i + 1]] for i in mine])
+
+    my_lens = [lens[i] for i in mine]
+    indptr = torch.zeros(len(my_lens) + 1, dtype=torch.int64)
+    if my_lens:
+        indptr[1:] = torch.tensor(my_lens, dtype=torch.int64).cumsum(0)
+    t = dict(q=pick(full.tensors["q"]), k=pick(full.tensors["k"]), v=pick(full.tensors["v"]),
+             indptr=indptr.to(full.tensors["indptr"].dtype).to(device))
+    flops = sum(4.0 * d * qh * n * (n + 1) / 2 for n in my_lens)
+    shard = _clone_workload(
+        full, lambda: flash_attention_v2(t["q"], t["k"], t["v"], is_causal=True, q_indptr=t["indptr"], kv_indptr=t["indptr"]),
+        t, flops, float((t["q"].numel() * 2 + 2 * t["k"].numel()) * 2), dict(lengths=my_lens, total_tokens=sum(my_lens)))
+
+    def assemble(parts):
+        out = torch.empty_like(full.tensors["q"])
+        for r, part in enumerate(parts):
+            cur = 0
+            for i in bins[r]:
+                out[starts[i]:starts[i + 1]] = part[cur:cur + lens[i]]
+                cur += lens[i]
+        return out
+
+    return shard, full, assemble
+
+
+def c4_strong(device, seed: int, rank: int, world: int, **cfg):
+    """Paged decode cut by batch: a rank owns a contiguous run of sequences (their q rows, lengths and block-table
+    rows); the page pool is the whole problem's, of which it touches only its sequences' pages."""
+    from kernels.decode import decode_attention
+
+    full = c4_paged_decode(device, seed, **cfg)
+    lens = full.meta["lengths"]
+    b0, b1 = contiguous_shard(len(lens), world, rank)
+    ft = full.tensors
+    t = dict(q=ft["q"][b0:b1].contiguous(), k_cache=ft["k_cache"], v_cache=ft["v_cache"], lens=ft["lens"][b0:b1].contiguous(),
+             k_table=ft["k_table"][b0:b1].contiguous(), v_table=ft["v_table"][b0:b1].contiguous())
+    ps = full.meta["page_size"]
+    frac = sum(lens[b0:b1]) / max(sum(lens), 1)
+    shard = _clone_workload(
+        full, lambda: decode_attention(t["q"], t["k_cache"], t["v_cache"], kv_indptr=t["lens"], k_block_table=t["k_table"],
+                                       v_block_table=t["v_table"], kv_page_size=ps),
+        t, full.flops * frac, full.kv_bytes * frac, dict(lengths=lens[b0:b1], tokens=sum(lens[b0:b1])))
+    return shard, full, lambda parts: torch.cat(parts)
+
+
+def c5_strong(device, seed: int, rank: int, world: int, **cfg):
+    """Paged speculative decode cut by KV head: a rank holds the pages of its KV heads (one head per GPU at 8 GPUs
+    with 8 KV heads) and the q heads that share them."""
+    from kernels.speculative_decode import speculative_decode_attention
+
+    full = c5_paged_spec_decode(device, seed, **cfg)
+    m = full.meta
+    group = m["q_heads"] // m["kv_heads"]
+    h0, h1 = kv_head_shard(m["kv_heads"], world, rank)
+    ft = full.tensors
+    t = dict(q=ft["q"][:, h0 * group:h1 * group].contiguous(), k_cache=ft["k_cache"][:, h0:h1].contiguous(),
+             v_cache=ft["v_cache"][:, h0:h1].contiguous(), lens=ft["lens"], k_table=ft["k_table"], v_table=ft["v_table"])
+    ps = m["page_size"]
+    frac = (h1 - h0) / m["kv_heads"]
+    shard = _clone_workload(
+        full, lambda: speculative_decode_attention(t["q"], t["k_cache"], t["v_cache"], causal=True, kv_indptr=t["lens"],
+                                                   k_block_table=t["k_table"], v_block_table=t["v_table"], kv_page_size=ps),
+        t, full.flops * frac, full.kv_bytes * frac, dict(q_heads=(h1 - h0) * group, kv_heads=h1 - h0))
+    return shard, full, lambda parts: torch.cat(parts, dim=1)
+
+
+STRONG = {"c2": c2_strong, "c3": c3_strong, "c4": c4_strong, "c5": c5_strong}

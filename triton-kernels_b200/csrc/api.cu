@@ -8,6 +8,7 @@
 #include "paged_append_launch.h"
 #include "softmax_launch.h"
 #include "prefill_launch.h"
+#include "sm100_ptx.cuh"
 
 namespace b200attn {
 
@@ -33,6 +34,26 @@ void set_error(const char* fmt, ...) {
 int cuda_fail(cudaError_t e, const char* what) {
   set_error("%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
   return B200ATTN_E_CUDA;
+}
+
+int ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  struct Entry { const void* kernel; int device; size_t bytes; };
+  static Entry table[256];
+  static int count = 0;
+  static std::mutex mu;
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
+  std::lock_guard<std::mutex> lock(mu);
+  Entry* hit = nullptr;
+  for (int i = 0; i < count; ++i)
+    if (table[i].kernel == kernel && table[i].device == device) { hit = &table[i]; break; }
+  if (hit && hit->bytes >= bytes) return 0;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(MaxDynamicSharedMemorySize)");
+  if (hit) hit->bytes = bytes;
+  else if (count < 256) table[count++] = Entry{kernel, device, bytes};
+  return 0;
 }
 
 static int query_device(int device, b200attn_device_info_t* out) {
@@ -88,6 +109,17 @@ static int check_arch(int device, b200attn_device_info_t* info) {
     return B200ATTN_E_ARCH;
   }
   return 0;
+}
+
+// One warp waits on an mbarrier that nothing will ever complete, with the same bounded wait the attention kernels
+// use (only the try limit differs), records the expiry the way they do and returns.
+__global__ void wait_expiry_selftest_kernel(int* header, uint32_t tries) {
+  __shared__ uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  if (threadIdx.x == 0) { ptx::mbar_init(b, 1); ptx::mbar_fence_init(); }
+  __syncwarp();
+  const bool ok = ptx::mbar_wait_limit(b, 0, tries);
+  if (!__all_sync(0xffffffffu, ok) && threadIdx.x == 0) header[0] = DEV_ERR_WAIT_EXPIRED;
 }
 
 }  // namespace b200attn
@@ -172,6 +204,29 @@ int b200attn_decode_static(const b200attn_decode_args_t* a, void* cuda_stream) {
   return launch_decode_static(*a, info.sm_count, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int b200attn_decode_static_check(int device, void* cuda_stream, int32_t* code) {
+  b200attn_device_info_t info;
+  int rc;
+  if ((rc = check_arch(device, &info))) return rc;
+  DeviceGuard guard;
+  if ((rc = guard.enter(device))) return rc;
+  return check_decode_static(device, static_cast<cudaStream_t>(cuda_stream), code);
+}
+
+int b200attn_selftest_wait_expiry(int device, void* workspace, uint32_t tries, void* cuda_stream) {
+  if (!workspace) { set_error("workspace is null"); return B200ATTN_E_INVALID; }
+  if (tries == 0 || tries > (1u << 20)) { set_error("selftest: tries %u outside 1..2^20", tries); return B200ATTN_E_INVALID; }
+  b200attn_device_info_t info;
+  int rc;
+  if ((rc = check_arch(device, &info))) return rc;
+  DeviceGuard guard;
+  if ((rc = guard.enter(device))) return rc;
+  wait_expiry_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(static_cast<int*>(workspace), tries);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e, "selftest kernel launch");
+  return B200ATTN_OK;
+}
+
 int b200attn_paged_append(const b200attn_paged_append_args_t* a, void* cuda_stream) {
   if (!a) { set_error("args is null"); return B200ATTN_E_INVALID; }
   if (a->batch < 0 || a->total_rows < 0 || a->cache_rows < 0 || a->table_stride < 0 || a->page_size <= 0) { set_error("paged_append: negative extent or bad page size"); return B200ATTN_E_INVALID; }
@@ -211,7 +266,8 @@ int b200attn_check_workspace(void* workspace, void* cuda_stream, int32_t* code) 
   if (e != cudaSuccess) return cuda_fail(e, "reading the workspace error word");
   if (code) *code = word;
   if (word != 0) {
-    e = cudaMemsetAsync(workspace, 0, sizeof(word), st);
+    // the whole header: a kernel that gave up may also have left its scheduling counters behind
+    e = cudaMemsetAsync(workspace, 0, kHeaderBytes, st);
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return cuda_fail(e, "clearing the workspace error word");
     set_error("a kernel reported device error code %d (1 = bounded wait expired, 2 = block-table entry out of range, 3 = planner overflow)", word);

@@ -16,6 +16,9 @@ namespace b200attn {
 // ---------------------------------------------------------------------------
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
+// Raises a kernel's dynamic shared-memory limit to `bytes` on the current device, once per (kernel, device): later
+// calls with the same or a smaller size return without a runtime call.  Returns 0 or a B200ATTN_E_* code.
+int ensure_dynamic_smem(const void* kernel, size_t bytes);
 
 // Device error codes written to the workspace header word 0.
 enum DeviceErr : int {
@@ -52,6 +55,11 @@ template <> struct ElemTraits<__half> {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
   }
+  // both halves of a packed pair multiplied by `a`
+  __device__ static __forceinline__ uint32_t scale2(uint32_t packed, float a) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&packed));
+    return pack2(f.x * a, f.y * a);
+  }
   __device__ static __forceinline__ float to_float(__half x) { return __half2float(x); }
   __device__ static __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
 };
@@ -60,6 +68,10 @@ template <> struct ElemTraits<__nv_bfloat16> {
   __device__ static __forceinline__ uint32_t pack2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
+  }
+  __device__ static __forceinline__ uint32_t scale2(uint32_t packed, float a) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
+    return pack2(f.x * a, f.y * a);
   }
   __device__ static __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
   __device__ static __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }

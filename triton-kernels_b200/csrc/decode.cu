@@ -95,6 +95,13 @@ __device__ __forceinline__ int find_sequence(const int* item_start, int batch, i
   return lo;
 }
 
+// Fills `rows` combined rows with NaN accumulators and (m, l) = (0, 1); every thread of the CTA takes part.
+__device__ __forceinline__ void poison_rows(float* comb_o, float* comb_ml, int rows, int d) {
+  const float nan = __int_as_float(0x7fc00000);
+  for (int i = threadIdx.x; i < rows * d; i += blockDim.x) comb_o[i] = nan;
+  for (int i = threadIdx.x; i < rows; i += blockDim.x) { comb_ml[2 * i] = 0.f; comb_ml[2 * i + 1] = 1.f; }
+}
+
 // ---------------------------------------------------------------------------
 // Emit the CTA's combined (m, l, acc) rows, then merge if this CTA is the last
 // of its (sequence, kv head).  `comb_o` is smem [KS][rows_pad][D] fp32,
@@ -682,7 +689,13 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
     }
   }
   __syncthreads();
-  if (ctrl->abort_flag) return;
+  if (ctrl->abort_flag) {
+    // A bounded wait ran out: the CTA's rows are unknown.  It still emits and draws its ticket, so that the
+    // (sequence, kv head) is merged and its counter returns to zero, but with NaN rows: the failure shows in the
+    // output as well as in the error word.
+    poison_rows(comb_o, comb_ml, KS * rows_pad, D);
+    __syncthreads();
+  }
   emit_and_merge<T, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, KS, rows_pad, &ctrl->ticket);
 }
 
@@ -995,14 +1008,14 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
   }
   __syncthreads();   // every tile consumed (or the CTA gave up): the stage ring is free for the row exchange
-  if (ctrl->abort_flag) {
-    if (warp == kMma) { tc_fence_after(); tmem_dealloc(tmem, kUmmaTmemCols); }
-    return;
-  }
   // O rows (fp32, un-normalised) and (m, l) -> shared memory, then the common emit / ticket merge
   float* comb_o = reinterpret_cast<float*>(smem);
   float* comb_ml = comb_o + static_cast<size_t>(R) * D;
-  if (warp < active_warps) {
+  const bool aborted = ctrl->abort_flag != 0;
+  if (aborted) {
+    // see decode_mma_kernel: emit NaN rows and still take the ticket
+    poison_rows(comb_o, comb_ml, R, D);
+  } else if (warp < active_warps) {
     const int row = tid;
     tc_fence_after();
     const uint32_t tO = tmem + (static_cast<uint32_t>(warp * 32) << 16) + kOCol;
@@ -1116,9 +1129,7 @@ __global__ void __launch_bounds__(128) decode_simt_kernel(const DecodeParams p) 
 
 template <typename K>
 int set_smem(K kernel, size_t bytes) {
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
-  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(decode)");
-  return 0;
+  return ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), bytes);
 }
 
 }  // namespace
@@ -1238,12 +1249,15 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
     }
 #undef B200ATTN_LAUNCH_UMMA
   } else {
+    // at most 16 q rows per KV head reach this kernel (more go to the tcgen05 kernel above): one 16-row tile, four
+    // consumer warps that split every K/V tile by key slice, and the producer warp
     const int nmt = p.n_mtiles;
-    const int ksl = nmt <= 2 ? 4 : (nmt <= 4 ? 2 : 1);
-    const int threads = 32 * (nmt * ksl + 1);   // + the producer warp
+    if (nmt != 1) { set_error("decode: %d row tiles per KV head in the warp-level kernel", nmt); return B200ATTN_E_UNSUPPORTED; }
+    const int ksl = 4;
+    const int threads = 32 * (nmt * ksl + 1);
     // measured on B200 (paged decode, 32/8 heads): 2 stages with Q re-read from shared memory lets three CTAs share an
-    // SM and hides each CTA's start-up and merge behind its neighbours; the larger CTAs keep 3 stages
-    const int stages = threads <= 160 ? 2 : 3;
+    // SM and hides each CTA's start-up and merge behind its neighbours
+    const int stages = 2;
     const size_t stage_bytes = static_cast<size_t>(stages) * 2 * kTileN * D * 2;
     const size_t comb_bytes = sizeof(float) * static_cast<size_t>(ksl) * nmt * 16 * (D + 2);
     const size_t smem = 1024 + std::max(stage_bytes, comb_bytes) + static_cast<size_t>(nmt) * 16 * D * 2 + sizeof(DecodeCtrl);
@@ -1272,13 +1286,7 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
       if (rc) return rc;                                                                                  \
       decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB><<<grid, threads, smem, stream>>>(tk, tv, p);\
     } while (0)
-#define B200ATTN_LAUNCH_DECODE(TYPE, DIM)                                                \
-    do {                                                                                 \
-      if (threads <= 160) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 2, 1, 160, 3);      \
-      else if (threads <= 224) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 3, 2, 224, 2); \
-      else if (ksl == 4) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 3, 1, 288, 1);       \
-      else B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 3, 2, 288, 1);                     \
-    } while (0)
+#define B200ATTN_LAUNCH_DECODE(TYPE, DIM) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 2, 1, 160, 3)
     if (a.dtype == B200ATTN_BF16) {
       if (D == 128) B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 128); else B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 64);
     } else {
@@ -1343,6 +1351,40 @@ int launch_decode_static(const b200attn_decode_args_t& a, int sm_count, cudaStre
   // The planner kernel rewrites the item prefix and zeroes the merge tickets at the start of every
   // call, and partial slots are always written before they are read, so stale contents are harmless.
   return launch_decode(b, sm_count, stream);
+}
+
+
+// Reads and clears the device error word of the built-in array (word 0, where the kernels of
+// launch_decode_static report an expired wait, an out-of-range block-table entry or a planner overflow).
+// One small copy on `stream`, which it synchronises; allocates nothing.  `device` must be current.
+int check_decode_static(int device, cudaStream_t stream, int32_t* code) {
+  if (device < 0 || device >= kScratchMaxDevices) {
+    set_error("decode_static_check: device ordinal %d out of range", device);
+    return B200ATTN_E_INVALID;
+  }
+  void* ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_ptr[device] == nullptr) {
+      void* resolved = nullptr;
+      const cudaError_t e = cudaGetSymbolAddress(&resolved, g_decode_scratch);
+      if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(decode scratch)");
+      g_scratch_ptr[device] = resolved;
+    }
+    ptr = g_scratch_ptr[device];
+  }
+  int32_t word = 0;
+  cudaError_t e = cudaMemcpyAsync(&word, ptr, sizeof(word), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return cuda_fail(e, "reading the built-in array's error word");
+  if (code) *code = word;
+  if (word == 0) return B200ATTN_OK;
+  e = cudaMemsetAsync(ptr, 0, sizeof(word), stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return cuda_fail(e, "clearing the built-in array's error word");
+  set_error("a decode_static kernel reported device error code %d (1 = bounded wait expired, 2 = block-table entry "
+            "out of range, 3 = planner overflow)", word);
+  return B200ATTN_E_DEVICE;
 }
 
 }  // namespace b200attn

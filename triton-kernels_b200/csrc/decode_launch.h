@@ -62,5 +62,6 @@ struct DecodeWsLayout {
 DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count);
 int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream);
 int launch_decode_static(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream);
+int check_decode_static(int device, cudaStream_t stream, int32_t* code);
 
 }  // namespace b200attn

@@ -1022,7 +1022,7 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
     for (int i = 0; i < 3; ++i) {
       const long long n4 = static_cast<long long>(cnt[i] / 4);  // head_dim is a multiple of 4
       if (n4 == 0) continue;
-      const int blocks = static_cast<int>(std::min<long long>((n4 + 255) / 256, 148 * 16));
+      const int blocks = static_cast<int>(std::min<long long>((n4 + 255) / 256, static_cast<long long>(sm_count) * 16));
       cast_f32_to_f16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4*>(src[i]),
                                                          reinterpret_cast<uint2*>(ws + off[i]), n4);
     }
@@ -1090,9 +1090,7 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
 #define B200ATTN_LAUNCH_PREFILL(TYPE, DIM, OUT)                                                          \
   do {                                                                                                   \
     const size_t smem = std::max<size_t>(SmemPlan<DIM>::kTotal + 1024, 120 * 1024);                      \
-    e = cudaFuncSetAttribute(prefill_kernel<TYPE, DIM, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize,\
-                             static_cast<int>(smem));                                                    \
-    if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(prefill)");                          \
+    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(prefill_kernel<TYPE, DIM, OUT>), smem))) return rc; \
     prefill_kernel<TYPE, DIM, OUT><<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);                     \
   } while (0)
   if (f32) {

@@ -579,9 +579,7 @@ __global__ void softmax_stream_kernel(const T* x, T* out, long long rows, long l
 
 template <typename K>
 int set_smem_limit(K kernel, size_t bytes) {
-  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
-  if (e != cudaSuccess) return cuda_fail(e, "cudaFuncSetAttribute(softmax)");
-  return 0;
+  return ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), bytes);
 }
 
 template <typename T, bool LOG, bool VEC>

@@ -32,6 +32,8 @@ EXPORTS = (
     "b200attn_prefill",
     "b200attn_decode",
     "b200attn_decode_static",
+    "b200attn_decode_static_check",
+    "b200attn_selftest_wait_expiry",
     "b200attn_paged_append",
     "b200attn_softmax",
     "b200attn_check_workspace",
@@ -176,6 +178,10 @@ def lib() -> C.CDLL:
         handle.b200attn_decode.restype = C.c_int
         handle.b200attn_decode_static.argtypes = [C.POINTER(DecodeArgs), C.c_void_p]
         handle.b200attn_decode_static.restype = C.c_int
+        handle.b200attn_decode_static_check.argtypes = [C.c_int, C.c_void_p, C.POINTER(C.c_int32)]
+        handle.b200attn_decode_static_check.restype = C.c_int
+        handle.b200attn_selftest_wait_expiry.argtypes = [C.c_int, C.c_void_p, C.c_uint32, C.c_void_p]
+        handle.b200attn_selftest_wait_expiry.restype = C.c_int
         handle.b200attn_paged_append.argtypes = [C.POINTER(PagedAppendArgs), C.c_void_p]
         handle.b200attn_paged_append.restype = C.c_int
         handle.b200attn_softmax.argtypes = [C.POINTER(SoftmaxArgs), C.c_void_p]
@@ -210,6 +216,9 @@ def device_info(device: int) -> DeviceInfo:
 # Word 0 is the device error code; kernels of the same stream reuse the rest.
 # ---------------------------------------------------------------------------
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+# buffers replaced by a larger one: a kernel still running may yet set its error word in one of them, so they are
+# kept (alive and un-reused) until the next error check has read them
+_retired: Dict[Tuple[int, int], list] = {}
 
 
 def workspace(device: torch.device, stream_ptr: int, nbytes: int) -> torch.Tensor:
@@ -218,6 +227,8 @@ def workspace(device: torch.device, stream_ptr: int, nbytes: int) -> torch.Tenso
     if buf is None or buf.numel() < nbytes:
         size = max(int(nbytes), 1 << 20)
         size = (size + 255) & ~255
+        if buf is not None:
+            _retired.setdefault(key, []).append(buf)
         buf = torch.zeros(size, dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
@@ -225,12 +236,18 @@ def workspace(device: torch.device, stream_ptr: int, nbytes: int) -> torch.Tenso
 
 def check_device_errors() -> None:
     """Synchronise and raise if any kernel launched so far recorded a device-side error
-    (bounded wait expired, block-table entry out of range)."""
+    (bounded wait expired, block-table entry out of range, planner overflow)."""
     code = C.c_int32(0)
+    first_error = None
     for (dev, stream_ptr), buf in list(_workspaces.items()):
-        status = lib().b200attn_check_workspace(C.c_void_p(buf.data_ptr()), C.c_void_p(stream_ptr), C.byref(code))
-        check(status, f"device error check on cuda:{dev}")
+        for b in [buf] + _retired.pop((dev, stream_ptr), []):
+            status = lib().b200attn_check_workspace(C.c_void_p(b.data_ptr()), C.c_void_p(stream_ptr), C.byref(code))
+            if status != 0 and first_error is None:
+                first_error = (status, f"device error check on cuda:{dev}", last_error())
+    if first_error is not None:
+        raise RuntimeError(f"{first_error[1]} failed with status {first_error[0]}: {first_error[2]}")
 
 
 def release_workspaces() -> None:
     _workspaces.clear()
+    _retired.clear()
