@@ -247,6 +247,23 @@ def time_end_to_end(wl, steps, warmup, world):
     return intervals, h2d, d2h
 
 
+def pin_rank_to_cores(local_rank, world):
+    """With several ranks on one host, give each its own equal slice of the cores this process may use, so that the
+    ranks' launch and copy-submission threads do not migrate onto each other.  Returns the slice (or None)."""
+    if world <= 1 or not hasattr(os, "sched_getaffinity"):
+        return None
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+        per = len(cores) // world
+        if per < 1:
+            return None
+        mine = cores[local_rank * per:(local_rank + 1) * per]
+        os.sched_setaffinity(0, mine)
+        return [mine[0], mine[-1]]
+    except OSError:
+        return None
+
+
 def pcie_link(index):
     """Current PCIe link of the GPU (read-only query), e.g. {"gen": 5, "width": 16}."""
     try:
@@ -464,6 +481,7 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (sm_100a); there is no CPU fallback")
+    affinity = pin_rank_to_cores(local_rank, world)
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
@@ -504,6 +522,7 @@ def main():
             "gpu_launches": main_res["gpu_launches"],
             "roofline": main_res["roofline"],
             "clocks": clocks,
+            "cpu_affinity_rank0": affinity,
             "workloads": {n: {k: r[k] for k in ("workload", "value", "unit", "ms_per_step", "ms_min", "e2e", "roofline",
                                                 "strong") if k in r}
                           for n, r in results.items()},

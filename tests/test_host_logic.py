@@ -79,7 +79,7 @@ def test_product_path_never_imports_the_oracle():
                 assert "oracle" not in text, os.path.join(base, f)
 
 
-@pytest.mark.parametrize("qh,kvh,m", [(32, 8, 1), (64, 8, 5), (8, 1, 16), (8, 8, 1), (64, 1, 2)])
+@pytest.mark.parametrize("qh,kvh,m", [(32, 8, 1), (64, 8, 5), (8, 1, 16), (8, 8, 1), (64, 1, 2), (32, 1, 5), (48, 1, 16)])
 def test_decode_plan_bounds(qh, kvh, m):
     from utils.launch_config import decode_chunk_tokens, decode_items, decode_plan
 
@@ -93,7 +93,10 @@ def test_decode_plan_bounds(qh, kvh, m):
         assert sum(items) <= plan.max_items
         assert all(i >= 1 for i in items)
         assert all((i - 1) * chunk < max(n, 1) for i, n in zip(items, lens))
-        assert plan.threads <= 288 and plan.mma_tiles * 16 >= (qh // kvh) * m
+        from utils.launch_config import decode_pass_group
+
+        sub = decode_pass_group(qh // kvh, m)
+        assert (qh // kvh) % sub == 0 and sub * m <= 128 and plan.mma_tiles * 16 >= sub * m
 
 
 def test_prefill_grid_and_boxes():
@@ -151,3 +154,25 @@ def test_sequence_balancing_and_shards():
         assert covered == list(range(64))
     assert [kv_head_shard(8, 8, r) for r in range(8)] == [(r, r + 1) for r in range(8)]
     assert kv_head_shard(8, 2, 1) == (4, 8)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("qh,kvh,m,batch,d,fp32", [(32, 8, 1, 64, 128, False), (64, 8, 5, 32, 128, False), (8, 2, 1, 4, 64, True),
+                                                   (32, 1, 5, 3, 128, False), (48, 1, 16, 2, 64, False), (8, 8, 16, 300, 64, False)])
+def test_planning_mirror_agrees_with_the_library(qh, kvh, m, batch, d, fp32):
+    """utils/launch_config.py restates the library's decode planning; the scratch size both derive from it must be
+    the same number, or the mirror (and the CPU tests built on it) no longer describes the library."""
+    import ctypes as C
+
+    from kernels import _native
+    from utils.launch_config import decode_pass_group, decode_plan, decode_workspace_bytes
+
+    info = _native.device_info(torch.cuda.current_device())
+    a = _native.DecodeArgs()
+    a.batch, a.q_heads, a.kv_heads, a.q_len, a.head_dim = batch, qh, kvh, m, d
+    a.dtype = _native.F32 if fp32 else _native.BF16
+    a.layout, a.device = _native.RAGGED, torch.cuda.current_device()
+    want = _native.lib().b200attn_decode_workspace_bytes(C.byref(a))
+    plan = decode_plan(info.sm_count, batch, qh, kvh, m, fp32=fp32)
+    rows = decode_pass_group(qh // kvh, m) * m
+    assert decode_workspace_bytes(plan, batch, kvh, d, rows) == want

@@ -105,3 +105,20 @@ def test_spec_m_too_large_rejected():
     k = torch.zeros((1, 2, 32, 64), device=DEVICE, dtype=torch.float16)
     with pytest.raises(AssertionError):
         speculative_decode_attention(q, k, k)
+
+
+@pytest.mark.parametrize("qh,kvh,m", [(32, 1, 5), (24, 1, 16), (64, 2, 6)], ids=["mqa32x5=160rows", "mqa24x16=384rows", "gqa32x6=192rows"])
+@pytest.mark.parametrize("layout", ["ragged", "paged"])
+def test_spec_more_than_128_rows_per_kv_head(qh, kvh, m, layout):
+    """Any head ratio with M <= 16 is legal in the reference (kernels/speculative_decode.py:262-299); group x M beyond
+    the 128 rows one CTA holds is served by several launches over the same K/V."""
+    dtype = torch.bfloat16
+    rng, gen = make_rngs("spec-wide", qh, kvh, m, layout)
+    lens = [700, 90, 2300]
+    qs = [torch.randn((qh, m, 128), generator=gen).to(dtype).to(DEVICE) for _ in lens]
+    ks = [torch.randn((n + m, kvh, 128), generator=gen).to(dtype).to(DEVICE) for n in lens]
+    vs = [torch.randn((n + m, kvh, 128), generator=gen).to(dtype).to(DEVICE) for n in lens]
+    refs = sdpa_ref.spec_decode_reference(qs, ks, vs, qh, kvh, True)
+    out = run_spec(layout, qs, ks, vs, True, permute=7, pad=-1, poison=float("nan"))
+    for b in range(len(lens)):
+        assert_close_both(out[b], refs[b], dtype, lens[b] + m, f"seq {b}")

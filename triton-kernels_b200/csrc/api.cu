@@ -173,7 +173,6 @@ int b200attn_decode(const b200attn_decode_args_t* a, void* cuda_stream) {
   if (!a->q || !a->k || !a->v || !a->out) { set_error("decode: null tensor pointer"); return B200ATTN_E_INVALID; }
   if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out)) { set_error("decode: tensors must be 16-byte aligned"); return B200ATTN_E_INVALID; }
   if (a->q_len < 1 || a->q_len > 16) { set_error("decode: q_len %d outside 1..16", a->q_len); return B200ATTN_E_INVALID; }
-  if ((a->q_heads / a->kv_heads) * a->q_len > 128) { set_error("decode: group*q_len = %d rows exceed 128", (a->q_heads / a->kv_heads) * a->q_len); return B200ATTN_E_UNSUPPORTED; }
   if (a->layout == B200ATTN_RAGGED && (!a->kv_indptr || a->total_kv < 0)) { set_error("decode: ragged layout needs kv_indptr and total_kv"); return B200ATTN_E_INVALID; }
   if (a->layout == B200ATTN_PAGED && (!a->kv_indptr || !a->k_table || !a->v_table || a->page_size <= 0 || a->table_stride < 0)) { set_error("decode: paged layout needs lengths, both block tables and a page size"); return B200ATTN_E_INVALID; }
   if (a->layout == B200ATTN_DENSE && a->max_kv < 0) { set_error("decode: negative extent"); return B200ATTN_E_INVALID; }
@@ -192,7 +191,6 @@ int b200attn_decode_static(const b200attn_decode_args_t* a, void* cuda_stream) {
   if (!a->q || !a->k || !a->v || !a->out) { set_error("decode_static: null tensor pointer"); return B200ATTN_E_INVALID; }
   if (!aligned16(a->q) || !aligned16(a->k) || !aligned16(a->v) || !aligned16(a->out)) { set_error("decode_static: tensors must be 16-byte aligned"); return B200ATTN_E_INVALID; }
   if (a->q_len < 1 || a->q_len > 16) { set_error("decode_static: q_len %d outside 1..16", a->q_len); return B200ATTN_E_INVALID; }
-  if ((a->q_heads / a->kv_heads) * a->q_len > 128) { set_error("decode_static: group*q_len exceeds 128 rows"); return B200ATTN_E_UNSUPPORTED; }
   if (a->layout == B200ATTN_RAGGED && (!a->kv_indptr || a->total_kv < 0)) { set_error("decode_static: ragged layout needs kv_indptr and total_kv"); return B200ATTN_E_INVALID; }
   if (a->layout == B200ATTN_PAGED && (!a->kv_indptr || !a->k_table || !a->v_table || a->page_size <= 0 || a->table_stride < 0)) { set_error("decode_static: paged layout needs lengths, both block tables and a page size"); return B200ATTN_E_INVALID; }
   if (a->layout == B200ATTN_DENSE && a->max_kv < 0) { set_error("decode_static: negative extent"); return B200ATTN_E_INVALID; }

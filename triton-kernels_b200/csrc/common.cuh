@@ -55,11 +55,6 @@ template <> struct ElemTraits<__half> {
     __half2 h = __floats2half2_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
   }
-  // both halves of a packed pair multiplied by `a`
-  __device__ static __forceinline__ uint32_t scale2(uint32_t packed, float a) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&packed));
-    return pack2(f.x * a, f.y * a);
-  }
   __device__ static __forceinline__ float to_float(__half x) { return __half2float(x); }
   __device__ static __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
 };
@@ -68,10 +63,6 @@ template <> struct ElemTraits<__nv_bfloat16> {
   __device__ static __forceinline__ uint32_t pack2(float a, float b) {
     __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<uint32_t*>(&h);
-  }
-  __device__ static __forceinline__ uint32_t scale2(uint32_t packed, float a) {
-    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&packed));
-    return pack2(f.x * a, f.y * a);
   }
   __device__ static __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
   __device__ static __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }

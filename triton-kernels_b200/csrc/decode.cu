@@ -114,7 +114,7 @@ __device__ __forceinline__ void emit_and_merge(const DecodeParams& p, int b, int
   constexpr int D4 = D / 4;
   const int R = p.rows;
   T* out = static_cast<T*>(p.out) +
-           ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.group) * p.q_len) * D;
+           ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
   const long long slot = (static_cast<long long>(item0) + c) * p.kv_heads + h;
   for (int idx = threadIdx.x; idx < R * D4; idx += blockDim.x) {
     const int r = idx / D4, d4 = idx - r * D4;
@@ -433,7 +433,7 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
   // Q rows (group x drafts, contiguous in memory) -> smem, zero padded to 16-row tiles
   {
     const T* qg = static_cast<const T*>(p.q) +
-                  ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.group) * p.q_len) * D;
+                  ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
     for (int idx = tid; idx < rows_pad * CPR; idx += blockDim.x) {
       const int row = idx / CPR, ch = idx % CPR;
       uint4 val = make_uint4(0u, 0u, 0u, 0u);
@@ -921,7 +921,7 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     // Q row -> TMEM as the packed 16-bit A operand (rows past R are zero)
     {
       const T* qg = static_cast<const T*>(p.q) +
-                    ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.group) * p.q_len) * D;
+                    ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
 #pragma unroll
       for (int cc = 0; cc < kQCols / 32; ++cc) {
         uint32_t qv[32];
@@ -1077,7 +1077,7 @@ __global__ void __launch_bounds__(128) decode_simt_kernel(const DecodeParams p) 
   const float* kg = static_cast<const float*>(p.k);
   const float* vg = static_cast<const float*>(p.v);
   const float* qg = static_cast<const float*>(p.q) +
-                    ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.group) * p.q_len) * D;
+                    ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
   const float sl2 = p.scale_log2;
 
   for (int r = warp; r < R; r += nwarps) {
@@ -1137,9 +1137,19 @@ int set_smem(K kernel, size_t bytes) {
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
+// q heads of one KV head that one launch serves.  A CTA holds at most 128 q rows (group x draft tokens) per KV head;
+// a larger group is cut into the largest equal sub-groups that fit, one launch each over the same K/V (the reference
+// takes any head ratio: kernels/speculative_decode.py:262-299).
+int decode_pass_group(int group, int q_len) {
+  if (q_len < 1) q_len = 1;
+  int g = group;
+  while (g > 1 && (g * q_len > 128 || group % g != 0)) --g;
+  return g < 1 ? 1 : g;
+}
+
 DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count) {
   DecodeWsLayout w;
-  const int group = a.kv_heads > 0 ? a.q_heads / a.kv_heads : 1;
+  const int group = decode_pass_group(a.kv_heads > 0 ? a.q_heads / a.kv_heads : 1, a.q_len);
   const int rows = group * a.q_len;
   // Six (item, kv head) CTAs per SM: two or three waves of the tensor-core kernels (3 or 2 resident CTAs per SM).
   // Fewer, longer CTAs amortise start-up and merge; the planner keeps the item count at or below this, so the grid
@@ -1168,12 +1178,30 @@ DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count) {
   return w;
 }
 
+namespace {
+int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream, const DecodeWsLayout& w,
+                       int pass_group, int head0);
+}  // namespace
+
 int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream) {
   const DecodeWsLayout w = decode_ws_layout(a, sm_count);
   if (a.workspace == nullptr || a.workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(a.workspace) & 255)) {
     set_error("decode: workspace needs %zu bytes, 256-byte aligned (got %zu)", w.total, a.workspace_bytes);
     return B200ATTN_E_WORKSPACE;
   }
+  const int group = a.q_heads / a.kv_heads;
+  const int pass_group = decode_pass_group(group, a.q_len);
+  // one launch per sub-group of q heads; they run back to back on the stream and share the workspace
+  for (int head0 = 0; head0 < group; head0 += pass_group) {
+    const int rc = launch_decode_pass(a, sm_count, stream, w, pass_group, head0);
+    if (rc) return rc;
+  }
+  return B200ATTN_OK;
+}
+
+namespace {
+int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream, const DecodeWsLayout& w,
+                       int pass_group, int head0) {
   DecodeParams p;
   p.q = a.q; p.k = a.k; p.v = a.v; p.out = a.out;
   p.kv_indptr = a.kv_indptr; p.k_table = a.k_table; p.v_table = a.v_table;
@@ -1187,7 +1215,8 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
   p.total_kv = a.total_kv; p.table_stride = a.table_stride;
   p.layout = a.layout; p.indptr_is_i64 = a.indptr_is_i64;
   p.batch = a.batch; p.q_heads = a.q_heads; p.kv_heads = a.kv_heads;
-  p.group = a.q_heads / a.kv_heads; p.q_len = a.q_len; p.rows = p.group * a.q_len;
+  p.head_stride = a.q_heads / a.kv_heads; p.head0 = head0;
+  p.group = pass_group; p.q_len = a.q_len; p.rows = p.group * a.q_len;
   p.n_mtiles = (p.rows + 15) / 16;
   p.max_kv = a.max_kv; p.page_size = a.layout == B200ATTN_PAGED ? a.page_size : 1;
   p.page_shift = -1;
@@ -1299,6 +1328,7 @@ int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t st
   if (e != cudaSuccess) return cuda_fail(e, "decode kernel launch");
   return B200ATTN_OK;
 }
+}  // namespace
 
 // ---------------------------------------------------------------------------
 // Decode without any caller-provided or allocated scratch memory.

@@ -30,7 +30,9 @@ struct DecodeParams {
   int batch;
   int q_heads;
   int kv_heads;
-  int group;         // q heads per kv head
+  int group;         // q heads per kv head served by this launch
+  int head_stride;   // q heads per kv head in the tensors
+  int head0;         // first q head (inside each kv head's group) this launch serves
   int q_len;         // M
   int rows;          // group * M: q rows that share one kv head
   int n_mtiles;      // ceil(rows / 16)
@@ -59,6 +61,7 @@ struct DecodeWsLayout {
   int max_items;
 };
 
+int decode_pass_group(int group, int q_len);
 DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count);
 int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream);
 int launch_decode_static(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream);

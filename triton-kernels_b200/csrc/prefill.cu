@@ -60,17 +60,6 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
 
 
-// Development aid (compiled out unless B200ATTN_TRACE is defined): CTA (0,0,0) stamps clock64 into the
-// workspace behind the header, one slot per (role, iteration, event).
-#ifdef B200ATTN_TRACE
-#define TRACE_AT(idx) do { if (trace_on) p.header[64 + (idx)] = static_cast<int>(clock64() - trace_t0); } while (0)
-// per-CTA summary (lane 0 of the MMA warp): global timer stamps in ns and counters
-#define TRACE_CTA(slot, val) do { if (lane == 0) p.header[64 + 8192 + blockIdx.x * 8 + (slot)] = static_cast<int>(val); } while (0)
-__device__ __forceinline__ unsigned long long trace_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-#else
-#define TRACE_AT(idx) do { } while (0)
-#define TRACE_CTA(slot, val) do { } while (0)
-#endif
 
 // Everything one work item needs; decoded once by the scheduler warp.  An item is two 128-row query tiles
 // ("slots") that share one KV head: with an even GQA group the same 128 rows of two neighbouring q heads (equal
@@ -260,10 +249,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   Control* ctrl = reinterpret_cast<Control*>(smem + Plan::kCtrlOff);
   const uint32_t smem_base = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-#ifdef B200ATTN_TRACE
-  const bool trace_on = blockIdx.x == 0 && lane == 0;
-  const long long trace_t0 = clock64();
-#endif
 
   if (tid == 0) {
     mbar_init(smem_u32(&ctrl->q_full), 1);
@@ -354,7 +339,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mbar_arrive(smem_u32(&ctrl->q_full));   // keeps one q_full phase per item
         }
       }
-      TRACE_AT(3840 + (k & 31) * 2 + 0);
       // K/V tiles travel in pairs that share one barrier: pair 0 of an item is K_0 alone, pair j + 1 is {V_j, K_j+1}
       // (the last one V alone).  Stage = pair % 2; its V buffer is ring buffer 2 * stage, its K buffer 2 * stage + 1.
       pair_lo = pair_e;
@@ -421,7 +405,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
           }
         }
-        TRACE_AT(3072 + (pair_e & 255));
       }
     }
     if (!ok) {
@@ -479,35 +462,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mma_commit_lead(smem_u32(&ctrl->o_done[s]), lead);
     };
 
-#ifdef B200ATTN_TRACE
-    TRACE_CTA(0, trace_gtime() & 0x7fffffff);
-    int trace_items = 0, trace_iters = 0;
-#endif
     for (int k = 0; ok; ++k) {
-      TRACE_AT(3328 + (k & 31) * 8 + 0);
       ok = warp_wait(smem_u32(&ctrl->sched_full[k & 1]), (k >> 1) & 1);
       if (!ok || *abort_flag) { ok = false; break; }
       const int item = ctrl->sched_item[k & 1];
       if (item < 0) break;
       const ItemWork& wr = ctrl->sched_work[k & 1];
       const int nkv0 = wr.nkv[0], nkv1 = wr.nkv[1], nkv_max = wr.nkv_max, len_k = wr.len_k;
-      TRACE_AT(3328 + (k & 31) * 8 + 1);
       ok = warp_wait(smem_u32(&ctrl->q_full), k & 1);
       if (!ok) break;
-      TRACE_AT(3328 + (k & 31) * 8 + 2);
       if (nkv_max > 0) {
         ok = pair_full_wait(pair_base);
         if (!ok) break;
-        TRACE_AT(3328 + (k & 31) * 8 + 3);
         tc_fence_after();
         // (slots whose first score tile was already issued while the previous item finished are skipped)
         if (nkv0 > 0 && !pre_issued0) issue_s(0, k_desc_of(pair_base));
         if (nkv1 > 0 && !pre_issued1) issue_s(1, k_desc_of(pair_base));
-        TRACE_AT(3328 + (k & 31) * 8 + 4);
-#ifdef B200ATTN_TRACE
-        if (k == 0) TRACE_CTA(1, trace_gtime() & 0x7fffffff);
-        ++trace_items; trace_iters += nkv_max;
-#endif
         mma_commit_lead(smem_u32(&ctrl->kv_empty[pair_base % kStages]), lead);
         if (nkv_max == 1) mma_commit_lead(smem_u32(&ctrl->q_empty), lead);
       } else {
@@ -574,17 +544,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // (the softmax warps do that just before they hand over this tile's P)
             if (!warp_wait(smem_u32(&ctrl->o_free[s]), (k - 1) & 1)) return false;
           }
-          TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 0);
           if (!warp_wait(smem_u32(&ctrl->p_ready[s]), tiles_done & 1)) return false;
-          TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 1);
           tc_fence_after();
           issue_pv(s, vb, j == 0);
-          TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 2);
           if (s_next) {
             issue_s(s, kb);
             if (last_iter) pre_issued = true;
           }
-          TRACE_AT(2048 + ((tiles_done0 + tiles_done1) & 127) * 4 + 3);
           ++tiles_done;
           return true;
         };
@@ -609,11 +575,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));
       __syncwarp();
     }
-#ifdef B200ATTN_TRACE
-    TRACE_CTA(2, trace_gtime() & 0x7fffffff);
-    TRACE_CTA(3, trace_items);
-    TRACE_CTA(4, trace_iters);
-#endif
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
   } else if (warp < kSoftmaxWarps) {
     // =========================== softmax warps ===========================
@@ -631,7 +592,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t tS = tmem + s * kBN + lane_off;
     const uint32_t tO = tmem + 2 * kBN + s * D + lane_off;
     const float sl2 = p.scale_log2;
-    const bool tracer = (warp & 7) == 0;
     int tile_cnt = 0;     // score tiles of this slot consumed so far (barrier phases run across items)
     bool ok = true;
     // The epilogue of an item is finished lazily: O is read out of tensor memory at the end of the first score
@@ -793,11 +753,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       float m_a = -INFINITY, m_b = -INFINITY;   // exponent references currently baked into O and l
       float l_a = 0.f, l_b = 0.f;               // partial row sums over this thread's columns
       for (int j = 0; j < n; ++j, ++tile_cnt) {
-        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 0);
         ok = warp_wait(smem_u32(&ctrl->s_full[s]), tile_cnt & 1);
         if (!ok || *abort_flag) { ok = false; break; }
         tc_fence_after();
-        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 1);
         // masking is needed only on the tile that holds the sequence end or the causal diagonal; `lim` is the last
         // visible column of the tile for the row
         int lim_a = len_k - 1 - j * kBN, lim_b = lim_a;
@@ -830,7 +788,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           mx_a = quad_max(a0);
           mx_b = quad_max(b0);
         }
-        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 2);
         const float mn_a = fmaxf(m_a, mx_a * sl2), mn_b = fmaxf(m_b, mx_b * sl2);
         const bool need_a = (mn_a - m_a) > kRescaleThreshold;   // false for NaN / (-inf)-(-inf)
         const bool need_b = (mn_b - m_b) > kRescaleThreshold;
@@ -859,7 +816,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tmem_st_16x256b_x8(tO + c * 64, ov);
           }
         }
-        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 4);
         const float neg_a = (m_a == -INFINITY) ? 0.f : -m_a, neg_b = (m_b == -INFINITY) ? 0.f : -m_b;
         uint64_t rs_a = pack_f2(0.f, 0.f), rs_b = pack_f2(0.f, 0.f);
         const uint64_t sl2_2 = pack_f2(sl2, sl2), nega_2 = pack_f2(neg_a, neg_a), negb_2 = pack_f2(neg_b, neg_b);
@@ -925,7 +881,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           unpack_f2(rs_b, r0, r1);
           l_b += r0 + r1;
         }
-        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 5);
         tmem_wait_st();
         if (pend) {
           // first tile of an item: the previous item's O must leave tensor memory before this tile's PV
@@ -935,11 +890,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_fence_before();
           mbar_arrive(smem_u32(&ctrl->p_ready[s]));
         }
-        if (tracer) TRACE_AT(s * 1024 + (tile_cnt & 127) * 8 + 6);
       }
       if (!ok) break;
       // ---------------- the item's epilogue becomes pending ----------------
-      if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 0);
       const int len_q = w.len_q;
       const bool slot_live = w.valid && m0s < len_q;
       const long long qrow0 = w.q_row0[s];
@@ -958,7 +911,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         pend_off = (qrow0 + m0s + rowA) * D;
       }
       __syncwarp();
-      if (tracer) TRACE_AT(3584 + (s * 32 + (k & 31)) * 4 + 2);
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->sched_empty[k & 1]));
     }
     if (ok && pend) ok = flush(false);

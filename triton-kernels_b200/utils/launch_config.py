@@ -1,11 +1,11 @@
-"""Launch planning for the attention path.
+"""Launch planning for the attention path, restated in Python.
 
-Pure-Python mirrors of the planning rules compiled into ``libb200attn.so``
-(csrc/decode.cu ``decode_ws_layout`` / ``decode_plan_kernel`` and the prefill
-grid in csrc/prefill.cu).  They replace the reference's split heuristics
-(kernels/attention.py:836-841, kernels/decode.py:271-278,
-kernels/speculative_decode.py:301-309) and let the planning be unit-tested
-without a GPU.
+These are mirrors of the planning rules compiled into ``libb200attn.so`` (csrc/decode.cu ``decode_pass_group`` /
+``decode_ws_layout`` / ``decode_plan_kernel`` and the prefill grid in csrc/prefill.cu), which replace the
+reference's split heuristics (kernels/attention.py:836-841, kernels/decode.py:271-278,
+kernels/speculative_decode.py:301-309).  Nothing on the product path calls them: the library plans for itself.
+They exist so that the rules can be unit-tested without a GPU, and ``decode_workspace_bytes`` is compared with the
+library's own ``b200attn_decode_workspace_bytes`` in the GPU tests so that the two cannot drift apart unnoticed.
 """
 from __future__ import annotations
 
@@ -28,8 +28,32 @@ class DecodePlan:
     threads: int
 
 
+def decode_pass_group(group: int, q_len: int) -> int:
+    """q heads of one KV head that one launch serves: at most 128 q rows (group x draft tokens) per CTA; a larger
+    group is cut into the largest equal sub-groups that fit."""
+    q_len = max(1, q_len)
+    g = group
+    while g > 1 and (g * q_len > 128 or group % g != 0):
+        g -= 1
+    return max(g, 1)
+
+
+def decode_workspace_bytes(plan: "DecodePlan", batch: int, kv_heads: int, head_dim: int, rows: int) -> int:
+    """Bytes of scratch a decode call needs: header, item prefix, merge tickets, item records, (m, l) and O partials,
+    each rounded up to 256 bytes (csrc/decode.cu decode_ws_layout)."""
+    up = lambda x: (x + 255) & ~255
+    off = 256
+    off = up(off + 4 * (batch + 1))
+    off = up(off + 4 * batch * kv_heads)
+    off = up(off + 32 * plan.max_items)
+    slots = plan.max_items * kv_heads
+    off = up(off + 4 * slots * rows * 2)
+    off = up(off + 4 * slots * rows * head_dim)
+    return off
+
+
 def decode_plan(sm_count: int, batch: int, q_heads: int, kv_heads: int, q_len: int, fp32: bool = False) -> DecodePlan:
-    group = q_heads // kv_heads
+    group = decode_pass_group(q_heads // kv_heads, q_len)
     rows = group * q_len
     # six (item, kv head) CTAs per SM for the tensor-core kernels (a whole number of waves at 2 or 3 resident CTAs
     # per SM), eight for the fp32 kernel

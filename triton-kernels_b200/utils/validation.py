@@ -191,5 +191,4 @@ def validate_decode(q, k, v, kv_indptr, k_block_table, v_block_table, kv_page_si
     if spec:
         assert m <= MAX_DRAFT_TOKENS, "Speculative decode is intended for small draft lengths (M <= 16)."
         assert m >= 1
-    assert (q_heads // prob.kv_heads) * m <= 128, "group size x draft tokens must not exceed 128 rows"
     return prob
