@@ -23,6 +23,7 @@
 #include <algorithm>
 #include <mutex>
 #include <type_traits>
+#include <utility>
 
 #include "common.cuh"
 #include "decode_launch.h"
@@ -37,6 +38,7 @@ constexpr int kTileN = 64;
 constexpr int kMaxStages = 4;
 constexpr int kPlanThreads = 1024;
 constexpr int kPlanBuckets = 32;    // size classes of the execution order (longest items first)
+constexpr int kPlanLenCache = 4096; // sequences whose lengths the planner keeps in shared memory
 
 struct SeqInfo {
   long long start;  // ragged: first row of the sequence
@@ -209,11 +211,22 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
   __shared__ int s_cand_chunk[kPlanThreads / 32], s_cand_items[kPlanThreads / 32];
   __shared__ int s_hist[kPlanBuckets];     // items per size class, then the class's first execution slot
   __shared__ int s_cursor[kPlanBuckets];
+  __shared__ int s_len[kPlanLenCache];      // sequence lengths, read from global memory once
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // The attention kernel behind this one is launched with programmatic stream serialisation: its CTAs may be
+  // scheduled now and wait (griddepcontrol.wait) until this grid has completed, which takes its launch latency off
+  // the critical path.
+  ptx::grid_dep_launch_dependents();
   if (tid < kPlanBuckets) { s_hist[tid] = 0; s_cursor[tid] = 0; }
+  const bool cached = p.batch <= kPlanLenCache;
+  auto len_of = [&](int b) -> int { return cached ? s_len[b] : seq_info(p, b).len; };
 
   long long tot = 0;
-  for (int b = tid; b < p.batch; b += kPlanThreads) tot += seq_info(p, b).len;
+  for (int b = tid; b < p.batch; b += kPlanThreads) {
+    const int len = seq_info(p, b).len;
+    if (cached) s_len[b] = len;
+    tot += len;
+  }
   for (int o = 16; o > 0; o >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, o);
   if (lane == 0) s_tot[warp] = tot;
   __syncthreads();
@@ -232,7 +245,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     const int ck = static_cast<int>(cand);
     long long n = 0;
     for (int b = lane; b < p.batch; b += 32) {
-      const int len = seq_info(p, b).len;
+      const int len = len_of(b);
       const int v = (len + ck - 1) / ck;
       n += v < 1 ? 1 : v;
     }
@@ -256,7 +269,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     const int b = base + tid;
     int v = 0;
     if (b < p.batch) {
-      const int len = seq_info(p, b).len;
+      const int len = len_of(b);
       v = (len + chunk - 1) / chunk;
       if (v < 1) v = 1;
     }
@@ -294,11 +307,11 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
   };
   // (a sequence's first n - 1 items have the same size, its last one takes the remainder: two size classes)
   for (int b = tid; b < p.batch; b += kPlanThreads) {
-    const SeqInfo si = seq_info(p, b);
+    const int len = len_of(b);
     const int first = b == 0 ? 0 : p.item_start[b];
     const int n = p.item_start[b + 1] - first;
-    const int per = seq_chunk(si.len, n, chunk, p.equal_split);
-    const int rem = max(0, si.len - (n - 1) * per);
+    const int per = seq_chunk(len, n, chunk, p.equal_split);
+    const int rem = max(0, len - (n - 1) * per);
     if (n > 1) atomicAdd(&s_hist[size_class(per)], n - 1);
     atomicAdd(&s_hist[size_class(rem)], 1);
   }
@@ -388,6 +401,7 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
   constexpr int STAGE_BYTES = 2 * TILE_BYTES;
   constexpr int KSTEPS = D / 16;
 
+  ptx::grid_dep_wait();      // the planner's records are complete and visible from here on
   const int n_items = p.header[2];
   // heads vary fastest across CTAs: the CTAs that run side by side walk the same pages and read
   // neighbouring head slices of each token row, which keeps DRAM rows open
@@ -741,6 +755,7 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
   constexpr int kOCol = kQCols + kTileN;      // O (D fp32 columns)
   static_assert(kOCol + D <= kUmmaTmemCols, "TMEM budget");
 
+  ptx::grid_dep_wait();      // the planner's records are complete and visible from here on
   const int n_items = p.header[2];
   const int item = blockIdx.x / p.kv_heads;
   if (item >= n_items) return;
@@ -1052,6 +1067,7 @@ __global__ void __launch_bounds__(128) decode_simt_kernel(const DecodeParams p) 
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_ticket;
   constexpr int VEC = D / 32;  // floats per lane
+  ptx::grid_dep_wait();      // the planner's records are complete and visible from here on
   const int n_items = p.header[2];
   // heads vary fastest across CTAs: the CTAs that run side by side walk the same pages and read
   // neighbouring head slices of each token row, which keeps DRAM rows open
@@ -1125,6 +1141,24 @@ __global__ void __launch_bounds__(128) decode_simt_kernel(const DecodeParams p) 
   }
   __syncthreads();
   emit_and_merge<float, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, 1, R, &s_ticket);
+}
+
+// Launches `kernel` so that it may be scheduled while the planner before it in the stream is still running; the
+// kernel itself waits (grid_dep_wait) before it reads what the planner wrote.
+template <typename... Params, typename... Args>
+cudaError_t launch_after_planner(void (*kernel)(Params...), dim3 grid, int threads, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(static_cast<unsigned>(threads), 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 template <typename K>
@@ -1243,8 +1277,8 @@ int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream
   if (a.dtype == B200ATTN_F32) {
     const size_t smem = sizeof(float) * static_cast<size_t>(p.rows) * (D + 2);
     int rc = 0;
-    if (D == 128) { rc = set_smem(decode_simt_kernel<128>, smem); if (rc) return rc; decode_simt_kernel<128><<<grid, 128, smem, stream>>>(p); }
-    else          { rc = set_smem(decode_simt_kernel<64>, smem);  if (rc) return rc; decode_simt_kernel<64><<<grid, 128, smem, stream>>>(p); }
+    if (D == 128) { rc = set_smem(decode_simt_kernel<128>, smem); if (rc) return rc; launch_after_planner(decode_simt_kernel<128>, grid, 128, smem, stream, p); }
+    else          { rc = set_smem(decode_simt_kernel<64>, smem);  if (rc) return rc; launch_after_planner(decode_simt_kernel<64>, grid, 128, smem, stream, p); }
   } else if (p.rows > 16) {
     // many q rows per KV head: one 128-row tcgen05 tile with Q and P in tensor memory
     CUtensorMap tk, tv;
@@ -1269,7 +1303,7 @@ int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream
     do {                                                                 \
       rc = set_smem(decode_umma_kernel<TYPE, DIM>, smem);                \
       if (rc) return rc;                                                 \
-      decode_umma_kernel<TYPE, DIM><<<grid, 192, smem, stream>>>(tk, tv, p); \
+      launch_after_planner(decode_umma_kernel<TYPE, DIM>, grid, 192, smem, stream, tk, tv, p); \
     } while (0)
     if (a.dtype == B200ATTN_BF16) {
       if (D == 128) B200ATTN_LAUNCH_UMMA(__nv_bfloat16, 128); else B200ATTN_LAUNCH_UMMA(__nv_bfloat16, 64);
@@ -1313,7 +1347,7 @@ int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream
     do {                                                                                                  \
       rc = set_smem(decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB>, smem);                       \
       if (rc) return rc;                                                                                  \
-      decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB><<<grid, threads, smem, stream>>>(tk, tv, p);\
+      launch_after_planner(decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB>, grid, threads, smem, stream, tk, tv, p);\
     } while (0)
 #define B200ATTN_LAUNCH_DECODE(TYPE, DIM) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 2, 1, 160, 3)
     if (a.dtype == B200ATTN_BF16) {

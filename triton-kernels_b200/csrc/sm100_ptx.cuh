@@ -82,6 +82,13 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
                : "memory");
 }
 
+// ------------------------------ programmatic dependent launch ----------------
+// A grid launched with programmatic stream serialisation may start while the grid before it in the stream is still
+// running; grid_dep_wait blocks until that grid has completed and its writes are visible (a no-op in a grid launched
+// the ordinary way).  grid_dep_launch_dependents, in the earlier grid, lets the later one be scheduled from then on.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 // ------------------------------ proxies / fences ----------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
