@@ -93,7 +93,13 @@ def flash_attention_v1(
     kv_page_size: int | None = None,
 ) -> torch.Tensor:
     """Same signature and semantics as the reference's single-pass variant
-    (kernels/attention.py:249-260); served by the same kernel as ``flash_attention_v2``."""
+    (kernels/attention.py:249-260); served by the same kernel as ``flash_attention_v2``.
+
+    One difference for fp32 inputs: the reference's v1 kernel keeps q, k and v in fp32 and multiplies in TF32
+    (kernels/attention.py:177-240), its v2 kernel rounds them to fp16 (:547-633).  This build follows v2 for both
+    names, so fp32 inputs are rounded to fp16 before the tensor cores: values beyond +-65504 become infinite here
+    where the reference's v1 would keep them finite, and the result is accurate to the 16-bit class (4e-3), not to
+    TF32."""
     return flash_attention_v2(
         q, k, v, is_causal=is_causal, q_indptr=q_indptr, kv_indptr=kv_indptr,
         k_block_table=k_block_table, v_block_table=v_block_table, kv_page_size=kv_page_size,
