@@ -212,6 +212,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
   __shared__ int s_hist[kPlanBuckets];     // items per size class, then the class's first execution slot
   __shared__ int s_cursor[kPlanBuckets];
   __shared__ int s_len[kPlanLenCache];      // sequence lengths, read from global memory once
+  __shared__ int s_first[kPlanLenCache + 1]; // item prefix per sequence (a copy of item_start that needs no round trip)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   // The attention kernel behind this one is launched with programmatic stream serialisation: its CTAs may be
   // scheduled now and wait (griddepcontrol.wait) until this grid has completed, which takes its launch latency off
@@ -291,7 +292,10 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     __syncthreads();
     const int carry = s_carry;
     const int before = warp > 0 ? s_warp[warp - 1] : 0;
-    if (b < p.batch) p.item_start[b + 1] = carry + before + incl;
+    if (b < p.batch) {
+      p.item_start[b + 1] = carry + before + incl;
+      if (cached) s_first[b + 1] = carry + before + incl;
+    }
     __syncthreads();
     if (tid == 0) s_carry = carry + s_warp[31];
     __syncthreads();
@@ -308,8 +312,8 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
   // (a sequence's first n - 1 items have the same size, its last one takes the remainder: two size classes)
   for (int b = tid; b < p.batch; b += kPlanThreads) {
     const int len = len_of(b);
-    const int first = b == 0 ? 0 : p.item_start[b];
-    const int n = p.item_start[b + 1] - first;
+    const int first = b == 0 ? 0 : (cached ? s_first[b] : p.item_start[b]);
+    const int n = (cached ? s_first[b + 1] : p.item_start[b + 1]) - first;
     const int per = seq_chunk(len, n, chunk, p.equal_split);
     const int rem = max(0, len - (n - 1) * per);
     if (n > 1) atomicAdd(&s_hist[size_class(per)], n - 1);
@@ -323,8 +327,8 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
   __syncthreads();
   for (int b = tid; b < p.batch; b += kPlanThreads) {
     const SeqInfo si = seq_info(p, b);
-    const int first = b == 0 ? 0 : p.item_start[b];
-    const int n = p.item_start[b + 1] - first;
+    const int first = b == 0 ? 0 : (cached ? s_first[b] : p.item_start[b]);
+    const int n = (cached ? s_first[b + 1] : p.item_start[b + 1]) - first;
     const int per = seq_chunk(si.len, n, chunk, p.equal_split);
     const int rem = max(0, si.len - (n - 1) * per);
     const int4 rec1 = make_int4(si.len, per, static_cast<int>(si.start & 0xffffffffll), static_cast<int>(si.start >> 32));

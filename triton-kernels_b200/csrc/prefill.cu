@@ -250,32 +250,40 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t smem_base = smem_u32(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  if (tid == 0) {
-    mbar_init(smem_u32(&ctrl->q_full), 1);
-    mbar_init(smem_u32(&ctrl->q_empty), 1);
-    for (int i = 0; i < kStages; ++i) { mbar_init(smem_u32(&ctrl->kv_full[i]), 1); mbar_init(smem_u32(&ctrl->kv_empty[i]), 1); }
-    for (int s = 0; s < kSlots; ++s) {
-      mbar_init(smem_u32(&ctrl->s_full[s]), 1);
-      mbar_init(smem_u32(&ctrl->p_ready[s]), 2 * kBM);
-      mbar_init(smem_u32(&ctrl->o_done[s]), 1);
-      mbar_init(smem_u32(&ctrl->o_free[s]), 8);          // one arrival per softmax warp of the slot
+  // The scheduler / producer warp sets the barriers up itself and goes straight on to draw and decode its first item
+  // and to issue the first copies: it only arrives at the start-up barrier, it does not wait there for the TMEM
+  // allocation of the MMA warp (it never touches tensor memory).  Everybody else waits until both are done.
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      mbar_init(smem_u32(&ctrl->q_full), 1);
+      mbar_init(smem_u32(&ctrl->q_empty), 1);
+      for (int i = 0; i < kStages; ++i) { mbar_init(smem_u32(&ctrl->kv_full[i]), 1); mbar_init(smem_u32(&ctrl->kv_empty[i]), 1); }
+      for (int s = 0; s < kSlots; ++s) {
+        mbar_init(smem_u32(&ctrl->s_full[s]), 1);
+        mbar_init(smem_u32(&ctrl->p_ready[s]), 2 * kBM);
+        mbar_init(smem_u32(&ctrl->o_done[s]), 1);
+        mbar_init(smem_u32(&ctrl->o_free[s]), 8);          // one arrival per softmax warp of the slot
+      }
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(smem_u32(&ctrl->sched_full[i]), 1);
+        mbar_init(smem_u32(&ctrl->sched_empty[i]), kSoftmaxWarps + 1);
+      }
+      ctrl->abort_flag = 0;
+      mbar_fence_init();
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(smem_u32(&ctrl->sched_full[i]), 1);
-      mbar_init(smem_u32(&ctrl->sched_empty[i]), kSoftmaxWarps + 1);
+    __syncwarp();
+    named_bar_arrive(1, kThreads);
+  } else {
+    // ---------------- TMEM allocation (MMA warp owns it) ----------------
+    if (warp == kMmaWarp) {
+      tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+      tmem_relinquish();
     }
-    ctrl->abort_flag = 0;
-    mbar_fence_init();
+    tc_fence_before();
+    named_bar_sync(1, kThreads);
+    tc_fence_after();
   }
-  // ---------------- TMEM allocation (MMA warp owns it) ----------------
-  if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = ctrl->tmem_base;
+  const uint32_t tmem = warp == kProducerWarp ? 0u : ctrl->tmem_base;   // (the producer never uses it)
   volatile int* abort_flag = &ctrl->abort_flag;
 
   if (warp == kProducerWarp) {
