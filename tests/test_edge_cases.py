@@ -208,3 +208,40 @@ def test_prefill_outlier_keys_move_the_exponent_reference(dtype, causal):
     ref = sdpa_ref.prefill_reference([q[0].transpose(0, 1)], [k[0].transpose(0, 1)], [v[0].transpose(0, 1)], qh, kvh, causal)[0]
     assert torch.isfinite(out.float()).all()
     assert_close_both(out[0].transpose(0, 1), ref, dtype, s, "outlier keys")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layout", ["dense", "paged"])
+@pytest.mark.parametrize("shape", [(1, 8, 2, 128, 2048, False, 128), (1, 8, 8, 128, 4096, False, 64), (2, 4, 1, 200, 1000, False, 128),
+                                   (1, 2, 1, 2048, 2048, True, 128), (1, 4, 2, 1100, 1100, True, 64), (3, 2, 2, 128, 640, False, 128)],
+                         ids=["b1-q128-kv2048", "b1-mha-kv4096-d64", "b2-q200-kv1000", "b1-causal-2048", "b1-causal-1100-d64", "b3-kv640"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
+def test_prefill_few_work_items_split_kv(layout, shape, dtype):
+    """Launches with far fewer (query tile, head pair, sequence) items than SMs: the library cuts every sequence's KV
+    range into parts that run as work items of their own and merges them by their log-sum-exps (the reference splits KV
+    when B x QH < SMs, kernels/attention.py:836-841).  Paged sequences are shorter than the table allows, so some parts
+    see no key at all."""
+    import ctypes as C
+
+    from kernels import _native
+    from test_attention import run_prefill
+
+    b, qh, kvh, lq, lkv, causal, d = shape
+    gen = torch.Generator().manual_seed(lq * 7 + lkv + qh)
+    qs = [torch.randn((lq, qh, d), generator=gen).to(dtype).to(DEV) for _ in range(b)]
+    if layout == "paged" and not causal:
+        kv_lens = [max(1, lkv - 300 * i - 77) for i in range(b)]      # shorter than the widest table row
+    else:
+        kv_lens = [lkv] * b
+    ks = [torch.randn((n, kvh, d), generator=gen).to(dtype).to(DEV) for n in kv_lens]
+    vs = [torch.randn((n, kvh, d), generator=gen).to(dtype).to(DEV) for n in kv_lens]
+    refs = sdpa_ref.prefill_reference(qs, ks, vs, qh, kvh, causal)
+    outs = run_prefill(layout, qs, ks, vs, causal, permute=11, pad=-1, poison=float("nan"))
+    for i in range(b):
+        assert_close_both(outs[i], refs[i], dtype, kv_lens[i], f"seq {i}", strict=4e-3 if dtype == torch.float32 else None)
+    # the split really is in play for these shapes: the library asks for room for the parts
+    a = _native.PrefillArgs()
+    a.dtype, a.layout = _native.DTYPE_CODE[dtype], _native.DENSE
+    a.batch, a.q_heads, a.kv_heads, a.max_q, a.max_kv, a.head_dim = b, qh, kvh, lq, lkv, d
+    a.device = torch.cuda.current_device()
+    assert _native.lib().b200attn_prefill_workspace_bytes(C.byref(a)) > b * qh * lq * d * 2

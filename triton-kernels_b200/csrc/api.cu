@@ -138,8 +138,10 @@ int b200attn_device_info(int device, b200attn_device_info_t* info) {
 }
 
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args_t* a) {
-  if (!a) return 0;
-  return prefill_workspace_bytes(*a);
+  if (!a || a->kv_heads <= 0 || a->q_heads <= 0) return 0;
+  b200attn_device_info_t info;
+  if (query_device(a->device, &info)) return 0;
+  return prefill_workspace_bytes(*a, info.sm_count);
 }
 
 size_t b200attn_decode_workspace_bytes(const b200attn_decode_args_t* a) {

@@ -67,7 +67,9 @@ constexpr int kExpEmuOf4 = B200ATTN_EXP_EMU_OF4;
 struct ItemWork {
   bool valid;
   int len_q, len_k;
-  long long kv_row0;   // first kv row of the sequence (dense / ragged)
+  long long kv_row0;   // first kv row this item reads (dense / ragged)
+  int kv_tok0;         // first key of the sequence this item reads (non-zero only when the KV range is split)
+  long long out_row0[kSlots];   // first output row (the partial buffer's rows when the KV range is split)
   int kv_head_coord;
   int b;
   int q_head[kSlots];
@@ -172,7 +174,8 @@ __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item
   } else {
     // row blocks are the slowest-varying index and, under a causal mask, are handed out heaviest first;
     // the q heads of one KV head are neighbours and share its K/V in L2
-    const int per_block = head_units * p.batch;
+    // with a split KV range every (sequence, KV part) pair is a sequence of its own here ("virtual" batch index)
+    const int per_block = head_units * p.batch * p.kv_split;
     const int nblocks = blocks_of(p.max_q, rows);
     const int blk = item / per_block, rest = item - blk * per_block;
     wblock = p.is_causal ? (nblocks - 1 - blk) : blk;
@@ -180,7 +183,11 @@ __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item
     wb = rest / head_units;
   }
   w.valid = wb >= 0;
+  const int vb = wb;                                   // virtual batch index: rows of the partial buffer
+  int part = 0;
+  if (p.kv_split > 1 && wb >= 0) { part = wb % p.kv_split; wb /= p.kv_split; }
   w.b = wb;
+  w.kv_tok0 = part * p.kv_split_len;
   w.len_q = w.len_k = 0;
   w.kv_row0 = 0;
   w.kv_head_coord = 0;
@@ -189,6 +196,7 @@ __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item
     w.q_head[s] = p.head_pair ? wunit * 2 + s : wunit;
     w.m0[s] = p.head_pair ? wblock * kBM : (wblock * kSlots + s) * kBM;
     w.q_row0[s] = 0;
+    w.out_row0[s] = 0;
     w.q_head_coord[s] = 0;
   }
   if (w.valid) {
@@ -203,20 +211,29 @@ __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item
       w.kv_row0 = ka;
       w.kv_head_coord = kv_head;
 #pragma unroll
-      for (int s = 0; s < kSlots; ++s) { w.q_row0[s] = qa; w.q_head_coord[s] = w.q_head[s]; }
+      for (int s = 0; s < kSlots; ++s) { w.q_row0[s] = qa; w.out_row0[s] = qa; w.q_head_coord[s] = w.q_head[s]; }
     } else {
       w.len_q = p.max_q;
 #pragma unroll
-      for (int s = 0; s < kSlots; ++s) w.q_row0[s] = (static_cast<long long>(wb) * p.q_heads + w.q_head[s]) * p.max_q;
+      for (int s = 0; s < kSlots; ++s) {
+        w.q_row0[s] = (static_cast<long long>(wb) * p.q_heads + w.q_head[s]) * p.max_q;
+        w.out_row0[s] = (static_cast<long long>(vb) * p.q_heads + w.q_head[s]) * p.max_q;
+      }
       if (p.layout == B200ATTN_DENSE) {
         w.len_k = p.max_kv;
-        w.kv_row0 = (static_cast<long long>(wb) * p.kv_heads + kv_head) * p.max_kv;
+        w.kv_row0 = (static_cast<long long>(wb) * p.kv_heads + kv_head) * p.max_kv + w.kv_tok0;
       } else {
         long long n = load_index(p.kv_indptr, p.indptr_is_i64, wb);
         const long long cap = p.table_stride * static_cast<long long>(p.page_size);
         n = n < 0 ? 0 : (n > cap ? cap : n);
         w.len_k = static_cast<int>(n);
         w.kv_head_coord = kv_head;
+      }
+      if (p.kv_split > 1) {
+        // this item sees the keys [kv_tok0, kv_tok0 + kv_split_len) of the sequence only
+        int local = w.len_k - w.kv_tok0;
+        local = local < 0 ? 0 : (local > p.kv_split_len ? p.kv_split_len : local);
+        w.len_k = local;
       }
     }
   }
@@ -226,8 +243,8 @@ __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item
     int n = 0;
     if (w.valid && w.m0[s] < w.len_q) {
       int kv_hi = w.len_k;
-      if (p.is_causal) kv_hi = min(kv_hi, min(w.m0[s] + kBM, w.len_q));
-      n = (kv_hi + kBN - 1) / kBN;
+      if (p.is_causal) kv_hi = min(kv_hi, min(w.m0[s] + kBM, w.len_q) - w.kv_tok0);
+      n = kv_hi > 0 ? (kv_hi + kBN - 1) / kBN : 0;
     }
     w.nkv[s] = n;
     w.nkv_max = max(w.nkv_max, n);
@@ -383,12 +400,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           int count = 0;
           auto page_row = [&](const int* table, int t) -> int {
             if (t >= w.len_k) return -1;
-            const int lp = t / p.page_size;
+            const int tg = t + w.kv_tok0;          // position in the whole sequence
+            const int lp = tg / p.page_size;
             const int page = __ldg(table + lp);
             // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
             const bool bad = page < 0 || page >= p.num_pages;
             if (bad) p.header[0] = DEV_ERR_PAGE_RANGE;
-            return p.num_pages > 0 ? (bad ? 0 : page) * p.page_size + (t - lp * p.page_size) : -1;
+            return p.num_pages > 0 ? (bad ? 0 : page) * p.page_size + (tg - lp * p.page_size) : -1;
           };
           const int* vtab = p.v_table + static_cast<long long>(w.b) * p.table_stride;
           const int* ktab = p.k_table + static_cast<long long>(w.b) * p.table_stride;
@@ -752,7 +770,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int n = w.nkv[s];
       const int m0s = w.m0[s];
       const int len_k = w.len_k;
-      const int row_abs = m0s + rowA;                   // query index of row A inside the sequence (row B: + 8)
+      const int row_abs = m0s + rowA - w.kv_tok0;       // query index of row A relative to the item's first key (row B: + 8)
       if (pend && n == 0) {
         // no score tile in this item to hang the previous item's epilogue on
         ok = flush(false);
@@ -903,7 +921,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // ---------------- the item's epilogue becomes pending ----------------
       const int len_q = w.len_q;
       const bool slot_live = w.valid && m0s < len_q;
-      const long long qrow0 = w.q_row0[s];
+      const long long qrow0 = w.out_row0[s];
       const int qhead = w.q_head[s];
       pend = true;
       pend_acc = n > 0;
@@ -911,6 +929,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       pend_rows = slot_live ? min(kBM, len_q - m0s) : 0;
       pend_la = quad_sum(l_a);
       pend_lb = quad_sum(l_b);
+      if (p.lse != nullptr && q == 0) {
+        // split KV range: the merge needs every row's log-sum-exp (log2 domain; -inf for a row that saw no key)
+        float* lse = p.lse + qrow0 + m0s + rowA;
+        if (rowA < (slot_live ? min(kBM, len_q - m0s) : 0)) lse[0] = pend_la > 0.f ? m_a + log2f(pend_la) : -INFINITY;
+        if (rowA + 8 < (slot_live ? min(kBM, len_q - m0s) : 0)) lse[8] = pend_lb > 0.f ? m_b + log2f(pend_lb) : -INFINITY;
+      }
       if (p.layout == B200ATTN_RAGGED) {
         pend_stride = static_cast<long long>(p.q_heads) * D;
         pend_off = ((qrow0 + m0s + rowA) * p.q_heads + qhead) * D;
@@ -937,6 +961,74 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 }  // namespace
 
 namespace {
+
+// Merge of the parts of a split KV range.  part[(b * parts + s)][h][r][:] holds the normalised output of part s and
+// lse[...] its log-sum-exp (log2 domain): out = sum_s 2^(lse_s - max) part_s / sum_s 2^(lse_s - max)
+// (the reference's merge kernel, kernels/attention.py:659-746, on normalised instead of raw accumulators).
+template <typename OutT, int D>
+__global__ void __launch_bounds__(256) prefill_merge_kernel(const OutT* __restrict__ part, const float* __restrict__ lse,
+                                                            OutT* __restrict__ out, long long rows_per_batch, int batch,
+                                                            int parts) {
+  constexpr int VEC = 16 / sizeof(OutT);          // elements per 16-byte piece
+  constexpr int PIECES = D / VEC;
+  const long long total = static_cast<long long>(batch) * rows_per_batch * PIECES;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int piece = static_cast<int>(idx % PIECES);
+    const long long row = idx / PIECES;                    // (b, h, r) flattened
+    const long long b = row / rows_per_batch, hr = row - b * rows_per_batch;
+    float mx = -INFINITY;
+    for (int sp = 0; sp < parts; ++sp) mx = fmaxf(mx, __ldg(lse + (b * parts + sp) * rows_per_batch + hr));
+    float acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+    float wsum = 0.f;
+    for (int sp = 0; sp < parts; ++sp) {
+      const long long prow = (b * parts + sp) * rows_per_batch + hr;
+      const float l = __ldg(lse + prow);
+      const float w = (l == -INFINITY) ? 0.f : fast_exp2(l - mx);
+      wsum += w;
+      const uint4 u = __ldg(reinterpret_cast<const uint4*>(part + prow * D) + piece);
+      const OutT* e = reinterpret_cast<const OutT*>(&u);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] += w * ElemTraits<OutT>::to_float(e[i]);
+    }
+    const float inv = wsum > 0.f ? 1.f / wsum : 0.f;
+    uint4 o;
+    OutT* oe = reinterpret_cast<OutT*>(&o);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) oe[i] = ElemTraits<OutT>::from_float(acc[i] * inv);
+    reinterpret_cast<uint4*>(out + row * D)[piece] = o;
+  }
+}
+
+// How a launch with few work items cuts every sequence's KV range, so that more SMs than there are (query tile, head
+// pair, sequence) items have work: the reference splits KV when B x QH < SMs (kernels/attention.py:836-841).  Dense and
+// paged layouts only: a ragged problem's lengths are not known on the host.
+struct SplitPlan {
+  int parts;        // 1: no split
+  int part_len;     // keys per part, a multiple of 128
+};
+SplitPlan split_plan(const b200attn_prefill_args_t& a, int sm_count) {
+  SplitPlan sp{1, 0};
+  if (a.layout == B200ATTN_RAGGED || a.batch <= 0 || a.max_q <= 0) return sp;
+  const int group = a.q_heads / a.kv_heads;
+  const bool head_pair = group % 2 == 0;
+  const int item_rows = head_pair ? kBM : 2 * kBM;
+  const long long head_units = head_pair ? a.q_heads / 2 : a.q_heads;
+  const long long items = static_cast<long long>((a.max_q + item_rows - 1) / item_rows) * head_units * a.batch;
+  const long long kv_cap = a.layout == B200ATTN_DENSE ? a.max_kv : a.table_stride * static_cast<long long>(a.page_size);
+  const long long tiles = (kv_cap + kBN - 1) / kBN;
+  if (items <= 0 || items * 2 > sm_count || tiles < 4) return sp;
+  long long parts = std::min<long long>(std::min<long long>(8, sm_count / items), tiles / 2);
+  if (parts < 2) return sp;
+  const long long per = (tiles + parts - 1) / parts;
+  sp.part_len = static_cast<int>(per * kBN);
+  sp.parts = static_cast<int>((tiles + per - 1) / per);
+  if (sp.parts < 2) sp.parts = 1;
+  return sp;
+}
+
 struct CastPlan {
   size_t q_elems, kv_elems, q_off, k_off, v_off, total;
 };
@@ -960,13 +1052,33 @@ CastPlan cast_plan(const b200attn_prefill_args_t& a) {
 }
 }  // namespace
 
-size_t prefill_workspace_bytes(const b200attn_prefill_args_t& a) {
-  if (a.dtype == B200ATTN_F32) return cast_plan(a).total;
-  return kHeaderBytes;
+namespace {
+// workspace: header | fp32 inputs rounded to fp16 (fp32 calls) | parts of a split KV range and their log-sum-exps
+struct WsPlan {
+  size_t part_off, lse_off, total;
+  SplitPlan split;
+};
+WsPlan ws_plan(const b200attn_prefill_args_t& a, int sm_count) {
+  WsPlan w{};
+  auto up = [](size_t x) { return (x + 255) & ~static_cast<size_t>(255); };
+  size_t off = a.dtype == B200ATTN_F32 ? cast_plan(a).total : static_cast<size_t>(kHeaderBytes);
+  w.split = split_plan(a, sm_count);
+  if (w.split.parts > 1) {
+    const size_t rows = static_cast<size_t>(a.batch) * w.split.parts * a.q_heads * a.max_q;
+    const size_t esz = a.dtype == B200ATTN_F32 ? 4 : 2;
+    w.part_off = off; off = up(off + rows * a.head_dim * esz);
+    w.lse_off = off;  off = up(off + rows * sizeof(float));
+  }
+  w.total = off;
+  return w;
 }
+}  // namespace
+
+size_t prefill_workspace_bytes(const b200attn_prefill_args_t& a, int sm_count) { return ws_plan(a, sm_count).total; }
 
 int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream_t stream) {
-  const size_t need = prefill_workspace_bytes(a_in);
+  const WsPlan wsp = ws_plan(a_in, sm_count);
+  const size_t need = wsp.total;
   if (a_in.workspace == nullptr || a_in.workspace_bytes < need || (reinterpret_cast<uintptr_t>(a_in.workspace) & 255)) {
     set_error("prefill: workspace needs %zu bytes, 256-byte aligned (got %zu)", need, a_in.workspace_bytes);
     return B200ATTN_E_WORKSPACE;
@@ -1010,6 +1122,16 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
   const int item_rows = p.head_pair ? kBM : 2 * kBM;
   const int head_units = p.head_pair ? a.q_heads / 2 : a.q_heads;
   p.scale_log2 = a.sm_scale * 1.4426950408889634f;
+  p.kv_split = wsp.split.parts;
+  p.kv_split_len = wsp.split.part_len;
+  p.lse = nullptr;
+  if (p.kv_split > 1) {
+    // the kernel writes every part's normalised output and log-sum-exp into the workspace; a merge kernel follows
+    unsigned char* ws = static_cast<unsigned char*>(a_in.workspace);
+    p.out = ws + wsp.part_off;
+    p.lse = reinterpret_cast<float*>(ws + wsp.lse_off);
+    p.out_align32 = 1;
+  }
 
   CUtensorMap tq, tk, tv;
   int rc;
@@ -1037,7 +1159,7 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
       if ((rc = make_token_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box))) return rc;
       if ((rc = make_token_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box))) return rc;
     }
-    total_items = static_cast<long long>((a.max_q + item_rows - 1) / item_rows) * head_units * a.batch;
+    total_items = static_cast<long long>((a.max_q + item_rows - 1) / item_rows) * head_units * a.batch * p.kv_split;
   }
   if (total_items <= 0) return B200ATTN_OK;
   if (total_items > 0x7fffffff) { set_error("prefill: too many work items"); return B200ATTN_E_UNSUPPORTED; }
@@ -1063,6 +1185,20 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
 #undef B200ATTN_LAUNCH_PREFILL
   e = cudaGetLastError();
   if (e != cudaSuccess) return cuda_fail(e, "prefill kernel launch");
+  if (p.kv_split > 1) {
+    const long long rows_per_batch = static_cast<long long>(a.q_heads) * a.max_q;
+    const long long pieces = static_cast<long long>(a.batch) * rows_per_batch * (D / (f32 ? 4 : 8));
+    const int blocks = static_cast<int>(std::min<long long>((pieces + 255) / 256, static_cast<long long>(sm_count) * 8));
+#define B200ATTN_LAUNCH_MERGE(OUT, DIM)                                                                              \
+    prefill_merge_kernel<OUT, DIM><<<blocks, 256, 0, stream>>>(static_cast<const OUT*>(p.out), p.lse,                 \
+                                                               static_cast<OUT*>(a_in.out), rows_per_batch, a.batch, p.kv_split)
+    if (f32) { if (D == 128) B200ATTN_LAUNCH_MERGE(float, 128); else B200ATTN_LAUNCH_MERGE(float, 64); }
+    else if (a.dtype == B200ATTN_BF16) { if (D == 128) B200ATTN_LAUNCH_MERGE(__nv_bfloat16, 128); else B200ATTN_LAUNCH_MERGE(__nv_bfloat16, 64); }
+    else { if (D == 128) B200ATTN_LAUNCH_MERGE(__half, 128); else B200ATTN_LAUNCH_MERGE(__half, 64); }
+#undef B200ATTN_LAUNCH_MERGE
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return cuda_fail(e, "prefill merge kernel launch");
+  }
   return B200ATTN_OK;
 }
 

@@ -32,10 +32,13 @@ struct PrefillParams {
   int is_causal;
   int out_align32;      // the output pointer is 32-byte aligned: the epilogue may use 32-byte stores
   int head_pair;        // 1: the two slots of a work item are two q heads of one KV head over the same 128 rows
+  int kv_split;         // parts every sequence's KV range is cut into (1: not split)
+  int kv_split_len;     // keys per part (a multiple of 128)
+  float* lse;           // split only: log-sum-exp per (virtual sequence, q head, row), log2 domain
   float scale_log2;
 };
 
-size_t prefill_workspace_bytes(const b200attn_prefill_args_t& a);
+size_t prefill_workspace_bytes(const b200attn_prefill_args_t& a, int sm_count);
 int launch_prefill(const b200attn_prefill_args_t& a, int sm_count, cudaStream_t stream);
 
 }  // namespace b200attn
