@@ -213,8 +213,8 @@ def test_prefill_outlier_keys_move_the_exponent_reference(dtype, causal):
 @pytest.mark.gpu
 @pytest.mark.parametrize("layout", ["dense", "paged"])
 @pytest.mark.parametrize("shape", [(1, 8, 2, 128, 2048, False, 128), (1, 8, 8, 128, 4096, False, 64), (2, 4, 1, 200, 1000, False, 128),
-                                   (1, 2, 1, 2048, 2048, True, 128), (1, 4, 2, 1100, 1100, True, 64), (3, 2, 2, 128, 640, False, 128)],
-                         ids=["b1-q128-kv2048", "b1-mha-kv4096-d64", "b2-q200-kv1000", "b1-causal-2048", "b1-causal-1100-d64", "b3-kv640"])
+                                   (1, 2, 1, 2048, 2048, True, 128), (1, 4, 2, 1100, 1100, True, 64), (3, 2, 2, 128, 1280, False, 128)],
+                         ids=["b1-q128-kv2048", "b1-mha-kv4096-d64", "b2-q200-kv1000", "b1-causal-2048", "b1-causal-1100-d64", "b3-kv1280"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32], ids=["bf16", "fp32"])
 def test_prefill_few_work_items_split_kv(layout, shape, dtype):
     """Launches with far fewer (query tile, head pair, sequence) items than SMs: the library cuts every sequence's KV
