@@ -1011,20 +1011,40 @@ struct SplitPlan {
 };
 SplitPlan split_plan(const b200attn_prefill_args_t& a, int sm_count) {
   SplitPlan sp{1, 0};
-  if (a.layout == B200ATTN_RAGGED || a.batch <= 0 || a.max_q <= 0) return sp;
+  if (a.layout == B200ATTN_RAGGED || a.batch <= 0 || a.max_q <= 0 || sm_count <= 0) return sp;
   const int group = a.q_heads / a.kv_heads;
   const bool head_pair = group % 2 == 0;
   const int item_rows = head_pair ? kBM : 2 * kBM;
   const long long head_units = head_pair ? a.q_heads / 2 : a.q_heads;
-  const long long items = static_cast<long long>((a.max_q + item_rows - 1) / item_rows) * head_units * a.batch;
+  const long long nblocks = (a.max_q + item_rows - 1) / item_rows;
+  const long long items = nblocks * head_units * a.batch;
   const long long kv_cap = a.layout == B200ATTN_DENSE ? a.max_kv : a.table_stride * static_cast<long long>(a.page_size);
-  const long long tiles = (kv_cap + kBN - 1) / kBN;
-  // a part is at least four tiles: below that the merge launch costs more than the idle SMs (measured on the
-  // reference's B = 16 grid: a 512-key range in two parts ran 14 % slower than unsplit, a 2 048-key one 26 % faster)
-  if (items <= 0 || items * 2 > sm_count || tiles < 8) return sp;
-  long long parts = std::min<long long>(std::min<long long>(8, sm_count / items), tiles / 4);
-  if (parts < 2) return sp;
-  const long long per = (tiles + parts - 1) / parts;
+  const long long tiles = (kv_cap + kBN - 1) / kBN;            // longest item, in 128-key steps
+  if (items <= 0 || tiles < 8) return sp;
+  // steps of all items: under a causal mask row block r stops at its diagonal
+  long long total = 0;
+  for (long long r = 0; r < nblocks; ++r) {
+    const long long reach = a.is_causal ? std::min<long long>(tiles, ((r + 1) * item_rows + kBN - 1) / kBN) : tiles;
+    total += reach;
+  }
+  total *= head_units * a.batch;
+  // Estimated duration in units of one 128-key step of both slots: the longest item or the average load of an SM,
+  // whichever is larger, with about two steps of fixed cost per item (pipeline fill, masked tile, epilogue) and two
+  // more for the merge launch.  Measured anchors on B200: B = 16, 8/2 heads, 128 x 2 048 cross attention (64 items)
+  // 45 -> 36 us in two parts; a 512-key range in two parts is slower than unsplit (hence four tiles per part at least).
+  auto cost = [&](long long parts) -> double {
+    const double longest = static_cast<double>((tiles + parts - 1) / parts) + 2.0;
+    const double load = (static_cast<double>(total) + 2.0 * static_cast<double>(items * parts)) / sm_count;
+    return std::max(longest, load) + (parts > 1 ? 2.0 : 0.0);
+  };
+  long long best = 1;
+  double best_cost = cost(1);
+  for (long long parts = 2; parts <= 8 && tiles / parts >= 4; parts *= 2) {
+    const double c = cost(parts);
+    if (c < 0.85 * cost(1) && c < best_cost) { best = parts; best_cost = c; }
+  }
+  if (best < 2) return sp;
+  const long long per = (tiles + best - 1) / best;
   sp.part_len = static_cast<int>(per * kBN);
   sp.parts = static_cast<int>((tiles + per - 1) / per);
   if (sp.parts < 2) sp.parts = 1;
