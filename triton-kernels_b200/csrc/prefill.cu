@@ -170,7 +170,12 @@ __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item
   int wb = -1, wblock = 0, wunit = 0;
   if (p.layout == B200ATTN_RAGGED) {
     wunit = item % head_units;
-    if (!find_ragged_work(p, item / head_units, rows, lane, &wb, &wblock)) wb = -1;
+    // Under a causal mask the row blocks are handed out from the end of the packed tensor backwards: the later
+    // blocks of a sequence are the heavier ones, and the blocks left for the drain of the grid are then the first,
+    // light ones of the first sequences (the sizes are not known on the host, so there is no global order by weight).
+    const int nflat = p.total_items / head_units;
+    const int flat = item / head_units;
+    if (!find_ragged_work(p, p.is_causal ? nflat - 1 - flat : flat, rows, lane, &wb, &wblock)) wb = -1;
   } else {
     // row blocks are the slowest-varying index and, under a causal mask, are handed out heaviest first;
     // the q heads of one KV head are neighbours and share its K/V in L2
