@@ -19,8 +19,15 @@ DEST = os.path.join(HERE, "_ref", "tests")
 FILES = ("test_attention.py", "test_decode.py", "test_speculative_decode.py")
 
 
-def stage(ref_root: str = "/root/reference") -> bool:
+def default_checkout() -> str:
+    """``$B200ATTN_REFERENCE_CHECKOUT``, else a directory named ``reference`` beside this repository."""
+    repo = os.path.dirname(HERE)
+    return os.environ.get("B200ATTN_REFERENCE_CHECKOUT", os.path.join(os.path.dirname(repo), "reference"))
+
+
+def stage(ref_root: str = "") -> bool:
     """Returns False (and stages nothing) when there is no reference checkout at ``ref_root``."""
+    ref_root = ref_root or default_checkout()
     src_dir = os.path.join(ref_root, "tests")
     if not all(os.path.isfile(os.path.join(src_dir, f)) for f in FILES):
         return False
@@ -37,5 +44,5 @@ def stage(ref_root: str = "/root/reference") -> bool:
 
 
 if __name__ == "__main__":
-    ok = stage(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ok = stage(sys.argv[1] if len(sys.argv) > 1 else "")
     print("staged into", DEST if ok else "nothing: no reference checkout found")

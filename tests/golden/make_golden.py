@@ -45,7 +45,9 @@ def load_reference_tests(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # the checkout: first argument, else $B200ATTN_REFERENCE_CHECKOUT, else a directory `reference` beside this repository
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get(
+        "B200ATTN_REFERENCE_CHECKOUT", os.path.join(os.path.dirname(ROOT), "reference"))
     ref = load_reference_tests(ref_root)
     t_att, t_dec, t_spec = ref["test_attention"], ref["test_decode"], ref["test_speculative_decode"]
 
