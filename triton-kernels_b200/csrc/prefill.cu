@@ -15,8 +15,8 @@
 // TMEM (512 columns): S0 | S1 | O0 | O1.  Per KV tile j and slot s:
 //   S_s = Q_s K_j^T   (SS MMA, 128x128xD)            -> commit s_full[s]
 //   the slot's warps read S_s, mask, keep a running max / sum per row in the exp2 domain, rescale O_s in TMEM only
-//   when the max moved by more than 2^8, and write P_s as packed 16-bit (16x128b layout) over the first 64 columns
-//   of S_s                                                            -> arrive p_ready[s]
+//   when the max moved by more than 2^8, and write P_s as packed 16-bit (16x128b layout) over the first 32 columns
+//   of each 64-column half of S_s                                     -> arrive p_ready[s]
 //   O_s += P_s V_j    (TS MMA, A from TMEM, V is the MN-major B operand) -> commit o_done[s]
 // The two slots are interleaved so that one slot's softmax overlaps the other's MMAs.  At the end of an item the
 // MMA warp issues the first score tile of the next item behind the last PVs, and the softmax warps finish the old
@@ -488,7 +488,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mma_commit_lead(smem_u32(&ctrl->s_full[s]), lead);
     };
     auto issue_pv = [&](int s, uint64_t vb, bool first) {
-      // O_s (+)= P_s V : A = packed 16-bit P in the first 64 TMEM columns of the S tile, B = V, MN-major
+      // O_s (+)= P_s V : A = packed 16-bit P, 32 TMEM columns at the start of each 64-column half of the S tile;
+      // B = V, MN-major
       mma_ts_batch8(tmem_O[s], tmem_S[s], vb, idesc_o, first ? 0u : 1u, lead);
       mma_commit_lead(smem_u32(&ctrl->o_done[s]), lead);
     };
@@ -792,29 +793,47 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         int lim_a = len_k - 1 - j * kBN, lim_b = lim_a;
         if (p.is_causal) { lim_a = min(lim_a, row_abs - j * kBN); lim_b = min(lim_b, row_abs + 8 - j * kBN); }
         const bool masked = min(lim_a, lim_b) < kBN - 1;
-        float mx_a, mx_b;
-        {
-          // pass 1: row maxima (the scores are read again in pass 2: 64 registers cannot be held across it)
-          uint32_t v[64];
-          tmem_ld_16x256b_x16(tS, v);
-          tmem_wait_ld();
-          if (masked) {
+        if (masked) {
+          // The mask is written into the score tile itself (-inf over the hidden columns) before the two passes
+          // below, which then have one form for every tile: a masked copy of their bodies, run once per item from a
+          // cold instruction cache, cost more than this extra round trip through tensor memory.
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t v[32];
+            tmem_ld_16x256b_x8(tS + c * 64, v);
+            tmem_wait_ld();
+            const int ta = lim_a - c * 64 - 2 * q, tb = lim_b - c * 64 - 2 * q;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < 8; ++i) {
 #pragma unroll
               for (int e = 0; e < 2; ++e) {
-                const int col = 8 * i + 2 * q + e;
-                if (col > lim_a) v[4 * i + e] = 0xff800000u;        // -inf
-                if (col > lim_b) v[4 * i + 2 + e] = 0xff800000u;
+                v[4 * i + e] = (8 * i + e > ta) ? 0xff800000u : v[4 * i + e];           // -inf
+                v[4 * i + 2 + e] = (8 * i + e > tb) ? 0xff800000u : v[4 * i + 2 + e];
               }
             }
+            tmem_st_16x256b_x8(tS + c * 64, v);
           }
+          tmem_wait_st();
+        }
+        float mx_a, mx_b;
+        uint32_t v_hi[32];     // columns 64..127 of the tile stay in registers from pass 1 to pass 2
+        {
+          // pass 1: row maxima.  Columns 0..63 are read again in pass 2 (all 128 scores cannot be held across it).
+          uint32_t v[32];
+          tmem_ld_16x256b_x8(tS, v);
+          tmem_ld_16x256b_x8(tS + 64, v_hi);
+          tmem_wait_ld();
           float a0 = fmaxf(__uint_as_float(v[0]), __uint_as_float(v[1]));
           float b0 = fmaxf(__uint_as_float(v[2]), __uint_as_float(v[3]));
 #pragma unroll
-          for (int i = 1; i < 16; ++i) {
+          for (int i = 1; i < 8; ++i) {
             a0 = max3(a0, __uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]));
             b0 = max3(b0, __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            a0 = max3(a0, __uint_as_float(v_hi[4 * i]), __uint_as_float(v_hi[4 * i + 1]));
+            b0 = max3(b0, __uint_as_float(v_hi[4 * i + 2]), __uint_as_float(v_hi[4 * i + 3]));
           }
           mx_a = quad_max(a0);
           mx_b = quad_max(b0);
@@ -832,19 +851,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           ok = warp_wait(smem_u32(&ctrl->o_done[s]), (tile_cnt - 1) & 1);
           if (!ok) break;
           tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < D / 64; ++c) {
-            uint32_t ov[32];
-            tmem_ld_16x256b_x8(tO + c * 64, ov);
+          // (rare: 16 columns at a time and not unrolled, so that the scores held in registers stay there)
+#pragma unroll 1
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t ov[8];
+            tmem_ld_16x256b_x2(tO + c * 16, ov);
             tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < 2; ++i) {
               ov[4 * i] = __float_as_uint(__uint_as_float(ov[4 * i]) * alpha_a);
               ov[4 * i + 1] = __float_as_uint(__uint_as_float(ov[4 * i + 1]) * alpha_a);
               ov[4 * i + 2] = __float_as_uint(__uint_as_float(ov[4 * i + 2]) * alpha_b);
               ov[4 * i + 3] = __float_as_uint(__uint_as_float(ov[4 * i + 3]) * alpha_b);
             }
-            tmem_st_16x256b_x8(tO + c * 64, ov);
+            tmem_st_16x256b_x2(tO + c * 16, ov);
           }
         }
         const float neg_a = (m_a == -INFINITY) ? 0.f : -m_a, neg_b = (m_b == -INFINITY) ? 0.f : -m_b;
@@ -878,24 +898,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           rs = add_f2(rs, pack_f2(p0, p1));
           return ElemTraits<T>::pack2(p0, p1);
         };
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          // pass 2, 64 columns at a time: exponentials, row sums, P as packed 16-bit in the 16x128b layout (the pair
-          // of columns 8 i + 2 q + {0, 1} is packed column 4 i + q), written over score columns that are done with
-          uint32_t v[32];
-          tmem_ld_16x256b_x8(tS + c * 64, v);
-          tmem_wait_ld();
-          if (masked) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const int col = c * 64 + 8 * i + 2 * q + e;
-                if (col > lim_a) v[4 * i + e] = 0xff800000u;        // -inf
-                if (col > lim_b) v[4 * i + 2 + e] = 0xff800000u;
-              }
-            }
-          }
+        // pass 2, 64 columns at a time: exponentials, row sums, P as packed 16-bit in the 16x128b layout (the pair of
+        // columns 8 i + 2 q + {0, 1} of a half is packed column 4 i + q).  Each half of P goes over the first 32
+        // columns of its own half of S (kPHalfStride apart), so the upper half, still in registers, is done first
+        // and only the lower half is read from tensor memory a second time.
+        auto exp_half = [&](const uint32_t (&v)[32], uint32_t dst) {
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -903,7 +910,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             pk[2 * i] = exp_pair(v[4 * i], v[4 * i + 1], nega_2, rs_a, emu);
             pk[2 * i + 1] = exp_pair(v[4 * i + 2], v[4 * i + 3], negb_2, rs_b, emu);
           }
-          tmem_st_16x128b_x8(tS + c * 32, pk);
+          tmem_st_16x128b_x8(dst, pk);
+        };
+        exp_half(v_hi, tS + ptx::kPHalfStride);
+        {
+          uint32_t v[32];
+          tmem_ld_16x256b_x8(tS, v);
+          tmem_wait_ld();
+          exp_half(v, tS);
         }
         {
           float r0, r1;

@@ -183,6 +183,18 @@ __device__ __forceinline__ void tmem_ld_16x256b_x16(uint32_t taddr, uint32_t (&r
       : "r"(taddr)
       : "memory");
 }
+// 16 columns at a time in the same layout: for code that runs rarely and must not hold many registers
+__device__ __forceinline__ void tmem_ld_16x256b_x2(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x256b_x2(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.16x256b.x2.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.16x256b.x8.b32 [%0], "
@@ -370,7 +382,10 @@ __device__ __forceinline__ void mma_ss_batch(uint32_t d_tmem, uint64_t a_desc, u
   "add.u32 a1, %1, " #AOFF ";\n\tadd.s64 b1, %2, " #BOFF ";\n\t"                                \
   "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %3, t;\n\t"
 
-// Eight k-steps (128 keys) of O += P V: A is packed 16-bit P in the 64 tensor-memory columns at `a_tmem`; B is an MN-major 128-row V tile, 16 rows (2 KiB) per k-step.
+// Eight k-steps (128 keys) of O += P V: A is packed 16-bit P, keys 0..63 in the 32 tensor-memory columns at `a_tmem`
+// and keys 64..127 in the 32 columns at `a_tmem + kPHalfStride`; B is an MN-major 128-row V tile, 16 rows (2 KiB)
+// per k-step.
+constexpr uint32_t kPHalfStride = 64;
 __device__ __forceinline__ void mma_ts_batch8(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                               uint32_t accumulate_first, uint32_t lead) {
   asm volatile(
@@ -378,8 +393,9 @@ __device__ __forceinline__ void mma_ts_batch8(uint32_t d_tmem, uint32_t a_tmem, 
       "setp.ne.b32 p, %4, 0;\n\tsetp.eq.b32 t, 0, 0;\n\tsetp.ne.b32 e, %5, 0;\n\t"
       "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
       B200ATTN_TS_STEP(8, 128) B200ATTN_TS_STEP(16, 256) B200ATTN_TS_STEP(24, 384)
-      B200ATTN_TS_STEP(32, 512) B200ATTN_TS_STEP(40, 640) B200ATTN_TS_STEP(48, 768) B200ATTN_TS_STEP(56, 896)
+      B200ATTN_TS_STEP(64, 512) B200ATTN_TS_STEP(72, 640) B200ATTN_TS_STEP(80, 768) B200ATTN_TS_STEP(88, 896)
       "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate_first), "r"(lead) : "memory");
+  static_assert(kPHalfStride == 64, "the offsets in the instruction list above");
 }
 #undef B200ATTN_TS_STEP
 
