@@ -176,3 +176,43 @@ def test_planning_mirror_agrees_with_the_library(qh, kvh, m, batch, d, fp32):
     plan = decode_plan(info.sm_count, batch, qh, kvh, m, fp32=fp32)
     rows = decode_pass_group(qh // kvh, m) * m
     assert decode_workspace_bytes(plan, batch, kvh, d, rows) == want
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("qh,kvh,m,lens", [
+    (32, 8, 1, [8192]),                                   # one sequence: a single wave of short items
+    (32, 8, 1, [8192] * 16),                              # uniform batch that fits one wave of three-resident CTAs
+    (32, 8, 1, [4096] * 32),                              # ... and one that stays with two waves
+    (64, 8, 5, [8192] * 32),                              # speculative decode, uniform: one item per sequence
+    (64, 8, 5, [8192] * 4),
+    (8, 1, 5, [1500, 9000, 31000, 700, 16000, 12000]),    # one KV head (the eight-GPU shard)
+    (32, 8, 1, [600, 8000, 512, 4100, 7777, 2300, 900, 5000] * 8),   # uneven lengths, more sequences than one wave holds
+])
+def test_planner_chunk_matches_the_mirror(qh, kvh, m, lens):
+    """The chunk size and item count the device planner wrote into the workspace header are the ones
+    utils/launch_config.py derives from the same lengths (several waves or a single one)."""
+    from kernels import _native
+    from kernels.decode import decode_attention
+    from kernels.speculative_decode import speculative_decode_attention
+    from utils.launch_config import decode_chunk_tokens, decode_items, decode_plan
+
+    dev = torch.device("cuda")
+    info = _native.device_info(torch.cuda.current_device())
+    gen = torch.Generator().manual_seed(5)
+    total = sum(lens)
+    k = torch.randn((total, kvh, 64), generator=gen).to(torch.bfloat16).to(dev)
+    v = torch.randn((total, kvh, 64), generator=gen).to(torch.bfloat16).to(dev)
+    indptr = torch.tensor([0] + lens, dtype=torch.int64).cumsum(0).to(torch.int32).to(dev)
+    if m == 1:
+        q = torch.randn((len(lens), qh, 64), generator=gen).to(torch.bfloat16).to(dev)
+        decode_attention(q, k, v, kv_indptr=indptr)
+    else:
+        q = torch.randn((len(lens), qh, m, 64), generator=gen).to(torch.bfloat16).to(dev)
+        speculative_decode_attention(q, k, v, kv_indptr=indptr, causal=False)
+    torch.cuda.synchronize()
+    ws = _native._workspaces[(torch.cuda.current_device(), int(torch.cuda.current_stream().cuda_stream))]
+    header = ws[:16].view(torch.int32).tolist()
+    plan = decode_plan(info.sm_count, len(lens), qh, kvh, m)
+    assert header[0] == 0
+    assert header[1] == decode_chunk_tokens(plan, lens)
+    assert header[2] == sum(decode_items(plan, lens))

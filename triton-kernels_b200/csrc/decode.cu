@@ -208,7 +208,8 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
   __shared__ int s_warp[32];
   __shared__ int s_carry;
   __shared__ int s_chunk;
-  __shared__ int s_cand_chunk[kPlanThreads / 32], s_cand_items[kPlanThreads / 32];
+  __shared__ int s_cand_chunk[kPlanThreads / 32], s_cand_items[kPlanThreads / 32], s_cand_max[kPlanThreads / 32];
+  __shared__ int s_pick_items;
   __shared__ int s_hist[kPlanBuckets];     // items per size class, then the class's first execution slot
   __shared__ int s_cursor[kPlanBuckets];
   __shared__ int s_len[kPlanLenCache];      // sequence lengths, read from global memory once
@@ -234,10 +235,16 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
   // Chunk size: the smallest of 32 candidates between total / target_items and twice that for which the batch
   // splits into at most target_items items.  target_items is a whole number of waves of resident CTAs, so the grid
   // never spills a few CTAs into one more wave (measured: 2.9 waves run 8 % faster than 3.4).  One warp per candidate.
-  {
-    long long t = 0;
-    for (int w = 0; w < kPlanThreads / 32; ++w) t += s_tot[w];
-    long long base = (t + p.target_items - 1) / p.target_items;
+  // Then the same for a single wave (wave_items): when every sequence can be cut into near-equal items that are all
+  // resident at once, nothing is started or merged a second or third time on an SM, which is worth more than the
+  // finer grain of several waves if the lengths allow it (measured, 32 x 8 192 keys, 40 rows per KV head: 212 us
+  // against 245 us; one KV head of that batch: 91 us against 159 us).  The two plans are compared by an estimate
+  // of their run time in keys: the largest item plus the per-item overhead for one wave, the average load of a
+  // resident CTA plus half an item for several.
+  long long t = 0;
+  for (int w = 0; w < kPlanThreads / 32; ++w) t += s_tot[w];
+  auto evaluate = [&](int target) {
+    long long base = (t + target - 1) / target;
     base = ((base + kTileN - 1) / kTileN) * kTileN;
     if (base < p.min_chunk) base = p.min_chunk;
     if (base > (1 << 29)) base = 1 << 29;
@@ -245,14 +252,25 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     cand = ((cand + kTileN - 1) / kTileN) * kTileN;
     const int ck = static_cast<int>(cand);
     long long n = 0;
+    int biggest = 0;
     for (int b = lane; b < p.batch; b += 32) {
       const int len = len_of(b);
-      const int v = (len + ck - 1) / ck;
-      n += v < 1 ? 1 : v;
+      int v = (len + ck - 1) / ck;
+      if (v < 1) v = 1;
+      n += v;
+      biggest = max(biggest, min(len, seq_chunk(len, v, ck, p.equal_split)));
     }
-    for (int o = 16; o > 0; o >>= 1) n += __shfl_xor_sync(0xffffffffu, n, o);
-    if (lane == 0) { s_cand_chunk[warp] = ck; s_cand_items[warp] = n > 0x7fffffff ? 0x7fffffff : static_cast<int>(n); }
-  }
+    for (int o = 16; o > 0; o >>= 1) {
+      n += __shfl_xor_sync(0xffffffffu, n, o);
+      biggest = max(biggest, __shfl_xor_sync(0xffffffffu, biggest, o));
+    }
+    if (lane == 0) {
+      s_cand_chunk[warp] = ck;
+      s_cand_items[warp] = n > 0x7fffffff ? 0x7fffffff : static_cast<int>(n);
+      s_cand_max[warp] = biggest;
+    }
+  };
+  evaluate(p.target_items);
   __syncthreads();
   if (tid == 0) {
     int pick = kPlanThreads / 32 - 1;
@@ -260,7 +278,27 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
       if (s_cand_items[k] <= p.target_items) { pick = k; break; }
     }
     s_chunk = s_cand_chunk[pick];
+    s_pick_items = s_cand_items[pick];
     s_carry = 0;
+  }
+  __syncthreads();
+  if (p.wave_items > 0 && p.wave_items < p.target_items && s_pick_items > p.wave_items) {
+    evaluate(p.wave_items);
+    __syncthreads();
+    if (tid == 0) {
+      int pick = -1;
+      for (int k = 0; k < kPlanThreads / 32; ++k) {
+        if (s_cand_items[k] <= p.wave_items) { pick = k; break; }
+      }
+      if (pick >= 0) {
+        const float ovh = static_cast<float>(p.item_overhead);
+        const float n_several = static_cast<float>(s_pick_items);
+        const float several = (static_cast<float>(t) + n_several * ovh) / static_cast<float>(p.wave_items) +
+                              0.5f * (static_cast<float>(t) / n_several + ovh);
+        const float one = static_cast<float>(s_cand_max[pick]) + ovh;
+        if (one < several) s_chunk = s_cand_chunk[pick];
+      }
+    }
   }
   for (int i = tid; i < p.batch * p.kv_heads; i += kPlanThreads) p.counters[i] = 0;
   __syncthreads();
@@ -1198,6 +1236,15 @@ DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count) {
   long long target = (static_cast<long long>(sm_count) * per_sm) / std::max(1, a.kv_heads);
   if (target < 1) target = 1;
   w.target_items = static_cast<int>(target);
+  // one wave of the tensor-core kernels: 2 (tcgen05 kernel, more than 16 rows) or 3 resident CTAs per SM; their
+  // per-item start-up + merge cost in keys of streaming time (from the sweeps quoted in the planner)
+  w.wave_items = 0;
+  w.item_overhead = 0;
+  if (a.dtype != B200ATTN_F32) {
+    const bool wide = rows > 16;
+    w.wave_items = static_cast<int>(std::max<long long>(1, (static_cast<long long>(sm_count) * (wide ? 2 : 3)) / std::max(1, a.kv_heads)));
+    w.item_overhead = wide ? 448 : 128;
+  }
   // keep the partial write (rows x D fp32) small next to the chunk's K/V bytes
   int min_chunk = 128;
   const int by_rows = ((rows * 8 + kTileN - 1) / kTileN) * kTileN;
@@ -1266,6 +1313,7 @@ int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream
   p.causal = a.causal_drafts ? 1 : 0;
   p.box_shift = 6;
   p.target_items = w.target_items; p.min_chunk = w.min_chunk; p.max_items = w.max_items;
+  p.wave_items = w.wave_items; p.item_overhead = w.item_overhead;
   // Equal items per sequence and longest-first order let the greedy CTA dispatch pair long and short items: with two
   // or three whole waves the grid drains almost level (measured on B200, 16-token pages: 0.80 -> 0.84 of the copy
   // bandwidth for paged decode, 0.68 -> 0.76 for speculative decode).

@@ -43,6 +43,8 @@ struct DecodeParams {
   int box_shift;     // log2 of the keys per TMA box (paged: the largest power of two that divides the page size, <= 64)
   int causal;
   int target_items;
+  int wave_items;    // items of one KV head that are resident at once (one wave of CTAs); 0: never plan a single wave
+  int item_overhead; // start-up and merge of a work item, in keys of streaming time (planner's cost estimate)
   int min_chunk;
   int equal_split;   // 1: a sequence's items are of equal size; 0: full chunks and one remainder
   int max_items;
@@ -57,6 +59,8 @@ struct DecodeWsLayout {
   size_t o_off;
   size_t total;
   int target_items;
+  int wave_items;    // items of one KV head that are resident at once (one wave of CTAs); 0: never plan a single wave
+  int item_overhead; // start-up and merge of a work item, in keys of streaming time (planner's cost estimate)
   int min_chunk;
   int max_items;
 };

@@ -26,6 +26,9 @@ class DecodePlan:
     mma_tiles: int     # 16-row MMA tiles that hold group x q_len rows
     key_slices: int    # warps that split the keys of one stage
     threads: int
+    wave_items: int = 0      # items of one KV head resident at once (one wave); 0: a single wave is never planned
+    item_overhead: int = 0   # start-up + merge of an item in keys of streaming time (the planner's cost estimate)
+    equal_split: bool = True
 
 
 def decode_pass_group(group: int, q_len: int) -> int:
@@ -62,23 +65,54 @@ def decode_plan(sm_count: int, batch: int, q_heads: int, kv_heads: int, q_len: i
     min_chunk = max(128, by_rows)
     tiles = -(-rows // 16)
     slices = 4 if tiles <= 2 else (2 if tiles <= 4 else 1)
-    return DecodePlan(target, min_chunk, target + batch, tiles, slices, 32 * (tiles * slices + 1))
+    wide = rows > 16           # more than one 16-row tile: the tcgen05 kernel, two resident CTAs per SM (else three)
+    wave = 0 if fp32 else max(1, (sm_count * (2 if wide else 3)) // max(1, kv_heads))
+    overhead = 0 if fp32 else (448 if wide else 128)
+    return DecodePlan(target, min_chunk, target + batch, tiles, slices, 32 * (tiles * slices + 1), wave, overhead,
+                      not fp32)
+
+
+def _round_up(x: int, m: int) -> int:
+    return -(-x // m) * m
+
+
+def _item_tokens(plan: DecodePlan, length: int, n: int, chunk: int) -> int:
+    """Keys per item of a sequence cut into ``n`` items (csrc/decode.cu seq_chunk)."""
+    if not plan.equal_split:
+        return chunk
+    return max(DECODE_TILE_TOKENS, _round_up(-(-length // n), DECODE_TILE_TOKENS))
+
+
+def _pick_chunk(plan: DecodePlan, lens: Sequence[int], target: int):
+    """First of 32 candidates between total / target and twice that with at most ``target`` items:
+    (chunk, items, largest item, found)."""
+    total = sum(lens)
+    base = max(_round_up(-(-total // target), DECODE_TILE_TOKENS), plan.min_chunk)
+    last = None
+    for k in range(32):
+        chunk = _round_up(base + (base * k) // 32, DECODE_TILE_TOKENS)
+        counts = [max(1, -(-n // chunk)) for n in lens]
+        biggest = max([min(n, _item_tokens(plan, n, c, chunk)) for n, c in zip(lens, counts)], default=0)
+        last = (chunk, sum(counts), biggest)
+        if last[1] <= target:
+            return last + (True,)
+    return last + (False,)
 
 
 def decode_chunk_tokens(plan: DecodePlan, lengths: Sequence[int]) -> int:
     """Chunk size the device planner picks for these lengths: the smallest of 32 candidates between
-    total / target_items and twice that which splits the batch into at most target_items items."""
+    total / target_items and twice that which splits the batch into at most target_items items - or, when the
+    batch also fits a single wave of resident CTAs and the estimate favours it (largest item + per-item overhead
+    against the average load of a resident CTA + half an item), the single-wave chunk."""
     lens = [max(0, int(n)) for n in lengths]
     total = sum(lens)
-    base = -(-total // plan.target_items)
-    base = -(-base // DECODE_TILE_TOKENS) * DECODE_TILE_TOKENS
-    base = max(base, plan.min_chunk)
-    chunk = base
-    for k in range(32):
-        chunk = base + (base * k) // 32
-        chunk = -(-chunk // DECODE_TILE_TOKENS) * DECODE_TILE_TOKENS
-        if sum(max(1, -(-n // chunk)) for n in lens) <= plan.target_items:
-            break
+    chunk, items, _, _ = _pick_chunk(plan, lens, plan.target_items)
+    if 0 < plan.wave_items < plan.target_items and items > plan.wave_items:
+        w_chunk, _, w_biggest, found = _pick_chunk(plan, lens, plan.wave_items)
+        if found:
+            several = (total + items * plan.item_overhead) / plan.wave_items + 0.5 * (total / items + plan.item_overhead)
+            if w_biggest + plan.item_overhead < several:
+                chunk = w_chunk
     return chunk
 
 
