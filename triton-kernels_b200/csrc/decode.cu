@@ -105,6 +105,87 @@ __device__ __forceinline__ void poison_rows(float* comb_o, float* comb_ml, int r
 }
 
 // ---------------------------------------------------------------------------
+// Merge of the n_chunks published partials of one (sequence, kv head) into its output rows, by the `nt` threads
+// t = 0 .. nt-1 of the CTA that drew the last ticket: g = max m; O = sum 2^(m-g) acc / sum 2^(m-g) l
+// (kernels/decode.py:186-197).  Leaves the ticket counter at zero for the next call.
+// ---------------------------------------------------------------------------
+template <typename T, int D>
+__device__ __forceinline__ void merge_chunks(const DecodeParams& p, int b, int h, int n_chunks, int item0, T* out,
+                                             int t, int nt) {
+  constexpr int D4 = D / 4;
+  const int R = p.rows;
+  __threadfence();
+  // One pass with a running maximum, two output elements and four chunks per step: the 24 loads of a step do not
+  // depend on each other or on the running state, so they are in flight together (the merge is a chain of L2 round
+  // trips otherwise).
+  constexpr int E = 2;
+  const long long slot0 = static_cast<long long>(item0) * p.kv_heads + h;   // chunk k lives in slot0 + k * kv_heads
+  const int total = R * D4;
+  for (int idx0 = t; idx0 < total; idx0 += nt * E) {
+    int r[E], d4[E];
+    bool live[E];
+    float mg[E], l[E];
+    float4 acc[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      const int idx = idx0 + e * nt;
+      live[e] = idx < total;
+      const int id = live[e] ? idx : idx0;
+      r[e] = id / D4;
+      d4[e] = id - r[e] * D4;
+      mg[e] = -INFINITY;
+      l[e] = 0.f;
+      acc[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int k0 = 0; k0 < n_chunks; k0 += 4) {
+      float mk[E][4], lk[E][4];
+      float4 o[E][4];
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const bool on = k0 + j < n_chunks;
+          const long long s = slot0 + static_cast<long long>(on ? k0 + j : k0) * p.kv_heads;
+          const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (s * R + r[e]) * 2));
+          o[e][j] = __ldcg(reinterpret_cast<const float4*>(p.part_o + (s * R + r[e]) * D + d4[e] * 4));
+          mk[e][j] = on ? ml.x : -INFINITY;
+          lk[e][j] = ml.y;
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float mn = fmaxf(fmaxf(mg[e], fmaxf(mk[e][0], mk[e][1])), fmaxf(mk[e][2], mk[e][3]));
+        const float keep = (mg[e] == -INFINITY) ? 0.f : fast_exp2(mg[e] - mn);
+        acc[e].x *= keep; acc[e].y *= keep; acc[e].z *= keep; acc[e].w *= keep;
+        l[e] *= keep;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float w = (mk[e][j] == -INFINITY) ? 0.f : fast_exp2(mk[e][j] - mn);
+          acc[e].x += w * o[e][j].x; acc[e].y += w * o[e][j].y; acc[e].z += w * o[e][j].z; acc[e].w += w * o[e][j].w;
+          l[e] += w * lk[e][j];
+        }
+        mg[e] = mn;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) {
+      if (!live[e]) continue;
+      const float inv = l[e] > 0.f ? 1.f / l[e] : 0.f;
+      T* dst = out + static_cast<long long>(r[e]) * D + d4[e] * 4;
+      if constexpr (sizeof(T) == 2) {
+        uint2 u;
+        u.x = ElemTraits<T>::pack2(acc[e].x * inv, acc[e].y * inv);
+        u.y = ElemTraits<T>::pack2(acc[e].z * inv, acc[e].w * inv);
+        *reinterpret_cast<uint2*>(dst) = u;
+      } else {
+        *reinterpret_cast<float4*>(dst) = make_float4(acc[e].x * inv, acc[e].y * inv, acc[e].z * inv, acc[e].w * inv);
+      }
+    }
+  }
+  if (t == 0) p.counters[b * p.kv_heads + h] = 0;  // leave the counter ready for the next call
+}
+
+// ---------------------------------------------------------------------------
 // Emit the CTA's combined (m, l, acc) rows, then merge if this CTA is the last
 // of its (sequence, kv head).  `comb_o` is smem [KS][rows_pad][D] fp32,
 // `comb_ml` is smem [KS][rows_pad][2] = (m in log2 units, l).
@@ -158,36 +239,7 @@ __device__ __forceinline__ void emit_and_merge(const DecodeParams& p, int b, int
   if (threadIdx.x == 0) *s_ticket = atomicAdd(p.counters + b * p.kv_heads + h, 1);
   __syncthreads();
   if (*s_ticket != n_chunks - 1) return;
-  __threadfence();
-  for (int idx = threadIdx.x; idx < R * D4; idx += blockDim.x) {
-    const int r = idx / D4, d4 = idx - r * D4;
-    float mg = -INFINITY;
-    for (int k = 0; k < n_chunks; ++k) {
-      const long long s = (static_cast<long long>(item0) + k) * p.kv_heads + h;
-      mg = fmaxf(mg, __ldcg(p.part_ml + (s * R + r) * 2));
-    }
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float l = 0.f;
-    for (int k = 0; k < n_chunks; ++k) {
-      const long long s = (static_cast<long long>(item0) + k) * p.kv_heads + h;
-      const float mk = __ldcg(p.part_ml + (s * R + r) * 2);
-      const float w = (mk == -INFINITY) ? 0.f : fast_exp2(mk - mg);
-      const float4 o = __ldcg(reinterpret_cast<const float4*>(p.part_o + (s * R + r) * D + d4 * 4));
-      acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
-      l += w * __ldcg(p.part_ml + (s * R + r) * 2 + 1);
-    }
-    const float inv = l > 0.f ? 1.f / l : 0.f;
-    T* dst = out + static_cast<long long>(r) * D + d4 * 4;
-    if constexpr (sizeof(T) == 2) {
-      uint2 u;
-      u.x = ElemTraits<T>::pack2(acc.x * inv, acc.y * inv);
-      u.y = ElemTraits<T>::pack2(acc.z * inv, acc.w * inv);
-      *reinterpret_cast<uint2*>(dst) = u;
-    } else {
-      *reinterpret_cast<float4*>(dst) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
-    }
-  }
-  if (threadIdx.x == 0) p.counters[b * p.kv_heads + h] = 0;  // leave the counter ready for the next call
+  merge_chunks<T, D>(p, b, h, n_chunks, item0, out, threadIdx.x, blockDim.x);
 }
 
 // ---------------------------------------------------------------------------
@@ -282,7 +334,8 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     s_carry = 0;
   }
   __syncthreads();
-  if (p.wave_items > 0 && p.wave_items < p.target_items && s_pick_items > p.wave_items) {
+  // (a batch of more sequences than a wave has CTAs cannot fit one: every sequence is at least one item)
+  if (p.wave_items > 0 && p.wave_items < p.target_items && s_pick_items > p.wave_items && p.batch <= p.wave_items) {
     evaluate(p.wave_items);
     __syncthreads();
     if (tid == 0) {
@@ -394,6 +447,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     }
     p.header[1] = chunk;
     p.header[2] = n_items;
+    p.header[3] = 0;          // pairs ready to be merged (tcgen05 kernel)
   }
 }
 
@@ -760,27 +814,65 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
 //
 // With 17..128 rows the warp-level MMA kernel above is bound by shared-memory bandwidth: every K/V fragment is
 // re-read by ldmatrix once per 16-row tile.  Here the rows are padded to one 128-row tcgen05 tile whose A operands
-// live in tensor memory (Q is written there once per CTA, P once per key tile), so shared memory is read exactly
-// once per K/V byte, by the tensor core.  Per 64-key tile: S = Q K^T (TS MMA, 128 x 64 x D) -> the softmax warps
-// (thread = q row, only the warps that hold real rows work) read S from TMEM, mask, keep the running max / sum in
-// the exp2 domain with the lazy 2^8 rescale, write P as packed 16-bit over S -> O += P V (TS MMA, V is the
+// live in tensor memory (Q is written there once per work unit, P once per key tile), so shared memory is read
+// exactly once per K/V byte, by the tensor core.  Per 64-key tile: S = Q K^T (TS MMA, 128 x 64 x D) -> the softmax
+// warps (thread = q row, only the warps that hold real rows work) read S from TMEM, mask, keep the running max / sum
+// in the exp2 domain with the lazy 2^8 rescale, write P as packed 16-bit over S -> O += P V (TS MMA, V is the
 // MN-major B operand).  Two CTAs share an SM (256 TMEM columns, 3 stages of 64 keys each), which overlaps one CTA's
-// softmax with the other's MMAs.  Planner, partials and the ticket merge are shared with the kernels above.
+// softmax with the other's MMAs.
+//
+// The kernel is persistent: the grid is one wave (two CTAs per SM) and CTA j works through the units
+// (item, kv head) j, 2G-1-j, 2G+j, ... of the planner's longest-first list (G = grid size; the back-and-forth order
+// evens out the sizes a CTA gets).  Every role walks that list by itself, so the producer warp runs ahead into the
+// next unit while the last tiles of the current one are still being consumed: the stage ring - the bytes the SM
+// keeps in flight, which is what bounds this kernel - never drains between units, and tensor memory, barriers and
+// tensor maps are set up once per CTA.  For that the epilogue leaves shared memory alone: each softmax thread writes
+// its O row from registers to the output (single-chunk sequences) or to the partials, and the ticket merge runs among
+// the softmax warps.  Planner and partial / ticket formats are shared with the kernels above.
 // ---------------------------------------------------------------------------
 constexpr int kUmmaStages = 3;
 constexpr int kUmmaTmemCols = 256;
+constexpr int kUmmaMaxClaims = 1;     // merges a CTA takes per sweep of the ticket counters in its teardown
+constexpr int kMergeClaimed = 1 << 30; // added to a pair's ticket counter by the CTA that merges it
 
 struct __align__(8) UmmaCtrl {
   uint64_t full[kUmmaStages];
   uint64_t empty[kUmmaStages];
-  uint64_t q_ready;
-  uint64_t s_full;
-  uint64_t p_ready;
-  uint64_t o_done;
+  uint64_t q_ready;   // softmax warps -> MMA warp: the unit's Q rows are in tensor memory
+  uint64_t s_full;    // MMA warp -> softmax warps (commit): S of a tile
+  uint64_t p_ready;   // softmax warps -> MMA warp: P of a tile
+  uint64_t o_done;    // MMA warp -> softmax warps (commit): PV of a tile
+  uint64_t o_free;    // softmax warps -> MMA warp: the finished unit's O has been read out of tensor memory
+  uint64_t rows_out;  // softmax threads: my partial rows of the unit are written and fenced
   uint32_t tmem_base;
-  int ticket;
   int abort_flag;
+  int abort_round;    // first round (unit of this CTA) whose output may be incomplete after a wait ran out
+  int ready;          // teardown: (sequence, kv head) pairs whose chunks are all published and that nobody merges yet
+  int n_reserved;     // teardown: claim attempts of this sweep
+  int n_claimed;      // teardown: pairs this CTA claimed in this sweep
+  int claimed[kUmmaMaxClaims];
 };
+
+// One (work item, kv head) unit as every role of the CTA reads it from the planner's records.
+struct UmmaUnit {
+  long long seq_start;
+  int b, h, c, n_chunks, item0, len, t_begin, t_end, ntiles;
+};
+
+__device__ __forceinline__ UmmaUnit umma_unit(const DecodeParams& p, int u) {
+  UmmaUnit w;
+  const int item = u / p.kv_heads;
+  w.h = u - item * p.kv_heads;
+  const int4 rec0 = __ldg(p.item_info + 2 * item);
+  const int4 rec1 = __ldg(p.item_info + 2 * item + 1);
+  w.b = rec0.x; w.c = rec0.y; w.n_chunks = rec0.z; w.item0 = rec0.w;
+  w.len = rec1.x;
+  w.seq_start = (static_cast<long long>(rec1.w) << 32) | static_cast<unsigned int>(rec1.z);
+  w.t_begin = w.c * rec1.y;                       // rec1.y: keys per item of this sequence
+  w.t_end = min(w.len, w.t_begin + rec1.y);
+  w.ntiles = w.t_end > w.t_begin ? (w.t_end - w.t_begin + kTileN - 1) / kTileN : 0;
+  return w;
+}
 
 template <typename T, int D>
 __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_constant__ CUtensorMap tm_k,
@@ -796,26 +888,12 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
   constexpr int kSCol = kQCols;               // S (64 fp32 columns); P overwrites its first 32
   constexpr int kOCol = kQCols + kTileN;      // O (D fp32 columns)
   static_assert(kOCol + D <= kUmmaTmemCols, "TMEM budget");
-
-  ptx::grid_dep_wait();      // the planner's records are complete and visible from here on
-  const int n_items = p.header[2];
-  const int item = blockIdx.x / p.kv_heads;
-  if (item >= n_items) return;
-  const int h = blockIdx.x - item * p.kv_heads;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int kProducer = 4, kMma = 5;
 
-  const int4 rec0 = __ldg(p.item_info + 2 * item);
-  const int4 rec1 = __ldg(p.item_info + 2 * item + 1);
-  const int b = rec0.x, c = rec0.y, n_chunks = rec0.z, item0 = rec0.w;
-  const int chunk = rec1.y;              // keys per item of this sequence
-  const int len = rec1.x;
-  const long long seq_start = (static_cast<long long>(rec1.w) << 32) | static_cast<unsigned int>(rec1.z);
-  const int t_begin = c * chunk;
-  const int t_end = min(len, t_begin + chunk);
-  const int ntiles = t_end > t_begin ? (t_end - t_begin + kTileN - 1) / kTileN : 0;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int R = p.rows;
   const int active_warps = (R + 31) >> 5;      // softmax warps that own real rows
+  const int n_softmax = active_warps * 32;
 
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   UmmaCtrl* ctrl = reinterpret_cast<UmmaCtrl*>(smem + kUmmaStages * STAGE_BYTES);
@@ -823,11 +901,14 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
 
   if (tid == 0) {
     for (int i = 0; i < kUmmaStages; ++i) { mbar_init(smem_u32(&ctrl->full[i]), 1); mbar_init(smem_u32(&ctrl->empty[i]), 1); }
-    mbar_init(smem_u32(&ctrl->q_ready), active_warps * 32);
+    mbar_init(smem_u32(&ctrl->q_ready), n_softmax);
     mbar_init(smem_u32(&ctrl->s_full), 1);
-    mbar_init(smem_u32(&ctrl->p_ready), active_warps * 32);
+    mbar_init(smem_u32(&ctrl->p_ready), n_softmax);
     mbar_init(smem_u32(&ctrl->o_done), 1);
+    mbar_init(smem_u32(&ctrl->o_free), n_softmax);
+    mbar_init(smem_u32(&ctrl->rows_out), n_softmax);
     ctrl->abort_flag = 0;
+    ctrl->abort_round = 0x7fffffff;
     mbar_fence_init();
   }
   if (warp == kMma) {
@@ -840,81 +921,90 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
   const uint32_t tmem = ctrl->tmem_base;
   volatile int* abort_flag = &ctrl->abort_flag;
 
-  // per-row softmax state of the softmax threads (row = tid)
-  float m_used = -INFINITY, l_run = 0.f;
+  ptx::grid_dep_wait();      // the planner's records are complete and visible from here on
+  const int n_units = p.header[2] * p.kv_heads;
+  const int G = static_cast<int>(gridDim.x), me = static_cast<int>(blockIdx.x);
+  // unit of this CTA in round r (out of range = the CTA is done: later rounds are out of range too)
+  auto unit_index = [&](int r) { return r * G + ((r & 1) ? G - 1 - me : me); };
 
   if (warp == kProducer) {
     // =========================== TMA producer ===========================
     if (lane == 0) { prefetch_tensormap(&tm_k); prefetch_tensormap(&tm_v); }
-    int h_coord = h;
-    long long row0 = seq_start;
-    if (p.layout == B200ATTN_DENSE) { h_coord = 0; row0 = (static_cast<long long>(b) * p.kv_heads + h) * p.max_kv; }
     bool ok = true;
-    int issued = 0;
+    int g = 0;                                   // tiles issued so far, over all units
     const int box_rows = 1 << p.box_shift;
-    for (int tile = 0; tile < ntiles; ++tile) {
-      const int stage = tile % kUmmaStages, use = tile / kUmmaStages;
-      if (use > 0) {
-        ok = warp_wait(smem_u32(&ctrl->empty[stage]), (use - 1) & 1);
-        if (!ok || *abort_flag) { ok = false; break; }
-      }
-      const int t0 = t_begin + tile * kTileN;
-      const uint32_t kdst = smem_base + stage * STAGE_BYTES;
-      const uint32_t vdst = kdst + TILE_BYTES;
-      const uint32_t bar = smem_u32(&ctrl->full[stage]);
-      if (p.layout != B200ATTN_PAGED) {
-        if (lane == 0) {
-          mbar_arrive_expect_tx(bar, STAGE_BYTES);
-          const int row = static_cast<int>(row0 + t0);
-#pragma unroll
-          for (int cc = 0; cc < CHUNKS; ++cc) {
-            tma_load_3d(kdst + cc * CHUNK_BYTES, &tm_k, bar, cc * 64, h_coord, row);
-            tma_load_3d(vdst + cc * CHUNK_BYTES, &tm_v, bar, cc * 64, h_coord, row);
-          }
+    for (int r = 0; ok; ++r) {
+      const int u = unit_index(r);
+      if (u >= n_units) break;
+      const UmmaUnit w = umma_unit(p, u);
+      int h_coord = w.h;
+      long long row0 = w.seq_start;
+      if (p.layout == B200ATTN_DENSE) { h_coord = 0; row0 = (static_cast<long long>(w.b) * p.kv_heads + w.h) * p.max_kv; }
+      for (int tile = 0; tile < w.ntiles; ++tile) {
+        const int stage = g % kUmmaStages, use = g / kUmmaStages;
+        if (use > 0) {
+          ok = warp_wait(smem_u32(&ctrl->empty[stage]), (use - 1) & 1);
+          if (!ok || *abort_flag) { ok = false; break; }
         }
-      } else {
-        const int boxes = kTileN >> p.box_shift;
-        const int* ktab = p.k_table + static_cast<long long>(b) * p.table_stride;
-        const int* vtab = p.v_table + static_cast<long long>(b) * p.table_stride;
-        int krow[2], vrow[2];
-        int count = 0, n = 0;
-        for (int i = lane; i < boxes; i += 32, ++n) {
-          const int t = t0 + i * box_rows;
-          int kr = -1, vr = -1;
-          if (t < t_end) {
-            int lp, off;
-            if (p.page_shift >= 0) { lp = t >> p.page_shift; off = t & (p.page_size - 1); }
-            else { lp = t / p.page_size; off = t - lp * p.page_size; }
-            const int kp = __ldg(ktab + lp), vp = __ldg(vtab + lp);
-            // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
-            const bool kbad = kp < 0 || kp >= p.num_pages, vbad = vp < 0 || vp >= p.num_pages;
-            if (kbad || vbad) p.header[0] = DEV_ERR_PAGE_RANGE;
-            if (p.num_pages > 0) {
-              kr = (kbad ? 0 : kp) * p.page_size + off;
-              vr = (vbad ? 0 : vp) * p.page_size + off;
+        const int t0 = w.t_begin + tile * kTileN;
+        const uint32_t kdst = smem_base + stage * STAGE_BYTES;
+        const uint32_t vdst = kdst + TILE_BYTES;
+        const uint32_t bar = smem_u32(&ctrl->full[stage]);
+        if (p.layout != B200ATTN_PAGED) {
+          if (lane == 0) {
+            mbar_arrive_expect_tx(bar, STAGE_BYTES);
+            const int row = static_cast<int>(row0 + t0);
+#pragma unroll
+            for (int cc = 0; cc < CHUNKS; ++cc) {
+              tma_load_3d(kdst + cc * CHUNK_BYTES, &tm_k, bar, cc * 64, h_coord, row);
+              tma_load_3d(vdst + cc * CHUNK_BYTES, &tm_v, bar, cc * 64, h_coord, row);
             }
           }
-          krow[n] = kr; vrow[n] = vr;
-          count += (kr >= 0) + (vr >= 0);
-        }
-        for (int off = 16; off > 0; off >>= 1) count += __shfl_xor_sync(0xffffffffu, count, off);
-        if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * box_rows * 128 * CHUNKS);
-        __syncwarp();
-        n = 0;
-        for (int i = lane; i < boxes; i += 32, ++n) {
-          const uint32_t roff = static_cast<uint32_t>(i) * box_rows * 128;
+        } else {
+          const int boxes = kTileN >> p.box_shift;
+          const int* ktab = p.k_table + static_cast<long long>(w.b) * p.table_stride;
+          const int* vtab = p.v_table + static_cast<long long>(w.b) * p.table_stride;
+          int krow[2], vrow[2];
+          int count = 0, n = 0;
+          for (int i = lane; i < boxes; i += 32, ++n) {
+            const int t = t0 + i * box_rows;
+            int kr = -1, vr = -1;
+            if (t < w.t_end) {
+              int lp, off;
+              if (p.page_shift >= 0) { lp = t >> p.page_shift; off = t & (p.page_size - 1); }
+              else { lp = t / p.page_size; off = t - lp * p.page_size; }
+              const int kp = __ldg(ktab + lp), vp = __ldg(vtab + lp);
+              // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
+              const bool kbad = kp < 0 || kp >= p.num_pages, vbad = vp < 0 || vp >= p.num_pages;
+              if (kbad || vbad) p.header[0] = DEV_ERR_PAGE_RANGE;
+              if (p.num_pages > 0) {
+                kr = (kbad ? 0 : kp) * p.page_size + off;
+                vr = (vbad ? 0 : vp) * p.page_size + off;
+              }
+            }
+            krow[n] = kr; vrow[n] = vr;
+            count += (kr >= 0) + (vr >= 0);
+          }
+          for (int off = 16; off > 0; off >>= 1) count += __shfl_xor_sync(0xffffffffu, count, off);
+          if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * box_rows * 128 * CHUNKS);
+          __syncwarp();
+          n = 0;
+          for (int i = lane; i < boxes; i += 32, ++n) {
+            const uint32_t roff = static_cast<uint32_t>(i) * box_rows * 128;
 #pragma unroll
-          for (int cc = 0; cc < CHUNKS; ++cc) {
-            if (krow[n] >= 0) tma_load_3d(kdst + cc * CHUNK_BYTES + roff, &tm_k, bar, cc * 64, h_coord, krow[n]);
-            if (vrow[n] >= 0) tma_load_3d(vdst + cc * CHUNK_BYTES + roff, &tm_v, bar, cc * 64, h_coord, vrow[n]);
+            for (int cc = 0; cc < CHUNKS; ++cc) {
+              if (krow[n] >= 0) tma_load_3d(kdst + cc * CHUNK_BYTES + roff, &tm_k, bar, cc * 64, h_coord, krow[n]);
+              if (vrow[n] >= 0) tma_load_3d(vdst + cc * CHUNK_BYTES + roff, &tm_v, bar, cc * 64, h_coord, vrow[n]);
+            }
           }
         }
+        ++g;
       }
-      issued = tile + 1;
     }
     if (!ok) {
       if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
-      for (int t = max(0, issued - kUmmaStages); t < issued; ++t)
+      // bounded drain of the copies still in flight before the CTA may exit
+      for (int t = max(0, g - kUmmaStages); t < g; ++t)
         mbar_wait(smem_u32(&ctrl->full[t % kUmmaStages]), (t / kUmmaStages) & 1);
     }
   } else if (warp == kMma) {
@@ -924,181 +1014,312 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     constexpr uint32_t idesc_o = make_idesc_f16(128, D, kFmt, 1);
     const uint64_t kdesc = make_smem_desc_sw128(smem_base, 16);
     const uint64_t vdesc = make_smem_desc_sw128(smem_base, CHUNK_BYTES);
-    bool ok = ntiles == 0 || warp_wait(smem_u32(&ctrl->q_ready), 0);
     // The warp stays converged while it issues (every lane runs the descriptor arithmetic, one elected lane issues
     // the tensor-core instructions and their commits): a divergent single-lane issuer loses most of its issue slots
     // to busy neighbouring warps.
     const uint32_t lead = elect_one();
-    auto issue_s = [&](int tile) {
-      const uint64_t kb = kdesc + static_cast<uint64_t>(((tile % kUmmaStages) * STAGE_BYTES) >> 4);
+    auto issue_s = [&](int gi) {
+      const uint64_t kb = kdesc + static_cast<uint64_t>(((gi % kUmmaStages) * STAGE_BYTES) >> 4);
       mma_ts_kmajor_batch<D / 16, (CHUNK_BYTES >> 4)>(tmem + kSCol, tmem, kb, idesc_s, 0u, lead);
       mma_commit_lead(smem_u32(&ctrl->s_full), lead);
     };
-    if (ok && ntiles > 0) {
-      ok = warp_wait(smem_u32(&ctrl->full[0]), 0);
-      if (ok) { tc_fence_after(); issue_s(0); }
-    }
-    for (int tile = 0; tile < ntiles && ok; ++tile) {
-      const int stage = tile % kUmmaStages;
-      // what does not depend on the softmax warps comes before the wait for their P: the next K tile (loaded long
-      // ago in steady state), the zero fill of V rows past the end, the operand descriptor
-      if (tile + 1 < ntiles) {
-        ok = warp_wait(smem_u32(&ctrl->full[(tile + 1) % kUmmaStages]), ((tile + 1) / kUmmaStages) & 1);
-        if (!ok) break;
+    bool ok = true;
+    int g = 0;                                   // tiles consumed so far, over all units
+    for (int r = 0; ok; ++r) {
+      const int u = unit_index(r);
+      if (u >= n_units) break;
+      const UmmaUnit w = umma_unit(p, u);
+      ok = warp_wait(smem_u32(&ctrl->q_ready), r & 1);
+      if (!ok || *abort_flag) { ok = false; break; }
+      if (w.ntiles == 0) {
+        // nothing to multiply; keep the o_free phase in step (the softmax warps arrive once per unit)
+        if (r > 0) ok = warp_wait(smem_u32(&ctrl->o_free), (r - 1) & 1);
+        continue;
       }
-      const int valid = len - (t_begin + tile * kTileN);
-      if (valid < kTileN) {
-        // keys past the sequence end carry P == 0 but their V rows may hold anything: zero them so 0 * x stays 0
-        // (the stage is complete: its K half was consumed by S(tile))
-        unsigned char* vbuf = smem + stage * STAGE_BYTES + TILE_BYTES;
-        const int first = valid > 0 ? valid : 0;
-        const int n16 = (kTileN - first) * 8;
-        for (int cc = 0; cc < CHUNKS; ++cc) {
-          uint4* dst = reinterpret_cast<uint4*>(vbuf + cc * CHUNK_BYTES + first * 128);
-          for (int i = lane; i < n16; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-      }
-      const uint64_t vb = vdesc + static_cast<uint64_t>((stage * STAGE_BYTES + TILE_BYTES) >> 4);
-      ok = warp_wait(smem_u32(&ctrl->p_ready), tile & 1);
+      ok = warp_wait(smem_u32(&ctrl->full[g % kUmmaStages]), (g / kUmmaStages) & 1);
       if (!ok) break;
       tc_fence_after();
-      mma_ts_batch4(tmem + kOCol, tmem + kSCol, vb, idesc_o, tile > 0 ? 1u : 0u, lead);
-      mma_commit_lead(smem_u32(&ctrl->o_done), lead);
-      if (tile + 1 < ntiles) issue_s(tile + 1);
-      // K_tile was read by S(tile) (complete: its P has come back) and V_tile by the PV just issued
-      mma_commit_lead(smem_u32(&ctrl->empty[stage]), lead);
+      issue_s(g);
+      for (int tile = 0; tile < w.ntiles && ok; ++tile, ++g) {
+        const int stage = g % kUmmaStages;
+        // what does not depend on the softmax warps comes before the wait for their P: the next K tile (loaded long
+        // ago in steady state), the zero fill of V rows past the end, the operand descriptor
+        if (tile + 1 < w.ntiles) {
+          ok = warp_wait(smem_u32(&ctrl->full[(g + 1) % kUmmaStages]), ((g + 1) / kUmmaStages) & 1);
+          if (!ok) break;
+        }
+        const int valid = w.len - (w.t_begin + tile * kTileN);
+        if (valid < kTileN) {
+          // keys past the sequence end carry P == 0 but their V rows may hold anything: zero them so 0 * x stays 0
+          // (the stage is complete: its K half was consumed by S(tile))
+          unsigned char* vbuf = smem + stage * STAGE_BYTES + TILE_BYTES;
+          const int first = valid > 0 ? valid : 0;
+          const int n16 = (kTileN - first) * 8;
+          for (int cc = 0; cc < CHUNKS; ++cc) {
+            uint4* dst = reinterpret_cast<uint4*>(vbuf + cc * CHUNK_BYTES + first * 128);
+            for (int i = lane; i < n16; i += 32) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+        }
+        const uint64_t vb = vdesc + static_cast<uint64_t>((stage * STAGE_BYTES + TILE_BYTES) >> 4);
+        ok = warp_wait(smem_u32(&ctrl->p_ready), g & 1);
+        if (!ok) break;
+        if (tile == 0 && r > 0) {
+          // this PV starts a new accumulator: the previous unit's O must have left tensor memory
+          ok = warp_wait(smem_u32(&ctrl->o_free), (r - 1) & 1);
+          if (!ok) break;
+        }
+        tc_fence_after();
+        mma_ts_batch4(tmem + kOCol, tmem + kSCol, vb, idesc_o, tile > 0 ? 1u : 0u, lead);
+        mma_commit_lead(smem_u32(&ctrl->o_done), lead);
+        if (tile + 1 < w.ntiles) issue_s(g + 1);
+        // K_tile was read by S(tile) (complete: its P has come back) and V_tile by the PV just issued
+        mma_commit_lead(smem_u32(&ctrl->empty[stage]), lead);
+      }
     }
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
   } else if (warp < active_warps) {
     // =========================== softmax warps: thread = q row ===========================
     const int row = tid;
     const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
-    // Q row -> TMEM as the packed 16-bit A operand (rows past R are zero)
-    {
-      const T* qg = static_cast<const T*>(p.q) +
-                    ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
+    const float sl2 = p.scale_log2;
+    const uint32_t tS = tmem + lane_off + kSCol;
+    const uint32_t tO = tmem + lane_off + kOCol;
+    bool ok = true;
+    int g = 0;                                   // tiles consumed so far, over all units
+    int merges = 0;                              // units of this CTA that went through the ticket (barrier phases)
+    int r = 0;
+    auto rows_of = [&](const UmmaUnit& w) {
+      return (static_cast<long long>(w.b) * p.q_heads + static_cast<long long>(w.h) * p.head_stride + p.head0) * p.q_len;
+    };
+    // Q row -> TMEM as the packed 16-bit A operand (rows past R are zero).  Called when the S MMAs of the unit before
+    // have all completed (this warp has consumed their last score tile), i.e. before that unit's epilogue, so that
+    // the MMA warp can start on the next unit while the rows of the finished one are written out.
+    auto write_q = [&](int unit) {
+      if (unit >= n_units) return;
+      const UmmaUnit w = umma_unit(p, unit);
+      const T* qg = static_cast<const T*>(p.q) + rows_of(w) * D;
 #pragma unroll
       for (int cc = 0; cc < kQCols / 32; ++cc) {
         uint32_t qv[32];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          uint4 u = make_uint4(0u, 0u, 0u, 0u);
-          if (row < R) u = __ldg(reinterpret_cast<const uint4*>(qg + static_cast<long long>(row) * D) + cc * 8 + i);
-          qv[i * 4 + 0] = u.x; qv[i * 4 + 1] = u.y; qv[i * 4 + 2] = u.z; qv[i * 4 + 3] = u.w;
+          uint4 x = make_uint4(0u, 0u, 0u, 0u);
+          if (row < R) x = __ldg(reinterpret_cast<const uint4*>(qg + static_cast<long long>(row) * D) + cc * 8 + i);
+          qv[i * 4 + 0] = x.x; qv[i * 4 + 1] = x.y; qv[i * 4 + 2] = x.z; qv[i * 4 + 3] = x.w;
         }
         tmem_st32(tmem + lane_off + cc * 32, qv);
       }
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(smem_u32(&ctrl->q_ready));
-    }
-    int lim = len - 1;                                   // last visible key of this row
-    if (p.causal) lim = len - p.q_len + (row % p.q_len);
-    const float sl2 = p.scale_log2;
-    const uint32_t tS = tmem + lane_off + kSCol;
-    const uint32_t tO = tmem + lane_off + kOCol;
-    bool ok = true;
-    for (int tile = 0; tile < ntiles; ++tile) {
-      ok = warp_wait(smem_u32(&ctrl->s_full), tile & 1);
-      if (!ok || *abort_flag) { ok = false; break; }
-      tc_fence_after();
-      const int limit = lim - (t_begin + tile * kTileN);   // columns 0..limit of this tile are visible
-      uint32_t ca[32], cb[32];
-      tmem_ld32(tS, ca);
-      tmem_ld32(tS + 32, cb);
-      tmem_wait_ld();
-      if (limit < kTileN - 1) {
+    };
+    write_q(unit_index(0));
+    for (; ok; ++r) {
+      const int u = unit_index(r);
+      if (u >= n_units) break;
+      const UmmaUnit w = umma_unit(p, u);
+      const long long row_base = rows_of(w);
+      float m_used = -INFINITY, l_run = 0.f;               // per-row softmax state
+      int lim = w.len - 1;                                 // last visible key of this row
+      if (p.causal) lim = w.len - p.q_len + (row % p.q_len);
+      for (int tile = 0; tile < w.ntiles; ++tile, ++g) {
+        ok = warp_wait(smem_u32(&ctrl->s_full), g & 1);
+        if (!ok || *abort_flag) { ok = false; break; }
+        tc_fence_after();
+        const int limit = lim - (w.t_begin + tile * kTileN);   // columns 0..limit of this tile are visible
+        uint32_t ca[32], cb[32];
+        tmem_ld32(tS, ca);
+        tmem_ld32(tS + 32, cb);
+        tmem_wait_ld();
+        if (limit < kTileN - 1) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (i > limit) ca[i] = 0xff800000u;          // -inf
-          if (32 + i > limit) cb[i] = 0xff800000u;
+          for (int i = 0; i < 32; ++i) {
+            if (i > limit) ca[i] = 0xff800000u;          // -inf
+            if (32 + i > limit) cb[i] = 0xff800000u;
+          }
         }
-      }
-      float ma = max3(__uint_as_float(ca[0]), __uint_as_float(ca[1]), __uint_as_float(ca[2]));
-      float mb = max3(__uint_as_float(cb[0]), __uint_as_float(cb[1]), __uint_as_float(cb[2]));
+        float ma = max3(__uint_as_float(ca[0]), __uint_as_float(ca[1]), __uint_as_float(ca[2]));
+        float mb = max3(__uint_as_float(cb[0]), __uint_as_float(cb[1]), __uint_as_float(cb[2]));
 #pragma unroll
-      for (int i = 3; i + 1 < 32; i += 2) {
-        ma = max3(ma, __uint_as_float(ca[i]), __uint_as_float(ca[i + 1]));
-        mb = max3(mb, __uint_as_float(cb[i]), __uint_as_float(cb[i + 1]));
+        for (int i = 3; i + 1 < 32; i += 2) {
+          ma = max3(ma, __uint_as_float(ca[i]), __uint_as_float(ca[i + 1]));
+          mb = max3(mb, __uint_as_float(cb[i]), __uint_as_float(cb[i + 1]));
+        }
+        const float mx = max3(ma, mb, fmaxf(__uint_as_float(ca[31]), __uint_as_float(cb[31]))) * sl2;
+        const bool need = (mx - m_used) > 8.f;
+        float alpha = 1.f;
+        if (need) { alpha = fast_exp2(m_used - mx); m_used = mx; l_run *= alpha; }
+        if (tile > 0 && __any_sync(0xffffffffu, need)) {
+          // PV(tile-1) has completed once S(tile) is visible (MMAs complete in issue order); the wait is immediate
+          ok = warp_wait(smem_u32(&ctrl->o_done), (g - 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int cc = 0; cc < D / 32; ++cc) {
+            uint32_t ov[32];
+            tmem_ld32(tO + cc * 32, ov);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            tmem_st32(tO + cc * 32, ov);
+          }
+        }
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        float rs = 0.f;
+        uint32_t pk[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p0 = fast_exp2(fmaf(__uint_as_float(ca[2 * i]), sl2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(ca[2 * i + 1]), sl2, neg_m));
+          const float p2 = fast_exp2(fmaf(__uint_as_float(cb[2 * i]), sl2, neg_m));
+          const float p3 = fast_exp2(fmaf(__uint_as_float(cb[2 * i + 1]), sl2, neg_m));
+          rs += (p0 + p1) + (p2 + p3);
+          pk[i] = ElemTraits<T>::pack2(p0, p1);
+          pk[16 + i] = ElemTraits<T>::pack2(p2, p3);
+        }
+        l_run += rs;
+        tmem_st32(tS, pk);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(smem_u32(&ctrl->p_ready));
       }
-      const float mx = max3(ma, mb, fmaxf(__uint_as_float(ca[31]), __uint_as_float(cb[31]))) * sl2;
-      const bool need = (mx - m_used) > 8.f;
-      float alpha = 1.f;
-      if (need) { alpha = fast_exp2(m_used - mx); m_used = mx; l_run *= alpha; }
-      if (tile > 0 && __any_sync(0xffffffffu, need)) {
-        // PV(tile-1) has completed once S(tile) is visible (MMAs complete in issue order); the wait is immediate
-        ok = warp_wait(smem_u32(&ctrl->o_done), (tile - 1) & 1);
+      if (!ok) break;
+      write_q(unit_index(r + 1));
+      // ---------------- the unit's rows leave tensor memory ----------------
+      if (w.ntiles > 0) {
+        ok = warp_wait(smem_u32(&ctrl->o_done), (g - 1) & 1);
         if (!ok) break;
         tc_fence_after();
+      }
+      const bool single = w.n_chunks == 1;
+      const long long slot = (static_cast<long long>(w.item0) + w.c) * p.kv_heads + w.h;
+      T* out = static_cast<T*>(p.out) + row_base * D;
+      const float inv = single ? (l_run > 0.f ? 1.f / l_run : 0.f) : 1.f;
 #pragma unroll
-        for (int cc = 0; cc < D / 32; ++cc) {
-          uint32_t ov[32];
+      for (int cc = 0; cc < D / 32; ++cc) {
+        uint32_t ov[32];
+        if (w.ntiles > 0) {
           tmem_ld32(tO + cc * 32, ov);
           tmem_wait_ld();
+        } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-          tmem_st32(tO + cc * 32, ov);
+          for (int i = 0; i < 32; ++i) ov[i] = 0u;
+        }
+        if (cc == D / 32 - 1) {
+          // O is in registers: the MMA warp may start the next unit's accumulator
+          tc_fence_before();
+          mbar_arrive(smem_u32(&ctrl->o_free));
+        }
+        if (row < R) {
+          if (single) {
+            if constexpr (sizeof(T) == 2) {
+              uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(row) * D + cc * 32);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 x;
+                x.x = ElemTraits<T>::pack2(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+                x.y = ElemTraits<T>::pack2(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+                x.z = ElemTraits<T>::pack2(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+                x.w = ElemTraits<T>::pack2(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+                dst[i] = x;
+              }
+            }
+          } else {
+            float4* dst = reinterpret_cast<float4*>(p.part_o + (slot * R + row) * D + cc * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(ov[4 * i]), __uint_as_float(ov[4 * i + 1]),
+                                   __uint_as_float(ov[4 * i + 2]), __uint_as_float(ov[4 * i + 3]));
+          }
         }
       }
-      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      float rs = 0.f;
-      uint32_t pk[32];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(ca[2 * i]), sl2, neg_m));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(ca[2 * i + 1]), sl2, neg_m));
-        const float p2 = fast_exp2(fmaf(__uint_as_float(cb[2 * i]), sl2, neg_m));
-        const float p3 = fast_exp2(fmaf(__uint_as_float(cb[2 * i + 1]), sl2, neg_m));
-        rs += (p0 + p1) + (p2 + p3);
-        pk[i] = ElemTraits<T>::pack2(p0, p1);
-        pk[16 + i] = ElemTraits<T>::pack2(p2, p3);
-      }
-      l_run += rs;
-      tmem_st32(tS, pk);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(smem_u32(&ctrl->p_ready));
-    }
-    if (ok && ntiles > 0) ok = warp_wait(smem_u32(&ctrl->o_done), (ntiles - 1) & 1);
-    if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
-  }
-  __syncthreads();   // every tile consumed (or the CTA gave up): the stage ring is free for the row exchange
-  // O rows (fp32, un-normalised) and (m, l) -> shared memory, then the common emit / ticket merge
-  float* comb_o = reinterpret_cast<float*>(smem);
-  float* comb_ml = comb_o + static_cast<size_t>(R) * D;
-  const bool aborted = ctrl->abort_flag != 0;
-  if (aborted) {
-    // see decode_mma_kernel: emit NaN rows and still take the ticket
-    poison_rows(comb_o, comb_ml, R, D);
-  } else if (warp < active_warps) {
-    const int row = tid;
-    tc_fence_after();
-    const uint32_t tO = tmem + (static_cast<uint32_t>(warp * 32) << 16) + kOCol;
-#pragma unroll
-    for (int cc = 0; cc < D / 32; ++cc) {
-      uint32_t ov[32];
-      if (ntiles > 0) {
-        tmem_ld32(tO + cc * 32, ov);
-        tmem_wait_ld();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) ov[i] = 0u;
-      }
-      if (row < R) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          *reinterpret_cast<uint4*>(comb_o + static_cast<size_t>(row) * D + cc * 32 + i * 4) =
-              make_uint4(ov[i * 4], ov[i * 4 + 1], ov[i * 4 + 2], ov[i * 4 + 3]);
+      if (!single) {
+        if (row < R) {
+          p.part_ml[(slot * R + row) * 2] = m_used;
+          p.part_ml[(slot * R + row) * 2 + 1] = l_run;
+        }
+        // Publish the partial and draw the pair's ticket.  Nobody merges here: the merge is left to the teardown of
+        // whichever CTA gets to it first (see there), so the softmax warps go straight on to their next unit.  The
+        // softmax threads meet on an mbarrier with a bounded wait, never on bar.sync: a warp that gave up must not
+        // hang the rest.
+        __threadfence();
+        mbar_arrive(smem_u32(&ctrl->rows_out));
+        if (tid == 0) {
+          if (mbar_wait(smem_u32(&ctrl->rows_out), merges & 1)) {
+            __threadfence();
+            const int ticket = atomicAdd(p.counters + w.b * p.kv_heads + w.h, 1);
+            if (ticket == w.n_chunks - 1) atomicAdd(p.header + 3, 1);     // one more pair ready to be merged
+          } else {
+            p.header[0] = DEV_ERR_WAIT_EXPIRED;
+            *abort_flag = 1;
+          }
+        }
+        ++merges;
       }
     }
-    if (row < R) { comb_ml[row * 2] = m_used; comb_ml[row * 2 + 1] = l_run; }
+    if (!ok) {
+      atomicMin(&ctrl->abort_round, r);
+      if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
+    }
   }
+  // ---------------- teardown ----------------
   tc_fence_before();
   __syncthreads();
   if (warp == kMma) { tc_fence_after(); tmem_dealloc(tmem, kUmmaTmemCols); }
-  emit_and_merge<T, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, 1, R, &ctrl->ticket);
+  // Merges.  A (sequence, kv head) pair whose chunks have all drawn their tickets is merged by whichever CTA claims
+  // it while sweeping the ticket counters here, with all of its threads: CTAs that finish early take the pairs that
+  // are ready, the CTA that publishes a pair's last chunk sweeps after it did, so every pair is merged by the time
+  // the last CTA leaves, and no CTA waits for another.  header[3] counts the ready, unclaimed pairs.
+  if (!ctrl->abort_flag) {
+    const int n_pairs = p.batch * p.kv_heads;
+    for (int sweep = 0; sweep < n_pairs + 64; ++sweep) {
+      if (tid == 0) {
+        ctrl->ready = *reinterpret_cast<volatile int*>(p.header + 3);
+        ctrl->n_reserved = 0;
+        ctrl->n_claimed = 0;
+      }
+      __syncthreads();
+      if (ctrl->ready <= 0) break;
+      for (int e = tid; e < n_pairs; e += static_cast<int>(blockDim.x)) {
+        const int pair = (e + me * 61) % n_pairs;            // CTAs start their sweeps at different pairs
+        const int b = pair / p.kv_heads;
+        const int n = p.item_start[b + 1] - p.item_start[b];
+        if (n > 1 && *reinterpret_cast<volatile int*>(p.counters + pair) == n &&
+            atomicAdd(&ctrl->n_reserved, 1) < kUmmaMaxClaims &&
+            atomicCAS(p.counters + pair, n, n + kMergeClaimed) == n) {
+          atomicSub(p.header + 3, 1);
+          ctrl->claimed[atomicAdd(&ctrl->n_claimed, 1)] = pair;
+        }
+      }
+      __syncthreads();
+      const int n_claimed = ctrl->n_claimed;
+      for (int i = 0; i < n_claimed; ++i) {
+        const int pair = ctrl->claimed[i];
+        const int b = pair / p.kv_heads, h = pair - b * p.kv_heads;
+        const int item0 = b == 0 ? 0 : p.item_start[b];
+        T* out = static_cast<T*>(p.out) +
+                 ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
+        merge_chunks<T, D>(p, b, h, p.item_start[b + 1] - item0, item0, out, tid, static_cast<int>(blockDim.x));
+      }
+      __syncthreads();
+    }
+  }
+  if (ctrl->abort_flag) {
+    // A bounded wait ran out: the rows of the unit the softmax warps were in, and of the units this CTA had not
+    // reached, are unknown.  They are filled with NaN (and their tickets are not drawn, so nobody merges over them):
+    // the failure shows in the output as well as in the error word.
+    const T nan_t = ElemTraits<T>::from_float(__int_as_float(0x7fc00000));
+    for (int r = ctrl->abort_round; r != 0x7fffffff; ++r) {
+      const int u = unit_index(r);
+      if (u >= n_units) break;
+      const UmmaUnit w = umma_unit(p, u);
+      T* out = static_cast<T*>(p.out) +
+               ((static_cast<long long>(w.b) * p.q_heads + static_cast<long long>(w.h) * p.head_stride + p.head0) * p.q_len) * D;
+      for (int i = tid; i < R * D; i += blockDim.x) out[i] = nan_t;
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1349,8 +1570,10 @@ int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream
     if ((rc = make_token_map(&tk, a.dtype, a.k, tokens, heads, D, box))) return rc;
     if ((rc = make_token_map(&tv, a.dtype, a.v, tokens, heads, D, box))) return rc;
     const size_t stage_bytes = static_cast<size_t>(kUmmaStages) * 2 * kTileN * D * 2;
-    const size_t comb_bytes = sizeof(float) * static_cast<size_t>(p.rows) * (D + 2);
-    const size_t smem = 1024 + std::max(stage_bytes, comb_bytes) + sizeof(UmmaCtrl);
+    const size_t smem = 1024 + stage_bytes + sizeof(UmmaCtrl);
+    // persistent: one wave of two CTAs per SM walks the unit list (fewer CTAs when the list cannot be longer)
+    const unsigned wave = 2u * static_cast<unsigned>(sm_count);
+    const dim3 grid(std::min(static_cast<unsigned>(w.max_items) * a.kv_heads, wave), 1);
 #define B200ATTN_LAUNCH_UMMA(TYPE, DIM)                                  \
     do {                                                                 \
       rc = set_smem(decode_umma_kernel<TYPE, DIM>, smem);                \
