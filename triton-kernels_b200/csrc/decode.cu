@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     }
     p.header[1] = chunk;
     p.header[2] = n_items;
-    p.header[3] = 0;          // pairs ready to be merged (tcgen05 kernel)
+    p.header[3] = 0;          // tickets drawn and not merged yet (tcgen05 kernel)
   }
 }
 
@@ -1096,9 +1096,8 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     // Q row -> TMEM as the packed 16-bit A operand (rows past R are zero).  Called when the S MMAs of the unit before
     // have all completed (this warp has consumed their last score tile), i.e. before that unit's epilogue, so that
     // the MMA warp can start on the next unit while the rows of the finished one are written out.
-    auto write_q = [&](int unit) {
+    auto write_q = [&](int unit, const UmmaUnit& w) {
       if (unit >= n_units) return;
-      const UmmaUnit w = umma_unit(p, unit);
       const T* qg = static_cast<const T*>(p.q) + rows_of(w) * D;
 #pragma unroll
       for (int cc = 0; cc < kQCols / 32; ++cc) {
@@ -1115,11 +1114,37 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
       tc_fence_before();
       mbar_arrive(smem_u32(&ctrl->q_ready));
     };
-    write_q(unit_index(0));
+    // The ticket of a unit's pair is drawn by thread 0 one unit later (or in the teardown): by then the barrier that
+    // says "all rows are written" completed long ago and the fence before the ticket has nothing left to wait for.
+    int owed_pair = -1, owed_round = 0;          // thread 0: pair whose ticket is still to be drawn, and its unit's round
+    auto draw_owed_ticket = [&]() {
+      if (tid != 0 || owed_pair < 0) return;
+      if (mbar_wait(smem_u32(&ctrl->rows_out), (merges - 1) & 1)) {
+        __threadfence();                         // the rows the other softmax threads wrote before they arrived, too
+        atomicAdd(p.counters + owed_pair, 1);
+        atomicAdd(p.header + 3, 1);              // tickets drawn and not merged yet (a hint for the teardown)
+      } else {
+        p.header[0] = DEV_ERR_WAIT_EXPIRED;
+        *abort_flag = 1;
+      }
+      owed_pair = -1;
+    };
+    UmmaUnit w = umma_unit(p, min(unit_index(0), max(n_units - 1, 0)));
+    write_q(unit_index(0), w);
     for (; ok; ++r) {
       const int u = unit_index(r);
       if (u >= n_units) break;
-      const UmmaUnit w = umma_unit(p, u);
+      // the next unit's record is read now, and its Q row pulled into L2, so that neither is waited for at the hand-over
+      const int u_next = unit_index(r + 1);
+      UmmaUnit w_next = w;
+      if (u_next < n_units) {
+        w_next = umma_unit(p, u_next);
+        if (row < R) {
+          const T* qn = static_cast<const T*>(p.q) + (rows_of(w_next) + row) * D;
+          prefetch_l2(qn);
+          if (D * sizeof(T) > 128) prefetch_l2(qn + 64);
+        }
+      }
       const long long row_base = rows_of(w);
       float m_used = -INFINITY, l_run = 0.f;               // per-row softmax state
       int lim = w.len - 1;                                 // last visible key of this row
@@ -1186,7 +1211,7 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
         mbar_arrive(smem_u32(&ctrl->p_ready));
       }
       if (!ok) break;
-      write_q(unit_index(r + 1));
+      write_q(u_next, w_next);
       // ---------------- the unit's rows leave tensor memory ----------------
       if (w.ntiles > 0) {
         ok = warp_wait(smem_u32(&ctrl->o_done), (g - 1) & 1);
@@ -1240,27 +1265,21 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
           p.part_ml[(slot * R + row) * 2] = m_used;
           p.part_ml[(slot * R + row) * 2 + 1] = l_run;
         }
-        // Publish the partial and draw the pair's ticket.  Nobody merges here: the merge is left to the teardown of
-        // whichever CTA gets to it first (see there), so the softmax warps go straight on to their next unit.  The
-        // softmax threads meet on an mbarrier with a bounded wait, never on bar.sync: a warp that gave up must not
-        // hang the rest.
-        __threadfence();
+        // Publish the partial.  Nobody merges here: the merge is left to the teardown of whichever CTA gets to it first
+        // (see there), so the softmax warps go straight on to their next unit.  The softmax threads meet on an
+        // mbarrier with a bounded wait, never on bar.sync: a warp that gave up must not hang the rest.
+        draw_owed_ticket();
         mbar_arrive(smem_u32(&ctrl->rows_out));
-        if (tid == 0) {
-          if (mbar_wait(smem_u32(&ctrl->rows_out), merges & 1)) {
-            __threadfence();
-            const int ticket = atomicAdd(p.counters + w.b * p.kv_heads + w.h, 1);
-            if (ticket == w.n_chunks - 1) atomicAdd(p.header + 3, 1);     // one more pair ready to be merged
-          } else {
-            p.header[0] = DEV_ERR_WAIT_EXPIRED;
-            *abort_flag = 1;
-          }
-        }
+        owed_pair = w.b * p.kv_heads + w.h;
+        owed_round = r;
         ++merges;
       }
+      w = w_next;
     }
+    if (ok) draw_owed_ticket();
     if (!ok) {
-      atomicMin(&ctrl->abort_round, r);
+      // (a unit whose ticket was still owed counts as unfinished: its pair will never be merged)
+      atomicMin(&ctrl->abort_round, (tid == 0 && owed_pair >= 0) ? owed_round : r);
       if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
     }
   }
@@ -1270,8 +1289,9 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
   if (warp == kMma) { tc_fence_after(); tmem_dealloc(tmem, kUmmaTmemCols); }
   // Merges.  A (sequence, kv head) pair whose chunks have all drawn their tickets is merged by whichever CTA claims
   // it while sweeping the ticket counters here, with all of its threads: CTAs that finish early take the pairs that
-  // are ready, the CTA that publishes a pair's last chunk sweeps after it did, so every pair is merged by the time
-  // the last CTA leaves, and no CTA waits for another.  header[3] counts the ready, unclaimed pairs.
+  // are complete, the CTA that draws a pair's last ticket sweeps after it did, so every pair is merged by the time
+  // the last CTA leaves, and no CTA waits for another.  A CTA takes one pair per sweep and sweeps again as long as it
+  // saw a complete pair; header[3] (tickets drawn and not merged) lets a CTA skip the sweep when there is nothing.
   if (!ctrl->abort_flag) {
     const int n_pairs = p.batch * p.kv_heads;
     for (int sweep = 0; sweep < n_pairs + 64; ++sweep) {
@@ -1289,16 +1309,17 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
         if (n > 1 && *reinterpret_cast<volatile int*>(p.counters + pair) == n &&
             atomicAdd(&ctrl->n_reserved, 1) < kUmmaMaxClaims &&
             atomicCAS(p.counters + pair, n, n + kMergeClaimed) == n) {
-          atomicSub(p.header + 3, 1);
+          atomicSub(p.header + 3, n);
           ctrl->claimed[atomicAdd(&ctrl->n_claimed, 1)] = pair;
         }
       }
       __syncthreads();
+      if (ctrl->n_reserved == 0) break;                      // no complete pair in sight: whoever completes one sweeps
       const int n_claimed = ctrl->n_claimed;
       for (int i = 0; i < n_claimed; ++i) {
         const int pair = ctrl->claimed[i];
         const int b = pair / p.kv_heads, h = pair - b * p.kv_heads;
-        const int item0 = b == 0 ? 0 : p.item_start[b];
+        const int item0 = p.item_start[b];
         T* out = static_cast<T*>(p.out) +
                  ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
         merge_chunks<T, D>(p, b, h, p.item_start[b + 1] - item0, item0, out, tid, static_cast<int>(blockDim.x));

@@ -91,6 +91,7 @@ __device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("gri
 
 // ------------------------------ named barriers --------------------------------
 // `count` threads in all; an arriving thread does not wait.
+__device__ __forceinline__ void prefetch_l2(const void* ptr) { asm volatile("prefetch.global.L2 [%0];\n" ::"l"(ptr)); }
 __device__ __forceinline__ void named_bar_arrive(int id, int count) { asm volatile("bar.arrive %0, %1;\n" ::"r"(id), "r"(count) : "memory"); }
 __device__ __forceinline__ void named_bar_sync(int id, int count) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory"); }
 
