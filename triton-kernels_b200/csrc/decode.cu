@@ -5,8 +5,10 @@
 //
 //   decode_plan_kernel : 1 CTA.  Reads the sequence lengths on the device (no host sync), picks the KV chunk size
 //       (the smallest of 32 candidates that keeps the batch at or below `target_items` work items, a whole number of
-//       waves of resident CTAs), splits every sequence into equal items and writes one record per item in execution
-//       order, longest first.  A work item is (sequence, KV chunk); CTAs are (item, kv head), heads fastest.
+//       waves of resident CTAs - or of a single wave, when the batch cuts into that few near-equal items and an
+//       estimate of the run time favours it), splits every sequence into equal items and writes one record per item
+//       in execution order, longest first.  A work item is (sequence, KV chunk); a unit is (item, kv head), heads
+//       fastest.
 //   decode_mma_kernel  : up to 16 q rows per KV head.  All q rows that share the KV head (group size G x draft
 //       tokens M) are packed into 16-row MMA tiles, so every K/V byte is read from HBM once per KV head (the
 //       reference re-reads it once per q head).  A producer warp stages K/V tiles of 64 keys by TMA (one 4-D box per
@@ -14,12 +16,14 @@
 //       and never dereferenced, V rows past the sequence end are zeroed in shared memory.  QK^T and PV run on
 //       bf16/fp16 mma.sync with fp32 accumulation and an online softmax in the exp2 domain.
 //   decode_umma_kernel : more than 16 q rows per KV head (speculative decode).  One 128-row tcgen05 tile: Q is
-//       written to tensor memory once per CTA, P once per 64-key tile, so both MMAs take their A operand from TMEM
-//       and shared memory is read once per K/V byte.  Same producer, planner and merge.
+//       written to tensor memory once per unit, P once per 64-key tile, so both MMAs take their A operand from TMEM
+//       and shared memory is read once per K/V byte.  Persistent: one wave of CTAs walks the unit list, the producer
+//       runs ahead across units.  Same planner and partial format; merges are claimed in the CTAs' teardown.
 //   decode_simt_kernel : the fp32-input variant, fp32 FMA arithmetic like the reference's decode kernel.
-//   All end in emit_and_merge(): a CTA whose sequence has a single chunk writes the output directly; otherwise it
-//       writes an (m, l, acc) partial and takes a ticket, and the CTA that draws the last ticket of its
-//       (sequence, kv head) performs the log-sum-exp merge.  No CTA ever waits for another.
+//   A unit whose sequence has a single chunk writes the output directly; otherwise it writes an (m, l, acc) partial
+//       and takes a ticket.  In the one-CTA-per-unit kernels (emit_and_merge) the CTA that draws the last ticket of
+//       its (sequence, kv head) performs the log-sum-exp merge; in the persistent kernel a CTA that has run out of
+//       units claims complete pairs and merges them.  No CTA ever waits for another.
 #include <algorithm>
 #include <mutex>
 #include <type_traits>
