@@ -48,7 +48,7 @@ NOMINAL = {"hbm_gbs": 8000.0, "bf16_tflops": 2250.0}
 L2_FLUSH_BYTES = 512 << 20
 
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum), one ncu capture per kernel and workload.
-NCU_TRAFFIC_BYTES = {"c2": 54.2e6, "c3": 778.6e6, "c4": 1137.2e6, "c5": 1787.6e6}
+NCU_TRAFFIC_BYTES = {"c2": 54.2e6, "c3": 778.6e6, "c4": 1137.2e6, "c5": 1805.4e6}
 # kernels of this library launched per call of the entry point (prefill: the persistent kernel;
 # decode: planner + split kernel with fused merge)
 LAUNCHES_PER_STEP = {"c2": 1, "c3": 1, "c4": 2, "c5": 2}
