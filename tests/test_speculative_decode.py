@@ -122,3 +122,33 @@ def test_spec_more_than_128_rows_per_kv_head(qh, kvh, m, layout):
     out = run_spec(layout, qs, ks, vs, True, permute=7, pad=-1, poison=float("nan"))
     for b in range(len(lens)):
         assert_close_both(out[b], refs[b], dtype, lens[b] + m, f"seq {b}")
+
+
+@pytest.mark.parametrize("qh,kvh,m", [(64, 8, 5), (64, 8, 16), (16, 8, 3)], ids=["40rows", "128rows", "6rows-warp-kernel"])
+@pytest.mark.parametrize("layout", ["ragged", "paged"])
+def test_spec_several_units_per_cta(qh, kvh, m, layout):
+    """More sequences than one wave of CTAs holds and uneven lengths: the planner stays with several waves, so a CTA
+    of the persistent tcgen05 kernel works through several (item, kv head) units, some of them chunks of a split
+    sequence whose merge is claimed in a teardown, others whole short sequences written directly (2, 4 and 1 softmax
+    warps; the 6-row case runs the one-CTA-per-unit warp-level kernel over the same plan)."""
+    from kernels import _native
+    from utils.launch_config import decode_items, decode_plan
+
+    dtype = torch.bfloat16
+    rng, gen = make_rngs("spec-units", qh, kvh, m, layout)
+    lens = [rng.choice([60, 300, 1500, 4000, 9000]) + rng.randint(0, 63) for _ in range(60)]
+    info = _native.device_info(torch.cuda.current_device())
+    plan = decode_plan(info.sm_count, len(lens), qh, kvh, m)
+    items = decode_items(plan, [n + m for n in lens])
+    assert sum(items) * kvh > 2 * info.sm_count and max(items) > 1      # several rounds, split sequences
+    qs = [torch.randn((qh, m, 64), generator=gen).to(dtype).to(DEVICE) for _ in lens]
+    ks = [torch.randn((n + m, kvh, 64), generator=gen).to(dtype).to(DEVICE) for n in lens]
+    vs = [torch.randn((n + m, kvh, 64), generator=gen).to(dtype).to(DEVICE) for n in lens]
+    refs = sdpa_ref.spec_decode_reference(qs, ks, vs, qh, kvh, True)
+    out = run_spec(layout, qs, ks, vs, True, permute=11, pad=-1, poison=float("nan"))
+    assert torch.isfinite(out.float()).all()
+    for b in range(len(lens)):
+        assert_close_both(out[b], refs[b], dtype, lens[b] + m, f"seq {b} len {lens[b]}")
+    # the same call again on the same workspace: tickets and the ready count were left clean
+    out2 = run_spec(layout, qs, ks, vs, True, permute=11, pad=-1, poison=float("nan"))
+    assert torch.equal(out, out2)
