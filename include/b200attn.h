@@ -110,6 +110,17 @@ typedef struct b200attn_prefill_args_t {
  *
  * causal_drafts != 0: the last M keys of each sequence are the draft tokens'
  * own keys and draft row i does not see draft keys i+1..M-1.
+ *
+ * Arithmetic: 16-bit inputs are multiplied on the tensor cores with fp32
+ * accumulation.  fp32 inputs with M == 1 (and at most 16 q rows per KV head)
+ * are multiplied in fp32 FMAs, as the reference's decode kernel does
+ * (kernels/decode.py:146-160); fp32 inputs with M > 1 are rounded to fp16
+ * copies in the workspace and multiplied on the tensor cores - the ten
+ * mantissa bits of the TF32 tl.dot the reference's speculative-decode kernel
+ * runs on fp32 operands (kernels/speculative_decode.py:153,175), but fp16's
+ * range: magnitudes beyond 65504 become infinite.  The workspace holds those
+ * copies (2 bytes per element of q, k and v as passed: a paged cache is copied
+ * whole).  b200attn_decode_static has no room for them and keeps fp32 FMAs.
  */
 typedef struct b200attn_decode_args_t {
   const void* q;

@@ -158,7 +158,8 @@ def test_sequence_balancing_and_shards():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("qh,kvh,m,batch,d,fp32", [(32, 8, 1, 64, 128, False), (64, 8, 5, 32, 128, False), (8, 2, 1, 4, 64, True),
-                                                   (32, 1, 5, 3, 128, False), (48, 1, 16, 2, 64, False), (8, 8, 16, 300, 64, False)])
+                                                   (32, 1, 5, 3, 128, False), (48, 1, 16, 2, 64, False), (8, 8, 16, 300, 64, False),
+                                                   (8, 1, 10, 16, 64, True)])
 def test_planning_mirror_agrees_with_the_library(qh, kvh, m, batch, d, fp32):
     """utils/launch_config.py restates the library's decode planning; the scratch size both derive from it must be
     the same number, or the mirror (and the CPU tests built on it) no longer describes the library."""
@@ -172,10 +173,13 @@ def test_planning_mirror_agrees_with_the_library(qh, kvh, m, batch, d, fp32):
     a.batch, a.q_heads, a.kv_heads, a.q_len, a.head_dim = batch, qh, kvh, m, d
     a.dtype = _native.F32 if fp32 else _native.BF16
     a.layout, a.device = _native.RAGGED, torch.cuda.current_device()
+    a.total_kv = 5000
     want = _native.lib().b200attn_decode_workspace_bytes(C.byref(a))
     plan = decode_plan(info.sm_count, batch, qh, kvh, m, fp32=fp32)
     rows = decode_pass_group(qh // kvh, m) * m
-    assert decode_workspace_bytes(plan, batch, kvh, d, rows) == want
+    cast = fp32 and (rows > 16 or m > 1)      # fp16 copies of q, k, v for the tensor-core kernels
+    assert decode_workspace_bytes(plan, batch, kvh, d, rows, batch * qh * m * d if cast else 0,
+                                  a.total_kv * kvh * d if cast else 0) == want
 
 
 @pytest.mark.gpu

@@ -10,7 +10,7 @@ import torch
 import test_attention as TA
 import test_decode as TD
 import test_speculative_decode as TS
-from helpers import PREFILL_F32_STRICT, assert_close_both
+from helpers import PREFILL_F32_STRICT, assert_close_both, spec_strict
 from oracle import sdpa_ref
 
 pytestmark = pytest.mark.gpu
@@ -81,7 +81,8 @@ def _decode_case(rng, gen, it, spec):
                             index_dtype=index_dtype)
     assert torch.isfinite(out.float()).all(), what
     for b in range(B):
-        assert_close_both(out[b], refs[b], dtype, max(kv_lens) + drafts, f"{what} seq {b}")
+        assert_close_both(out[b], refs[b], dtype, max(kv_lens) + drafts, f"{what} seq {b}",
+                          strict=spec_strict(dtype, QH, KVH, M) if spec else None)
 
 
 @pytest.mark.parametrize("chunk", range(6))

@@ -488,7 +488,9 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
 // The Q fragments are re-read from shared memory at every k-step instead of living in 4*D/16 registers per thread:
 // that keeps the kernel at 128 registers, so two or three CTAs share an SM.
 // NB: 16-key blocks a consumer warp handles per step (2 when a warp owns 32 or more keys of a stage).
-template <typename T, int D, int kStages, int NB, int kMaxThreads, int kMinBlocks>
+// T: element type of q, k, v as the kernel reads them; OutT: element type of the output rows (T, or float when the
+// inputs are fp16 copies of fp32 tensors).
+template <typename T, int D, int kStages, int NB, int kMaxThreads, int kMinBlocks, typename OutT = T>
 __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                          const __grid_constant__ CUtensorMap tm_v,
                                                          const DecodeParams p) {
@@ -810,7 +812,7 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
     poison_rows(comb_o, comb_ml, KS * rows_pad, D);
     __syncthreads();
   }
-  emit_and_merge<T, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, KS, rows_pad, &ctrl->ticket);
+  emit_and_merge<OutT, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, KS, rows_pad, &ctrl->ticket);
 }
 
 // ---------------------------------------------------------------------------
@@ -878,7 +880,9 @@ __device__ __forceinline__ UmmaUnit umma_unit(const DecodeParams& p, int u) {
   return w;
 }
 
-template <typename T, int D>
+// T: element type of q, k, v as the kernel reads them; OutT: element type of the output rows (T, or float when the
+// inputs are fp16 copies of fp32 tensors).
+template <typename T, int D, typename OutT = T>
 __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                              const __grid_constant__ CUtensorMap tm_v,
                                                              const DecodeParams p) {
@@ -1224,7 +1228,7 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
       }
       const bool single = w.n_chunks == 1;
       const long long slot = (static_cast<long long>(w.item0) + w.c) * p.kv_heads + w.h;
-      T* out = static_cast<T*>(p.out) + row_base * D;
+      OutT* out = static_cast<OutT*>(p.out) + row_base * D;
       const float inv = single ? (l_run > 0.f ? 1.f / l_run : 0.f) : 1.f;
 #pragma unroll
       for (int cc = 0; cc < D / 32; ++cc) {
@@ -1243,17 +1247,23 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
         }
         if (row < R) {
           if (single) {
-            if constexpr (sizeof(T) == 2) {
+            if constexpr (sizeof(OutT) == 2) {
               uint4* dst = reinterpret_cast<uint4*>(out + static_cast<long long>(row) * D + cc * 32);
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
                 uint4 x;
-                x.x = ElemTraits<T>::pack2(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
-                x.y = ElemTraits<T>::pack2(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
-                x.z = ElemTraits<T>::pack2(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
-                x.w = ElemTraits<T>::pack2(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
+                x.x = ElemTraits<OutT>::pack2(__uint_as_float(ov[8 * i]) * inv, __uint_as_float(ov[8 * i + 1]) * inv);
+                x.y = ElemTraits<OutT>::pack2(__uint_as_float(ov[8 * i + 2]) * inv, __uint_as_float(ov[8 * i + 3]) * inv);
+                x.z = ElemTraits<OutT>::pack2(__uint_as_float(ov[8 * i + 4]) * inv, __uint_as_float(ov[8 * i + 5]) * inv);
+                x.w = ElemTraits<OutT>::pack2(__uint_as_float(ov[8 * i + 6]) * inv, __uint_as_float(ov[8 * i + 7]) * inv);
                 dst[i] = x;
               }
+            } else {
+              float4* dst = reinterpret_cast<float4*>(out + static_cast<long long>(row) * D + cc * 32);
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                dst[i] = make_float4(__uint_as_float(ov[4 * i]) * inv, __uint_as_float(ov[4 * i + 1]) * inv,
+                                     __uint_as_float(ov[4 * i + 2]) * inv, __uint_as_float(ov[4 * i + 3]) * inv);
             }
           } else {
             float4* dst = reinterpret_cast<float4*>(p.part_o + (slot * R + row) * D + cc * 32);
@@ -1324,9 +1334,9 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
         const int pair = ctrl->claimed[i];
         const int b = pair / p.kv_heads, h = pair - b * p.kv_heads;
         const int item0 = p.item_start[b];
-        T* out = static_cast<T*>(p.out) +
-                 ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
-        merge_chunks<T, D>(p, b, h, p.item_start[b + 1] - item0, item0, out, tid, static_cast<int>(blockDim.x));
+        OutT* out = static_cast<OutT*>(p.out) +
+                    ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
+        merge_chunks<OutT, D>(p, b, h, p.item_start[b + 1] - item0, item0, out, tid, static_cast<int>(blockDim.x));
       }
       __syncthreads();
     }
@@ -1335,13 +1345,13 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     // A bounded wait ran out: the rows of the unit the softmax warps were in, and of the units this CTA had not
     // reached, are unknown.  They are filled with NaN (and their tickets are not drawn, so nobody merges over them):
     // the failure shows in the output as well as in the error word.
-    const T nan_t = ElemTraits<T>::from_float(__int_as_float(0x7fc00000));
+    const OutT nan_t = ElemTraits<OutT>::from_float(__int_as_float(0x7fc00000));
     for (int r = ctrl->abort_round; r != 0x7fffffff; ++r) {
       const int u = unit_index(r);
       if (u >= n_units) break;
       const UmmaUnit w = umma_unit(p, u);
-      T* out = static_cast<T*>(p.out) +
-               ((static_cast<long long>(w.b) * p.q_heads + static_cast<long long>(w.h) * p.head_stride + p.head0) * p.q_len) * D;
+      OutT* out = static_cast<OutT*>(p.out) +
+                  ((static_cast<long long>(w.b) * p.q_heads + static_cast<long long>(w.h) * p.head_stride + p.head0) * p.q_len) * D;
       for (int i = tid; i < R * D; i += blockDim.x) out[i] = nan_t;
     }
   }
@@ -1469,16 +1479,24 @@ int decode_pass_group(int group, int q_len) {
   return g < 1 ? 1 : g;
 }
 
-DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count) {
+DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count, bool allow_cast) {
   DecodeWsLayout w;
   const int group = decode_pass_group(a.kv_heads > 0 ? a.q_heads / a.kv_heads : 1, a.q_len);
   const int rows = group * a.q_len;
+  // fp32 inputs of a speculative-decode call (more than one q row per head, or more than 16 rows per KV head) are
+  // rounded to fp16 in the workspace and run on the tensor-core kernels with fp32 accumulation and fp32 output: the
+  // reference multiplies them with tl.dot on fp32 operands, i.e. in TF32, which keeps the same ten mantissa bits
+  // (kernels/speculative_decode.py:153,175); one fp32 FMA warp per q row re-reads K/V once per row and is one to two
+  // orders of magnitude slower there.  Plain decode (one q row per head), which the reference computes in fp32 FMAs
+  // (kernels/decode.py:146-160), stays on the fp32 kernel.
+  const bool cast16 = allow_cast && a.dtype == B200ATTN_F32 && (rows > 16 || a.q_len > 1);
+  const bool f32_kernel = a.dtype == B200ATTN_F32 && !cast16;
   // Six (item, kv head) CTAs per SM: two or three waves of the tensor-core kernels (3 or 2 resident CTAs per SM).
   // Fewer, longer CTAs amortise start-up and merge; the planner keeps the item count at or below this, so the grid
   // is a whole number of waves.  (Measured on B200, paged decode and speculative decode: 4 / 6 / 8 / 12 / 16 per SM
   // give 0.84 / 0.83 / 0.81 / 0.80 / 0.78 and 0.71 / 0.70 / 0.73 / 0.67 / 0.64 of the copy bandwidth without the
   // whole-wave rule, 0.76 for speculative decode with it.)  The fp32 kernel keeps eight.
-  const int per_sm = a.dtype == B200ATTN_F32 ? 8 : 6;
+  const int per_sm = f32_kernel ? 8 : 6;
   long long target = (static_cast<long long>(sm_count) * per_sm) / std::max(1, a.kv_heads);
   if (target < 1) target = 1;
   w.target_items = static_cast<int>(target);
@@ -1486,7 +1504,7 @@ DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count) {
   // per-item start-up + merge cost in keys of streaming time (from the sweeps quoted in the planner)
   w.wave_items = 0;
   w.item_overhead = 0;
-  if (a.dtype != B200ATTN_F32) {
+  if (!f32_kernel) {
     const bool wide = rows > 16;
     w.wave_items = static_cast<int>(std::max<long long>(1, (static_cast<long long>(sm_count) * (wide ? 2 : 3)) / std::max(1, a.kv_heads)));
     w.item_overhead = wide ? 448 : 128;
@@ -1505,34 +1523,74 @@ DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count) {
   const size_t slots = static_cast<size_t>(w.max_items) * a.kv_heads;
   w.ml_off = off;         off = up(off + sizeof(float) * slots * rows * 2);
   w.o_off = off;          off = up(off + sizeof(float) * slots * rows * a.head_dim);
+  w.cast_q_off = w.cast_k_off = w.cast_v_off = 0;
+  w.cast_q_elems = w.cast_kv_elems = 0;
+  if (cast16) {
+    w.cast_q_elems = static_cast<size_t>(a.batch) * a.q_heads * a.q_len * a.head_dim;
+    const size_t kv_rows = a.layout == B200ATTN_DENSE ? static_cast<size_t>(a.batch) * a.kv_heads * a.max_kv
+                                                      : static_cast<size_t>(a.total_kv) * a.kv_heads;
+    w.cast_kv_elems = kv_rows * a.head_dim;
+    w.cast_q_off = off; off = up(off + 2 * w.cast_q_elems);
+    w.cast_k_off = off; off = up(off + 2 * w.cast_kv_elems);
+    w.cast_v_off = off; off = up(off + 2 * w.cast_kv_elems);
+  }
   w.total = off;
   return w;
 }
 
 namespace {
 int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream, const DecodeWsLayout& w,
-                       int pass_group, int head0);
+                       int pass_group, int head0, bool f32_out);
+
+// fp32 -> fp16, four elements per thread (every tensor here is a whole number of head_dim rows)
+__global__ void __launch_bounds__(256) decode_cast_f16_kernel(const float4* __restrict__ src, uint2* __restrict__ dst,
+                                                              size_t n4) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n4;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const float4 x = __ldg(src + i);
+    dst[i] = make_uint2(ElemTraits<__half>::pack2(x.x, x.y), ElemTraits<__half>::pack2(x.z, x.w));
+  }
+}
 }  // namespace
 
-int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream) {
-  const DecodeWsLayout w = decode_ws_layout(a, sm_count);
+int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream, bool allow_cast) {
+  const DecodeWsLayout w = decode_ws_layout(a, sm_count, allow_cast);
   if (a.workspace == nullptr || a.workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(a.workspace) & 255)) {
     set_error("decode: workspace needs %zu bytes, 256-byte aligned (got %zu)", w.total, a.workspace_bytes);
     return B200ATTN_E_WORKSPACE;
   }
   const int group = a.q_heads / a.kv_heads;
   const int pass_group = decode_pass_group(group, a.q_len);
+  b200attn_decode_args_t b = a;
+  if (w.cast_kv_elems > 0) {
+    // fp16 copies of q, k, v (see decode_ws_layout); the launches below read them and write fp32 rows
+    unsigned char* ws = static_cast<unsigned char*>(a.workspace);
+    const void* src[3] = {a.q, a.k, a.v};
+    void* dst[3] = {ws + w.cast_q_off, ws + w.cast_k_off, ws + w.cast_v_off};
+    const size_t elems[3] = {w.cast_q_elems, w.cast_kv_elems, w.cast_kv_elems};
+    for (int i = 0; i < 3; ++i) {
+      const size_t n4 = elems[i] / 4;
+      if (n4 == 0) continue;
+      const unsigned blocks = static_cast<unsigned>(std::min<size_t>((n4 + 255) / 256, static_cast<size_t>(sm_count) * 16));
+      decode_cast_f16_kernel<<<blocks, 256, 0, stream>>>(static_cast<const float4*>(src[i]), static_cast<uint2*>(dst[i]), n4);
+      const cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return cuda_fail(e, "decode_cast_f16_kernel launch");
+    }
+    b.q = dst[0]; b.k = dst[1]; b.v = dst[2];
+    b.dtype = B200ATTN_F16;
+  }
   // one launch per sub-group of q heads; they run back to back on the stream and share the workspace
   for (int head0 = 0; head0 < group; head0 += pass_group) {
-    const int rc = launch_decode_pass(a, sm_count, stream, w, pass_group, head0);
+    const int rc = launch_decode_pass(b, sm_count, stream, w, pass_group, head0, w.cast_kv_elems > 0);
     if (rc) return rc;
   }
   return B200ATTN_OK;
 }
 
 namespace {
+// `f32_out`: the inputs are the fp16 copies of fp32 tensors and the output rows are fp32
 int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream, const DecodeWsLayout& w,
-                       int pass_group, int head0) {
+                       int pass_group, int head0, bool f32_out) {
   DecodeParams p;
   p.q = a.q; p.k = a.k; p.v = a.v; p.out = a.out;
   p.kv_indptr = a.kv_indptr; p.k_table = a.k_table; p.v_table = a.v_table;
@@ -1599,16 +1657,18 @@ int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream
     // persistent: one wave of two CTAs per SM walks the unit list (fewer CTAs when the list cannot be longer)
     const unsigned wave = 2u * static_cast<unsigned>(sm_count);
     const dim3 grid(std::min(static_cast<unsigned>(w.max_items) * a.kv_heads, wave), 1);
-#define B200ATTN_LAUNCH_UMMA(TYPE, DIM)                                  \
+#define B200ATTN_LAUNCH_UMMA(TYPE, DIM, OUT)                             \
     do {                                                                 \
-      rc = set_smem(decode_umma_kernel<TYPE, DIM>, smem);                \
+      rc = set_smem(decode_umma_kernel<TYPE, DIM, OUT>, smem);           \
       if (rc) return rc;                                                 \
-      launch_after_planner(decode_umma_kernel<TYPE, DIM>, grid, 192, smem, stream, tk, tv, p); \
+      launch_after_planner(decode_umma_kernel<TYPE, DIM, OUT>, grid, 192, smem, stream, tk, tv, p); \
     } while (0)
-    if (a.dtype == B200ATTN_BF16) {
-      if (D == 128) B200ATTN_LAUNCH_UMMA(__nv_bfloat16, 128); else B200ATTN_LAUNCH_UMMA(__nv_bfloat16, 64);
+    if (f32_out) {
+      if (D == 128) B200ATTN_LAUNCH_UMMA(__half, 128, float); else B200ATTN_LAUNCH_UMMA(__half, 64, float);
+    } else if (a.dtype == B200ATTN_BF16) {
+      if (D == 128) B200ATTN_LAUNCH_UMMA(__nv_bfloat16, 128, __nv_bfloat16); else B200ATTN_LAUNCH_UMMA(__nv_bfloat16, 64, __nv_bfloat16);
     } else {
-      if (D == 128) B200ATTN_LAUNCH_UMMA(__half, 128); else B200ATTN_LAUNCH_UMMA(__half, 64);
+      if (D == 128) B200ATTN_LAUNCH_UMMA(__half, 128, __half); else B200ATTN_LAUNCH_UMMA(__half, 64, __half);
     }
 #undef B200ATTN_LAUNCH_UMMA
   } else {
@@ -1643,17 +1703,19 @@ int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream
       if ((rc = make_kv_rows_map(&tk, a.dtype, a.k, a.total_kv, a.kv_heads, D, box, rstride, D * 2ll))) return rc;
       if ((rc = make_kv_rows_map(&tv, a.dtype, a.v, a.total_kv, a.kv_heads, D, box, rstride, D * 2ll))) return rc;
     }
-#define B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, STAGES, NBLK, MAXT, MINB)                                    \
+#define B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, STAGES, NBLK, MAXT, MINB, OUT)                               \
     do {                                                                                                  \
-      rc = set_smem(decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB>, smem);                       \
+      rc = set_smem(decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB, OUT>, smem);                  \
       if (rc) return rc;                                                                                  \
-      launch_after_planner(decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB>, grid, threads, smem, stream, tk, tv, p);\
+      launch_after_planner(decode_mma_kernel<TYPE, DIM, STAGES, NBLK, MAXT, MINB, OUT>, grid, threads, smem, stream, tk, tv, p);\
     } while (0)
-#define B200ATTN_LAUNCH_DECODE(TYPE, DIM) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 2, 1, 160, 3)
-    if (a.dtype == B200ATTN_BF16) {
-      if (D == 128) B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 128); else B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 64);
+#define B200ATTN_LAUNCH_DECODE(TYPE, DIM, OUT) B200ATTN_LAUNCH_DECODE_V(TYPE, DIM, 2, 1, 160, 3, OUT)
+    if (f32_out) {
+      if (D == 128) B200ATTN_LAUNCH_DECODE(__half, 128, float); else B200ATTN_LAUNCH_DECODE(__half, 64, float);
+    } else if (a.dtype == B200ATTN_BF16) {
+      if (D == 128) B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 128, __nv_bfloat16); else B200ATTN_LAUNCH_DECODE(__nv_bfloat16, 64, __nv_bfloat16);
     } else {
-      if (D == 128) B200ATTN_LAUNCH_DECODE(__half, 128); else B200ATTN_LAUNCH_DECODE(__half, 64);
+      if (D == 128) B200ATTN_LAUNCH_DECODE(__half, 128, __half); else B200ATTN_LAUNCH_DECODE(__half, 64, __half);
     }
 #undef B200ATTN_LAUNCH_DECODE_V
 #undef B200ATTN_LAUNCH_DECODE
@@ -1692,7 +1754,7 @@ int launch_decode_static(const b200attn_decode_args_t& a, int sm_count, cudaStre
     set_error("decode_static: device ordinal %d out of range", a.device);
     return B200ATTN_E_INVALID;
   }
-  const DecodeWsLayout w = decode_ws_layout(a, sm_count);
+  const DecodeWsLayout w = decode_ws_layout(a, sm_count, /*allow_cast=*/false);
   if (w.total > kStaticScratchBytes) {
     set_error("decode_static: this problem needs %zu bytes of scratch but the built-in array holds %zu; "
               "use b200attn_decode with a caller-provided workspace", w.total, kStaticScratchBytes);
@@ -1714,7 +1776,7 @@ int launch_decode_static(const b200attn_decode_args_t& a, int sm_count, cudaStre
   b.workspace_bytes = kStaticScratchBytes;
   // The planner kernel rewrites the item prefix and zeroes the merge tickets at the start of every
   // call, and partial slots are always written before they are read, so stale contents are harmless.
-  return launch_decode(b, sm_count, stream);
+  return launch_decode(b, sm_count, stream, /*allow_cast=*/false);
 }
 
 

@@ -63,11 +63,16 @@ struct DecodeWsLayout {
   int item_overhead; // start-up and merge of a work item, in keys of streaming time (planner's cost estimate)
   int min_chunk;
   int max_items;
+  // fp32 inputs of a speculative-decode call: fp16 copies of q, k, v that the tensor-core kernels read
+  // (0 elements: no copies, the launch reads the caller's tensors)
+  size_t cast_q_off, cast_k_off, cast_v_off;
+  size_t cast_q_elems, cast_kv_elems;
 };
 
 int decode_pass_group(int group, int q_len);
-DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count);
-int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream);
+// `allow_cast` false: plan fp32 inputs for the fp32 FMA kernel whatever the row count (no room for copies)
+DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count, bool allow_cast = true);
+int launch_decode(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream, bool allow_cast = true);
 int launch_decode_static(const b200attn_decode_args_t& a, int sm_count, cudaStream_t stream);
 int check_decode_static(int device, cudaStream_t stream, int32_t* code);
 

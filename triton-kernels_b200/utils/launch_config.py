@@ -41,9 +41,11 @@ def decode_pass_group(group: int, q_len: int) -> int:
     return max(g, 1)
 
 
-def decode_workspace_bytes(plan: "DecodePlan", batch: int, kv_heads: int, head_dim: int, rows: int) -> int:
+def decode_workspace_bytes(plan: "DecodePlan", batch: int, kv_heads: int, head_dim: int, rows: int,
+                           cast_q_elems: int = 0, cast_kv_elems: int = 0) -> int:
     """Bytes of scratch a decode call needs: header, item prefix, merge tickets, item records, (m, l) and O partials,
-    each rounded up to 256 bytes (csrc/decode.cu decode_ws_layout)."""
+    each rounded up to 256 bytes (csrc/decode.cu decode_ws_layout) - and, for fp32 inputs of a speculative-decode
+    call, the fp16 copies of q, k and v (``cast_*_elems`` elements each)."""
     up = lambda x: (x + 255) & ~255
     off = 256
     off = up(off + 4 * (batch + 1))
@@ -52,12 +54,19 @@ def decode_workspace_bytes(plan: "DecodePlan", batch: int, kv_heads: int, head_d
     slots = plan.max_items * kv_heads
     off = up(off + 4 * slots * rows * 2)
     off = up(off + 4 * slots * rows * head_dim)
+    if cast_kv_elems:
+        off = up(off + 2 * cast_q_elems)
+        off = up(off + 2 * cast_kv_elems)
+        off = up(off + 2 * cast_kv_elems)
     return off
 
 
 def decode_plan(sm_count: int, batch: int, q_heads: int, kv_heads: int, q_len: int, fp32: bool = False) -> DecodePlan:
     group = decode_pass_group(q_heads // kv_heads, q_len)
     rows = group * q_len
+    # fp32 inputs of a speculative-decode call (several q rows per head) run the tensor-core kernels on fp16 copies
+    # and are planned like 16-bit inputs
+    fp32 = fp32 and rows <= 16 and q_len <= 1
     # six (item, kv head) CTAs per SM for the tensor-core kernels (a whole number of waves at 2 or 3 resident CTAs
     # per SM), eight for the fp32 kernel
     target = max(1, (sm_count * (8 if fp32 else 6)) // max(1, kv_heads))
