@@ -260,7 +260,10 @@ __device__ __forceinline__ ItemWork decode_item(const PrefillParams& p, int item
 // Persistent kernel: one CTA per SM; work items are drawn from a global counter (heaviest first).
 // The producer warp is also the scheduler: it publishes item indices through a 2-deep ring, so it can fetch Q
 // and the first K/V tiles of the next item while the other roles finish the current one.
-template <typename T, int D, typename OutT>
+// kPaged: the instantiation launched for paged K/V; only it carries the block-table read-ahead of the producer (in
+// the dense / ragged kernel that code, though never run, cost 1 % on the dense benchmark configuration).  The other
+// layout checks stay run-time checks.
+template <typename T, int D, typename OutT, bool kPaged>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
@@ -373,6 +376,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // (the last one V alone).  Stage = pair % 2; its V buffer is ring buffer 2 * stage, its K buffer 2 * stage + 1.
       pair_lo = pair_e;
       const int npairs = w.nkv_max > 0 ? w.nkv_max + 1 : 0;
+      // Paged K/V with at most 32 boxes per tile (one per lane): the raw block-table entries of a pair's boxes (V of
+      // tile pi - 1, K of tile pi) are read one pair ahead, into two plain registers, so that the table read is not
+      // between "stage free" and "copies issued" (the ring is only two pairs deep).
+      constexpr int kNoPage = static_cast<int>(0x80000000u);
+      const int pf_boxes = kPaged ? kBN / p.box_rows : 0;
+      const bool pf = kPaged && pf_boxes <= 32;
+      int pg_v = kNoPage, pg_k = kNoPage;
+      auto fetch_pages = [&](int pi) {
+        const int tv = (pi - 1) * kBN + lane * p.box_rows, tk = pi * kBN + lane * p.box_rows;
+        pg_v = (lane < pf_boxes && pi >= 1 && tv < w.len_k)
+                   ? __ldg(p.v_table + static_cast<long long>(w.b) * p.table_stride + (tv + w.kv_tok0) / p.page_size) : kNoPage;
+        pg_k = (lane < pf_boxes && pi < w.nkv_max && tk < w.len_k)
+                   ? __ldg(p.k_table + static_cast<long long>(w.b) * p.table_stride + (tk + w.kv_tok0) / p.page_size) : kNoPage;
+      };
+      if (pf && npairs > 0) fetch_pages(0);
       for (int pi = 0; pi < npairs && ok; ++pi, ++pair_e) {
         const int stage = pair_e % kStages;
         const int use = pair_e / kStages;
@@ -397,6 +415,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                             static_cast<int>(w.kv_row0 + static_cast<long long>(jk) * kBN));
             }
           }
+        } else if (pf) {
+          // one box per lane and operand from the prefetched table entries
+          auto row_of = [&](int page, int t) -> int {
+            if (page == kNoPage) return -1;
+            // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
+            const bool bad = page < 0 || page >= p.num_pages;
+            if (bad) p.header[0] = DEV_ERR_PAGE_RANGE;
+            return p.num_pages > 0 ? (bad ? 0 : page) * p.page_size + (t + w.kv_tok0) % p.page_size : -1;
+          };
+          const int rv = row_of(pg_v, jv * kBN + lane * p.box_rows);
+          const int rk = row_of(pg_k, jk * kBN + lane * p.box_rows);
+          int count = (rv >= 0) + (rk >= 0);
+          for (int o = 16; o > 0; o >>= 1) count += __shfl_xor_sync(0xffffffffu, count, o);
+          if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * p.box_rows * 128 * Plan::kChunks);
+          __syncwarp();
+          for (int c = 0; c < Plan::kChunks; ++c) {
+            if (rv >= 0)
+              tma_load_3d(vdst + c * Plan::kChunkBytes + lane * p.box_rows * 128, &tm_v, bar, c * 64, w.kv_head_coord, rv);
+            if (rk >= 0)
+              tma_load_3d(kdst + c * Plan::kChunkBytes + lane * p.box_rows * 128, &tm_k, bar, c * 64, w.kv_head_coord, rk);
+          }
+          if (pi + 1 < npairs) fetch_pages(pi + 1);
         } else {
           // one box of `box_rows` tokens per lane per round and operand; only pages that exist are fetched
           const int boxes = kBN / p.box_rows;
@@ -1213,8 +1253,13 @@ int launch_prefill(const b200attn_prefill_args_t& a_in, int sm_count, cudaStream
 #define B200ATTN_LAUNCH_PREFILL(TYPE, DIM, OUT)                                                          \
   do {                                                                                                   \
     const size_t smem = std::max<size_t>(SmemPlan<DIM>::kTotal + 1024, 120 * 1024);                      \
-    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(prefill_kernel<TYPE, DIM, OUT>), smem))) return rc; \
-    prefill_kernel<TYPE, DIM, OUT><<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);                     \
+    if (a.layout == B200ATTN_PAGED) {                                                                    \
+      if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(prefill_kernel<TYPE, DIM, OUT, true>), smem))) return rc; \
+      prefill_kernel<TYPE, DIM, OUT, true><<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);             \
+    } else {                                                                                             \
+      if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(prefill_kernel<TYPE, DIM, OUT, false>), smem))) return rc; \
+      prefill_kernel<TYPE, DIM, OUT, false><<<grid, kThreads, smem, stream>>>(tq, tk, tv, p);            \
+    }                                                                                                    \
   } while (0)
   if (f32) {
     if (D == 128) B200ATTN_LAUNCH_PREFILL(__half, 128, float); else B200ATTN_LAUNCH_PREFILL(__half, 64, float);
