@@ -485,6 +485,53 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ok);
 }
 
+// Block-table read-ahead of a producer warp for paged caches: lane i owns box i of a 64-key tile (`on` only when a
+// tile has at most 32 boxes).  fetch() issues the two table reads of the tile that starts at key t0 and leaves the
+// raw entries in the caller's registers; row() turns an entry into the cache row of the lane's box, once the entry is
+// needed (checking it then, so that nothing waits for the read before).
+constexpr int kNoPage = static_cast<int>(0x80000000u);
+struct PageAhead {
+  const int* ktab;
+  const int* vtab;
+  int lane, boxes, box_rows;
+  bool on;
+  __device__ __forceinline__ PageAhead(const DecodeParams& p, int b, int lane_) : lane(lane_) {
+    boxes = kTileN >> p.box_shift;
+    box_rows = 1 << p.box_shift;
+    on = p.layout == B200ATTN_PAGED && boxes <= 32;
+    page_shift = p.page_shift;
+    page_size = p.page_size;
+    ktab = on ? p.k_table + static_cast<long long>(b) * p.table_stride : nullptr;
+    vtab = on ? p.v_table + static_cast<long long>(b) * p.table_stride : nullptr;
+  }
+  __device__ __forceinline__ void retarget(const DecodeParams& p, int b) {
+    if (on) {
+      ktab = p.k_table + static_cast<long long>(b) * p.table_stride;
+      vtab = p.v_table + static_cast<long long>(b) * p.table_stride;
+    }
+  }
+  __device__ __forceinline__ void fetch(int t0, int t_end, int& kp, int& vp) const {
+    const int t = t0 + lane * box_rows;
+    kp = vp = kNoPage;
+    if (lane < boxes && t < t_end) {
+      // (page size known only at run time; a shift when it is a power of two)
+      kp = __ldg(ktab + page_of(t));
+      vp = __ldg(vtab + page_of(t));
+    }
+  }
+  int page_shift, page_size;
+  __device__ __forceinline__ int page_of(int t) const { return page_shift >= 0 ? (t >> page_shift) : t / page_size; }
+  __device__ __forceinline__ int row(const DecodeParams& p, int page, int t0) const {
+    if (page == kNoPage) return -1;
+    const int t = t0 + lane * box_rows;
+    const int off = page_shift >= 0 ? (t & (page_size - 1)) : t % page_size;
+    // an entry outside the cache is reported and replaced by page 0: never dereferenced, output stays finite
+    const bool bad = page < 0 || page >= p.num_pages;
+    if (bad) p.header[0] = DEV_ERR_PAGE_RANGE;
+    return p.num_pages > 0 ? (bad ? 0 : page) * p.page_size + off : -1;
+  }
+};
+
 // The Q fragments are re-read from shared memory at every k-step instead of living in 4*D/16 registers per thread:
 // that keeps the kernel at 128 registers, so two or three CTAs share an SM.
 // NB: 16-key blocks a consumer warp handles per step (2 when a warp owns 32 or more keys of a stage).
@@ -575,6 +622,12 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
     if (p.layout == B200ATTN_DENSE) { h_coord = 0; row0 = (static_cast<long long>(b) * p.kv_heads + h) * p.max_kv; }
     bool ok = true;
     int issued = 0;
+    // Paged caches with at most one box per lane and tile: the block-table entries of a tile are read one tile ahead,
+    // into two plain registers (an array indexed by a loop counter would live in local memory and the read would be
+    // waited for at once), so that the table read is over by the time the tile's stage comes free.
+    const PageAhead ahead(p, b, lane);
+    int kp_next = kNoPage, vp_next = kNoPage;
+    if (ahead.on && ntiles > 0) ahead.fetch(t_begin, t_end, kp_next, vp_next);
     for (int tile = 0; tile < ntiles; ++tile) {
       const int stage = tile % kStages, use = tile / kStages;
       if (use > 0) {
@@ -592,6 +645,16 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
           ptx::tma_load_4d(kdst, &tm_k, bar, 0, row, 0, h_coord);
           ptx::tma_load_4d(vdst, &tm_v, bar, 0, row, 0, h_coord);
         }
+      } else if (ahead.on) {
+        const int kr = ahead.row(p, kp_next, t0), vr = ahead.row(p, vp_next, t0);
+        int count = (kr >= 0) + (vr >= 0);
+        for (int off = 16; off > 0; off >>= 1) count += __shfl_xor_sync(0xffffffffu, count, off);
+        if (lane == 0) ptx::mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * ahead.box_rows * 128 * CHUNKS);
+        __syncwarp();
+        const uint32_t boff = static_cast<uint32_t>(lane) * ahead.box_rows * 128 * CHUNKS;
+        if (kr >= 0) ptx::tma_load_4d(kdst + boff, &tm_k, bar, 0, kr, 0, h_coord);
+        if (vr >= 0) ptx::tma_load_4d(vdst + boff, &tm_v, bar, 0, vr, 0, h_coord);
+        if (tile + 1 < ntiles) ahead.fetch(t0 + kTileN, t_end, kp_next, vp_next);
       } else {
         // one box of box_rows keys per (lane, round); only pages that hold keys of this chunk are fetched
         const int boxes = kTileN >> p.box_shift;
@@ -941,10 +1004,15 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     bool ok = true;
     int g = 0;                                   // tiles issued so far, over all units
     const int box_rows = 1 << p.box_shift;
+    // block-table entries are read one tile ahead, across units too (see PageAhead)
+    PageAhead ahead(p, 0, lane);
+    int kp_next = kNoPage, vp_next = kNoPage;
+    int ahead_g = -1;                            // running tile index the entries in kp_next / vp_next belong to
     for (int r = 0; ok; ++r) {
       const int u = unit_index(r);
       if (u >= n_units) break;
       const UmmaUnit w = umma_unit(p, u);
+      ahead.retarget(p, w.b);
       int h_coord = w.h;
       long long row0 = w.seq_start;
       if (p.layout == B200ATTN_DENSE) { h_coord = 0; row0 = (static_cast<long long>(w.b) * p.kv_heads + w.h) * p.max_kv; }
@@ -966,6 +1034,31 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
             for (int cc = 0; cc < CHUNKS; ++cc) {
               tma_load_3d(kdst + cc * CHUNK_BYTES, &tm_k, bar, cc * 64, h_coord, row);
               tma_load_3d(vdst + cc * CHUNK_BYTES, &tm_v, bar, cc * 64, h_coord, row);
+            }
+          }
+        } else if (ahead.on) {
+          if (ahead_g != g) ahead.fetch(t0, w.t_end, kp_next, vp_next);   // first tile of the CTA, or after an empty unit
+          const int kr = ahead.row(p, kp_next, t0), vr = ahead.row(p, vp_next, t0);
+          int count = (kr >= 0) + (vr >= 0);
+          for (int off = 16; off > 0; off >>= 1) count += __shfl_xor_sync(0xffffffffu, count, off);
+          if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(count) * box_rows * 128 * CHUNKS);
+          __syncwarp();
+          const uint32_t roff = static_cast<uint32_t>(lane) * box_rows * 128;
+#pragma unroll
+          for (int cc = 0; cc < CHUNKS; ++cc) {
+            if (kr >= 0) tma_load_3d(kdst + cc * CHUNK_BYTES + roff, &tm_k, bar, cc * 64, h_coord, kr);
+            if (vr >= 0) tma_load_3d(vdst + cc * CHUNK_BYTES + roff, &tm_v, bar, cc * 64, h_coord, vr);
+          }
+          // read ahead: the next tile of this unit, or the first tile of the CTA's next unit
+          if (tile + 1 < w.ntiles) {
+            ahead.fetch(t0 + kTileN, w.t_end, kp_next, vp_next);
+            ahead_g = g + 1;
+          } else if (unit_index(r + 1) < n_units) {
+            const UmmaUnit w2 = umma_unit(p, unit_index(r + 1));
+            if (w2.ntiles > 0) {
+              ahead.retarget(p, w2.b);
+              ahead.fetch(w2.t_begin, w2.t_end, kp_next, vp_next);
+              ahead_g = g + 1;
             }
           }
         } else {
