@@ -358,7 +358,12 @@ def measure_strong(name, device, rank, world, steps, warmup, seed, peaks, flush,
         got = assemble(parts)
         torch.cuda.synchronize()
         diff = (got.float() - whole.float()).abs().max().item() if whole.numel() else 0.0
+        # bit equality where shard and whole take the same path (prefill without the KV split); otherwise partial
+        # sums are grouped differently and the two agree to rounding: the reference's own bar for this dtype at N = 1
+        # (bf16: atol 2.4e-2, rtol 2e-2; tests/test_attention.py:20-30 of the reference) is reported beside it
+        close = bool(torch.allclose(got.float(), whole.float(), atol=2.4e-2, rtol=2e-2)) if whole.numel() else True
         check = {"sharded_equals_single": bool(torch.equal(got, whole)), "max_abs_diff": diff,
+                 "within_reference_tolerance": close,
                  "gather_us": gather_us, "gathered_bytes": got.numel() * got.element_size()}
         del whole, got
     del parts, out
