@@ -139,14 +139,14 @@ int b200attn_device_info(int device, b200attn_device_info_t* info) {
 
 size_t b200attn_prefill_workspace_bytes(const b200attn_prefill_args_t* a) {
   if (!a || a->kv_heads <= 0 || a->q_heads <= 0) return 0;
-  b200attn_device_info_t info;
+  b200attn_device_info_t info = {};
   if (query_device(a->device, &info)) return 0;
   return prefill_workspace_bytes(*a, info.sm_count);
 }
 
 size_t b200attn_decode_workspace_bytes(const b200attn_decode_args_t* a) {
   if (!a || a->kv_heads <= 0 || a->batch < 0) return 0;
-  b200attn_device_info_t info;
+  b200attn_device_info_t info = {};
   if (query_device(a->device, &info)) return 0;
   return decode_ws_layout(*a, info.sm_count).total;
 }
@@ -160,7 +160,7 @@ int b200attn_prefill(const b200attn_prefill_args_t* a, void* cuda_stream) {
   if (a->layout == B200ATTN_RAGGED && (!a->q_indptr || !a->kv_indptr || a->total_q < 0 || a->total_kv < 0)) { set_error("prefill: ragged layout needs q_indptr, kv_indptr and totals"); return B200ATTN_E_INVALID; }
   if (a->layout == B200ATTN_PAGED && (!a->kv_indptr || !a->k_table || !a->v_table || a->page_size <= 0 || a->table_stride < 0)) { set_error("prefill: paged layout needs lengths, both block tables and a page size"); return B200ATTN_E_INVALID; }
   if (a->layout != B200ATTN_RAGGED && (a->max_q < 0 || (a->layout == B200ATTN_DENSE && a->max_kv < 0))) { set_error("prefill: negative extent"); return B200ATTN_E_INVALID; }
-  b200attn_device_info_t info;
+  b200attn_device_info_t info = {};
   if ((rc = check_arch(a->device, &info))) return rc;
   if (a->batch == 0) return B200ATTN_OK;
   DeviceGuard guard;
@@ -178,7 +178,7 @@ int b200attn_decode(const b200attn_decode_args_t* a, void* cuda_stream) {
   if (a->layout == B200ATTN_RAGGED && (!a->kv_indptr || a->total_kv < 0)) { set_error("decode: ragged layout needs kv_indptr and total_kv"); return B200ATTN_E_INVALID; }
   if (a->layout == B200ATTN_PAGED && (!a->kv_indptr || !a->k_table || !a->v_table || a->page_size <= 0 || a->table_stride < 0)) { set_error("decode: paged layout needs lengths, both block tables and a page size"); return B200ATTN_E_INVALID; }
   if (a->layout == B200ATTN_DENSE && a->max_kv < 0) { set_error("decode: negative extent"); return B200ATTN_E_INVALID; }
-  b200attn_device_info_t info;
+  b200attn_device_info_t info = {};
   if ((rc = check_arch(a->device, &info))) return rc;
   if (a->batch == 0) return B200ATTN_OK;
   DeviceGuard guard;
@@ -196,7 +196,7 @@ int b200attn_decode_static(const b200attn_decode_args_t* a, void* cuda_stream) {
   if (a->layout == B200ATTN_RAGGED && (!a->kv_indptr || a->total_kv < 0)) { set_error("decode_static: ragged layout needs kv_indptr and total_kv"); return B200ATTN_E_INVALID; }
   if (a->layout == B200ATTN_PAGED && (!a->kv_indptr || !a->k_table || !a->v_table || a->page_size <= 0 || a->table_stride < 0)) { set_error("decode_static: paged layout needs lengths, both block tables and a page size"); return B200ATTN_E_INVALID; }
   if (a->layout == B200ATTN_DENSE && a->max_kv < 0) { set_error("decode_static: negative extent"); return B200ATTN_E_INVALID; }
-  b200attn_device_info_t info;
+  b200attn_device_info_t info = {};
   if ((rc = check_arch(a->device, &info))) return rc;
   if (a->batch == 0) return B200ATTN_OK;
   DeviceGuard guard;
@@ -205,7 +205,7 @@ int b200attn_decode_static(const b200attn_decode_args_t* a, void* cuda_stream) {
 }
 
 int b200attn_decode_static_check(int device, void* cuda_stream, int32_t* code) {
-  b200attn_device_info_t info;
+  b200attn_device_info_t info = {};
   int rc;
   if ((rc = check_arch(device, &info))) return rc;
   DeviceGuard guard;
@@ -216,7 +216,7 @@ int b200attn_decode_static_check(int device, void* cuda_stream, int32_t* code) {
 int b200attn_selftest_wait_expiry(int device, void* workspace, uint32_t tries, void* cuda_stream) {
   if (!workspace) { set_error("workspace is null"); return B200ATTN_E_INVALID; }
   if (tries == 0 || tries > (1u << 20)) { set_error("selftest: tries %u outside 1..2^20", tries); return B200ATTN_E_INVALID; }
-  b200attn_device_info_t info;
+  b200attn_device_info_t info = {};
   int rc;
   if ((rc = check_arch(device, &info))) return rc;
   DeviceGuard guard;
@@ -235,7 +235,7 @@ int b200attn_paged_append(const b200attn_paged_append_args_t* a, void* cuda_stre
   if (!a->src || !a->cache || !a->src_indptr || !a->table) { set_error("paged_append: null pointer"); return B200ATTN_E_INVALID; }
   if (!aligned16(a->src) || !aligned16(a->cache)) { set_error("paged_append: src and cache must be 16-byte aligned"); return B200ATTN_E_INVALID; }
   if (!a->workspace || a->workspace_bytes < static_cast<size_t>(kHeaderBytes)) { set_error("paged_append: workspace needs %d bytes", kHeaderBytes); return B200ATTN_E_WORKSPACE; }
-  b200attn_device_info_t info;
+  b200attn_device_info_t info = {};
   int rc;
   if ((rc = check_arch(a->device, &info))) return rc;
   DeviceGuard guard;
@@ -249,7 +249,7 @@ int b200attn_softmax(const b200attn_softmax_args_t* a, void* cuda_stream) {
   if (a->rows == 0 || a->cols == 0) return B200ATTN_OK;
   if (!a->x || !a->out) { set_error("softmax: null pointer"); return B200ATTN_E_INVALID; }
   if (a->dtype != B200ATTN_F16 && a->dtype != B200ATTN_BF16 && a->dtype != B200ATTN_F32) { set_error("softmax: unknown dtype %d", a->dtype); return B200ATTN_E_UNSUPPORTED; }
-  b200attn_device_info_t info;
+  b200attn_device_info_t info = {};
   int rc;
   if ((rc = check_arch(a->device, &info))) return rc;
   DeviceGuard guard;

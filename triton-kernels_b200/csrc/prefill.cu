@@ -42,7 +42,6 @@ using namespace ptx;
 
 constexpr int kBM = 128;           // query rows per slot
 constexpr int kBN = 128;           // keys per K/V tile
-constexpr int kHalf = 64;          // keys per softmax / MMA step
 constexpr int kSlots = 2;
 constexpr int kRing = 4;           // K/V tile buffers: two stages of one V buffer and one K buffer
 constexpr int kStages = 2;         // a stage holds the pair {V_j, K_j+1}: one barrier to wait for, one to release
