@@ -1479,59 +1479,88 @@ __global__ void __launch_bounds__(128) decode_simt_kernel(const DecodeParams p) 
   const int t_begin = c * chunk;
   const int t_end = min(len, t_begin + chunk);
 
-  float* comb_o = reinterpret_cast<float*>(smem);          // [R][D]
-  float* comb_ml = comb_o + static_cast<size_t>(R) * D;    // [R][2]
+  float* comb_o = reinterpret_cast<float*>(smem);                            // [KS][R][D], KS * R <= max(R, warps)
+  float* comb_ml = comb_o + static_cast<size_t>(max(R, nwarps)) * D;         // [KS][R][2]
   const float* kg = static_cast<const float*>(p.k);
   const float* vg = static_cast<const float*>(p.v);
   const float* qg = static_cast<const float*>(p.q) +
                     ((static_cast<long long>(b) * p.q_heads + static_cast<long long>(h) * p.head_stride + p.head0) * p.q_len) * D;
   const float sl2 = p.scale_log2;
 
-  for (int r = warp; r < R; r += nwarps) {
+  // A warp owns one q row (lanes split head_dim) and takes four keys per step: four independent dot products and
+  // shuffle reductions in flight, one online-softmax update for the four.  With fewer rows than warps (plain decode
+  // with a small GQA group) the warps of a row split its keys in groups of four and leave one partial each, which
+  // emit_and_merge combines like the key slices of the tensor-core kernel.
+  constexpr int TB = 4;
+  const int KS = (R <= nwarps && nwarps % R == 0) ? nwarps / R : 1;
+  for (int rr = warp; rr < R * KS; rr += nwarps) {
+    const int r = rr % R, ks = rr / R;
     float qv[VEC], acc[VEC];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) { qv[i] = qg[static_cast<long long>(r) * D + lane * VEC + i]; acc[i] = 0.f; }
     const int lim = p.causal ? (len - p.q_len + (r % p.q_len)) : (len - 1);
     const int stop = min(t_end, lim + 1);
     float m = -INFINITY, l = 0.f;
-    for (int t = t_begin; t < stop; ++t) {
-      const long long ko = row_offset(p, p.k_table, b, h, si.start, t, D);
-      const long long vo = (p.layout == B200ATTN_PAGED) ? row_offset(p, p.v_table, b, h, si.start, t, D) : ko;
-      if (ko < 0 || vo < 0) {
-        if (lane == 0) p.header[0] = DEV_ERR_PAGE_RANGE;
-        continue;
-      }
-      float kv[VEC], vv[VEC];
-      if constexpr (VEC == 4) {
-        const float4 k4 = __ldg(reinterpret_cast<const float4*>(kg + ko) + lane);
-        const float4 v4 = __ldg(reinterpret_cast<const float4*>(vg + vo) + lane);
-        kv[0] = k4.x; kv[1] = k4.y; kv[2] = k4.z; kv[3] = k4.w;
-        vv[0] = v4.x; vv[1] = v4.y; vv[2] = v4.z; vv[3] = v4.w;
-      } else {
-        const float2 k2 = __ldg(reinterpret_cast<const float2*>(kg + ko) + lane);
-        const float2 v2 = __ldg(reinterpret_cast<const float2*>(vg + vo) + lane);
-        kv[0] = k2.x; kv[1] = k2.y;
-        vv[0] = v2.x; vv[1] = v2.y;
-      }
-      float dot = 0.f;
+    for (int t = t_begin + ks * TB; t < stop; t += KS * TB) {
+      float dot[TB], vv[TB][VEC];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) dot = fmaf(qv[i], kv[i], dot);
-      for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-      const float sc = dot * sl2;
-      const float mn = fmaxf(m, sc);
-      const float a = fast_exp2(m - mn);
-      const float pw = fast_exp2(sc - mn);
-      l = l * a + pw;
+      for (int j = 0; j < TB; ++j) {
+        dot[j] = -INFINITY;                       // a key past the end, or on a page outside the cache, weighs nothing
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] = fmaf(pw, vv[i], acc[i] * a);
+        for (int i = 0; i < VEC; ++i) vv[j][i] = 0.f;
+        if (t + j >= stop) continue;
+        const long long ko = row_offset(p, p.k_table, b, h, si.start, t + j, D);
+        const long long vo = (p.layout == B200ATTN_PAGED) ? row_offset(p, p.v_table, b, h, si.start, t + j, D) : ko;
+        if (ko < 0 || vo < 0) {
+          if (lane == 0) p.header[0] = DEV_ERR_PAGE_RANGE;
+          continue;
+        }
+        float kv[VEC];
+        if constexpr (VEC == 4) {
+          const float4 k4 = __ldg(reinterpret_cast<const float4*>(kg + ko) + lane);
+          const float4 v4 = __ldg(reinterpret_cast<const float4*>(vg + vo) + lane);
+          kv[0] = k4.x; kv[1] = k4.y; kv[2] = k4.z; kv[3] = k4.w;
+          vv[j][0] = v4.x; vv[j][1] = v4.y; vv[j][2] = v4.z; vv[j][3] = v4.w;
+        } else {
+          const float2 k2 = __ldg(reinterpret_cast<const float2*>(kg + ko) + lane);
+          const float2 v2 = __ldg(reinterpret_cast<const float2*>(vg + vo) + lane);
+          kv[0] = k2.x; kv[1] = k2.y;
+          vv[j][0] = v2.x; vv[j][1] = v2.y;
+        }
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) d = fmaf(qv[i], kv[i], d);
+        dot[j] = d;
+      }
+      // (-inf + -inf stays -inf through the reduction: every lane of the warp took the same branch for key j)
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+        for (int j = 0; j < TB; ++j) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], off);
+      }
+      float mn = m;
+#pragma unroll
+      for (int j = 0; j < TB; ++j) { dot[j] *= sl2; mn = fmaxf(mn, dot[j]); }
+      if (mn == -INFINITY) continue;              // nothing visible yet
+      const float a = fast_exp2(m - mn);          // m == -inf: exp2(-inf) = 0
+      l *= a;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] *= a;
+#pragma unroll
+      for (int j = 0; j < TB; ++j) {
+        const float pw = fast_exp2(dot[j] - mn);
+        l += pw;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = fmaf(pw, vv[j][i], acc[i]);
+      }
       m = mn;
     }
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) comb_o[static_cast<size_t>(r) * D + lane * VEC + i] = acc[i];
-    if (lane == 0) { comb_ml[r * 2] = m; comb_ml[r * 2 + 1] = l; }
+    for (int i = 0; i < VEC; ++i) comb_o[(static_cast<size_t>(ks) * R + r) * D + lane * VEC + i] = acc[i];
+    if (lane == 0) { comb_ml[(ks * R + r) * 2] = m; comb_ml[(ks * R + r) * 2 + 1] = l; }
   }
   __syncthreads();
-  emit_and_merge<float, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, 1, R, &s_ticket);
+  emit_and_merge<float, D>(p, b, h, c, n_chunks, item0, comb_o, comb_ml, KS, R, &s_ticket);
 }
 
 // Launches `kernel` so that it may be scheduled while the planner before it in the stream is still running; the
@@ -1724,7 +1753,7 @@ int launch_decode_pass(const b200attn_decode_args_t& a, int sm_count, cudaStream
   const dim3 grid(static_cast<unsigned>(w.max_items) * a.kv_heads, 1);
   const int D = a.head_dim;
   if (a.dtype == B200ATTN_F32) {
-    const size_t smem = sizeof(float) * static_cast<size_t>(p.rows) * (D + 2);
+    const size_t smem = sizeof(float) * static_cast<size_t>(std::max(p.rows, 4)) * (D + 2);   // 4 warps: see the kernel
     int rc = 0;
     if (D == 128) { rc = set_smem(decode_simt_kernel<128>, smem); if (rc) return rc; launch_after_planner(decode_simt_kernel<128>, grid, 128, smem, stream, p); }
     else          { rc = set_smem(decode_simt_kernel<64>, smem);  if (rc) return rc; launch_after_planner(decode_simt_kernel<64>, grid, 128, smem, stream, p); }
