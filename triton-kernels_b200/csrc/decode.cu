@@ -259,6 +259,16 @@ __device__ __forceinline__ int seq_chunk(int len, int n, int global_chunk, int e
   return c < kTileN ? kTileN : c;
 }
 
+// ceil(a / b) for a >= 0, b > 0 with `inv_b` = 1 / b in float: exact (the float quotient is at most one off for
+// a < 2^22, and is corrected; larger a take the integer division).
+__device__ __forceinline__ int ceil_div_fast(int a, int b, float inv_b) {
+  if (a >= (1 << 22)) return static_cast<int>((static_cast<long long>(a) + b - 1) / b);
+  int q = __float2int_ru(static_cast<float>(a) * inv_b);
+  if (q * b < a) ++q;
+  else if (q > 0 && (q - 1) * b >= a) --q;
+  return q;
+}
+
 __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeParams p) {
   __shared__ long long s_tot[32];
   __shared__ int s_warp[32];
@@ -299,7 +309,9 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
   // resident CTA plus half an item for several.
   long long t = 0;
   for (int w = 0; w < kPlanThreads / 32; ++w) t += s_tot[w];
-  auto evaluate = [&](int target) {
+  // (the two divisions per sequence go through a float reciprocal, corrected to the exact quotient: a pass over 256
+  // lengths with integer divisions cost 2 us, and the pass runs once or twice per call)
+  auto evaluate = [&](int target, bool with_largest) {
     long long base = (t + target - 1) / target;
     base = ((base + kTileN - 1) / kTileN) * kTileN;
     if (base < p.min_chunk) base = p.min_chunk;
@@ -307,14 +319,22 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     long long cand = base + (base * warp) / 32;
     cand = ((cand + kTileN - 1) / kTileN) * kTileN;
     const int ck = static_cast<int>(cand);
+    const float inv_ck = 1.f / static_cast<float>(ck);
     long long n = 0;
     int biggest = 0;
     for (int b = lane; b < p.batch; b += 32) {
       const int len = len_of(b);
-      int v = (len + ck - 1) / ck;
+      int v = ceil_div_fast(len, ck, inv_ck);
       if (v < 1) v = 1;
       n += v;
-      biggest = max(biggest, min(len, seq_chunk(len, v, ck, p.equal_split)));
+      if (with_largest) {
+        int per = ck;
+        if (p.equal_split) {
+          per = ((ceil_div_fast(len, v, __frcp_rn(static_cast<float>(v))) + kTileN - 1) / kTileN) * kTileN;
+          if (per < kTileN) per = kTileN;
+        }
+        biggest = max(biggest, min(len, per));
+      }
     }
     for (int o = 16; o > 0; o >>= 1) {
       n += __shfl_xor_sync(0xffffffffu, n, o);
@@ -326,7 +346,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
       s_cand_max[warp] = biggest;
     }
   };
-  evaluate(p.target_items);
+  evaluate(p.target_items, false);
   __syncthreads();
   if (tid == 0) {
     int pick = kPlanThreads / 32 - 1;
@@ -340,7 +360,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
   __syncthreads();
   // (a batch of more sequences than a wave has CTAs cannot fit one: every sequence is at least one item)
   if (p.wave_items > 0 && p.wave_items < p.target_items && s_pick_items > p.wave_items && p.batch <= p.wave_items) {
-    evaluate(p.wave_items);
+    evaluate(p.wave_items, true);
     __syncthreads();
     if (tid == 0) {
       int pick = -1;
