@@ -472,6 +472,7 @@ __global__ void __launch_bounds__(kPlanThreads) decode_plan_kernel(const DecodeP
     p.header[1] = chunk;
     p.header[2] = n_items;
     p.header[3] = 0;          // tickets drawn and not merged yet (tcgen05 kernel)
+    p.header[4] = 0;          // units drawn beyond the CTAs' first ones (tcgen05 kernel)
   }
 }
 
@@ -910,17 +911,18 @@ __global__ void __launch_bounds__(kMaxThreads, kMinBlocks) decode_mma_kernel(con
 // MN-major B operand).  Two CTAs share an SM (256 TMEM columns, 3 stages of 64 keys each), which overlaps one CTA's
 // softmax with the other's MMAs.
 //
-// The kernel is persistent: the grid is one wave (two CTAs per SM) and CTA j works through the units
-// (item, kv head) j, 2G-1-j, 2G+j, ... of the planner's longest-first list (G = grid size; the back-and-forth order
-// evens out the sizes a CTA gets).  Every role walks that list by itself, so the producer warp runs ahead into the
-// next unit while the last tiles of the current one are still being consumed: the stage ring - the bytes the SM
-// keeps in flight, which is what bounds this kernel - never drains between units, and tensor memory, barriers and
-// tensor maps are set up once per CTA.  For that the epilogue leaves shared memory alone: each softmax thread writes
-// its O row from registers to the output (single-chunk sequences) or to the partials, and the ticket merge runs among
-// the softmax warps.  Planner and partial / ticket formats are shared with the kernels above.
+// The kernel is persistent: the grid is one wave (two CTAs per SM); a CTA starts with unit (item, kv head) number
+// blockIdx.x of the planner's longest-first list and its producer warp draws further units from a counter in the
+// workspace header, publishing them to the MMA and softmax warps through a four-deep ring in shared memory.  The
+// producer runs ahead into the next unit while the last tiles of the current one are still being consumed: the stage
+// ring - the bytes the SM keeps in flight, which is what bounds this kernel - never drains between units, and tensor
+// memory, barriers and tensor maps are set up once per CTA.  For that the epilogue leaves shared memory alone: each
+// softmax thread writes its O row from registers to the output (single-chunk sequences) or to the partials; merges
+// are claimed by CTAs in their teardown.  Planner and partial / ticket formats are shared with the kernels above.
 // ---------------------------------------------------------------------------
 constexpr int kUmmaStages = 3;
 constexpr int kUmmaTmemCols = 256;
+constexpr int kUmmaUnitRing = 4;      // units the producer may be ahead of the slowest consumer
 constexpr int kUmmaMaxClaims = 1;     // merges a CTA takes per sweep of the ticket counters in its teardown
 constexpr int kMergeClaimed = 1 << 30; // added to a pair's ticket counter by the CTA that merges it
 
@@ -933,6 +935,10 @@ struct __align__(8) UmmaCtrl {
   uint64_t o_done;    // MMA warp -> softmax warps (commit): PV of a tile
   uint64_t o_free;    // softmax warps -> MMA warp: the finished unit's O has been read out of tensor memory
   uint64_t rows_out;  // softmax threads: my partial rows of the unit are written and fenced
+  uint64_t unit_full[kUmmaUnitRing];    // producer -> MMA and softmax warps: slot r % ring holds the CTA's r-th unit
+  uint64_t unit_empty[kUmmaUnitRing];   // MMA warp + softmax warps -> producer: done with that slot
+  int unit_ring[kUmmaUnitRing];         // unit indices (n_units or more: the CTA has no r-th unit)
+  int published;                        // units published so far, the end mark included
   uint32_t tmem_base;
   int abort_flag;
   int abort_round;    // first round (unit of this CTA) whose output may be incomplete after a wait ran out
@@ -998,6 +1004,11 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     mbar_init(smem_u32(&ctrl->o_done), 1);
     mbar_init(smem_u32(&ctrl->o_free), n_softmax);
     mbar_init(smem_u32(&ctrl->rows_out), n_softmax);
+    for (int i = 0; i < kUmmaUnitRing; ++i) {
+      mbar_init(smem_u32(&ctrl->unit_full[i]), 1);
+      mbar_init(smem_u32(&ctrl->unit_empty[i]), 1 + active_warps);
+    }
+    ctrl->published = 0;
     ctrl->abort_flag = 0;
     ctrl->abort_round = 0x7fffffff;
     mbar_fence_init();
@@ -1015,8 +1026,19 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
   ptx::grid_dep_wait();      // the planner's records are complete and visible from here on
   const int n_units = p.header[2] * p.kv_heads;
   const int G = static_cast<int>(gridDim.x), me = static_cast<int>(blockIdx.x);
-  // unit of this CTA in round r (out of range = the CTA is done: later rounds are out of range too)
-  auto unit_index = [&](int r) { return r * G + ((r & 1) ? G - 1 - me : me); };
+  // Units are handed out dynamically, longest first: a CTA's first unit is its own index, later ones are drawn from a
+  // counter in the workspace header by the producer warp, which publishes them to the other warps through a small
+  // ring in shared memory (a static deal cannot follow a batch of a few long and many short sequences: the CTAs that
+  // were dealt one more long unit finish last).  unit_at(r): the CTA's r-th unit, n_units or more when there is
+  // none, -1 when the (bounded) wait for the producer ran out.
+  auto unit_at = [&](int r) -> int {
+    if (!warp_wait(smem_u32(&ctrl->unit_full[r % kUmmaUnitRing]), (r / kUmmaUnitRing) & 1)) return -1;
+    return *reinterpret_cast<volatile int*>(&ctrl->unit_ring[r % kUmmaUnitRing]);
+  };
+  auto unit_done = [&](int r) {   // this warp will not read slot r again
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&ctrl->unit_empty[r % kUmmaUnitRing]));
+  };
 
   if (warp == kProducer) {
     // =========================== TMA producer ===========================
@@ -1028,9 +1050,14 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     PageAhead ahead(p, 0, lane);
     int kp_next = kNoPage, vp_next = kNoPage;
     int ahead_g = -1;                            // running tile index the entries in kp_next / vp_next belong to
-    for (int r = 0; ok; ++r) {
-      const int u = unit_index(r);
-      if (u >= n_units) break;
+    auto publish = [&](int r, int u) {            // lane 0
+      ctrl->unit_ring[r % kUmmaUnitRing] = u;
+      ctrl->published = r + 1;
+      mbar_arrive(smem_u32(&ctrl->unit_full[r % kUmmaUnitRing]));
+    };
+    int u = me < n_units ? me : n_units;
+    if (lane == 0) publish(0, u);
+    for (int r = 0; ok && u < n_units; ++r) {
       const UmmaUnit w = umma_unit(p, u);
       ahead.retarget(p, w.b);
       int h_coord = w.h;
@@ -1069,17 +1096,10 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
             if (kr >= 0) tma_load_3d(kdst + cc * CHUNK_BYTES + roff, &tm_k, bar, cc * 64, h_coord, kr);
             if (vr >= 0) tma_load_3d(vdst + cc * CHUNK_BYTES + roff, &tm_v, bar, cc * 64, h_coord, vr);
           }
-          // read ahead: the next tile of this unit, or the first tile of the CTA's next unit
+          // read ahead: the next tile of this unit (the first tile of the next unit: after the draw below)
           if (tile + 1 < w.ntiles) {
             ahead.fetch(t0 + kTileN, w.t_end, kp_next, vp_next);
             ahead_g = g + 1;
-          } else if (unit_index(r + 1) < n_units) {
-            const UmmaUnit w2 = umma_unit(p, unit_index(r + 1));
-            if (w2.ntiles > 0) {
-              ahead.retarget(p, w2.b);
-              ahead.fetch(w2.t_begin, w2.t_end, kp_next, vp_next);
-              ahead_g = g + 1;
-            }
           }
         } else {
           const int boxes = kTileN >> p.box_shift;
@@ -1121,6 +1141,32 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
         }
         ++g;
       }
+      if (!ok) break;
+      // The unit's last copy is on its way: only now draw the next unit (as late as the ring allows, so that the
+      // longest-first list is dealt to whoever runs dry first), publish it, and pull what its first steps need -
+      // the block-table entries of its first tile, its Q rows (into L2) - ahead of the warps that will ask for them.
+      int u_next = n_units;
+      if (r + 1 >= kUmmaUnitRing) {
+        ok = warp_wait(smem_u32(&ctrl->unit_empty[(r + 1) % kUmmaUnitRing]), ((r + 1) / kUmmaUnitRing - 1) & 1);
+        if (!ok || *abort_flag) { ok = false; break; }
+      }
+      if (lane == 0) {
+        u_next = min(G + atomicAdd(p.header + 4, 1), n_units);
+        publish(r + 1, u_next);
+      }
+      u_next = __shfl_sync(0xffffffffu, u_next, 0);
+      if (u_next < n_units) {
+        const UmmaUnit w2 = umma_unit(p, u_next);
+        if (ahead.on && w2.ntiles > 0) {
+          ahead.retarget(p, w2.b);
+          ahead.fetch(w2.t_begin, w2.t_end, kp_next, vp_next);
+          ahead_g = g;
+        }
+        const T* q2 = static_cast<const T*>(p.q) +
+                      ((static_cast<long long>(w2.b) * p.q_heads + static_cast<long long>(w2.h) * p.head_stride + p.head0) * p.q_len) * D;
+        for (int i = lane; i < (R * D * static_cast<int>(sizeof(T))) / 128; i += 32) prefetch_l2(reinterpret_cast<const char*>(q2) + i * 128);
+      }
+      u = u_next;
     }
     if (!ok) {
       if (lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
@@ -1146,8 +1192,10 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     };
     bool ok = true;
     int g = 0;                                   // tiles consumed so far, over all units
+    // (the record of the next unit is read while the current one runs: two L2 round trips less at every hand-over)
     for (int r = 0; ok; ++r) {
-      const int u = unit_index(r);
+      const int u = unit_at(r);
+      if (u < 0) { ok = false; break; }
       if (u >= n_units) break;
       const UmmaUnit w = umma_unit(p, u);
       ok = warp_wait(smem_u32(&ctrl->q_ready), r & 1);
@@ -1155,6 +1203,7 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
       if (w.ntiles == 0) {
         // nothing to multiply; keep the o_free phase in step (the softmax warps arrive once per unit)
         if (r > 0) ok = warp_wait(smem_u32(&ctrl->o_free), (r - 1) & 1);
+        unit_done(r);
         continue;
       }
       ok = warp_wait(smem_u32(&ctrl->full[g % kUmmaStages]), (g / kUmmaStages) & 1);
@@ -1198,6 +1247,7 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
         // K_tile was read by S(tile) (complete: its P has come back) and V_tile by the PV just issued
         mma_commit_lead(smem_u32(&ctrl->empty[stage]), lead);
       }
+      if (ok) unit_done(r);
     }
     if (!ok && lane == 0) { p.header[0] = DEV_ERR_WAIT_EXPIRED; *abort_flag = 1; }
   } else if (warp < active_warps) {
@@ -1250,22 +1300,12 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
       }
       owed_pair = -1;
     };
-    UmmaUnit w = umma_unit(p, min(unit_index(0), max(n_units - 1, 0)));
-    write_q(unit_index(0), w);
+    int u = unit_at(0);
+    if (u < 0) ok = false;
+    UmmaUnit w = umma_unit(p, min(max(u, 0), max(n_units - 1, 0)));
+    if (ok) write_q(u, w);
     for (; ok; ++r) {
-      const int u = unit_index(r);
       if (u >= n_units) break;
-      // the next unit's record is read now, and its Q row pulled into L2, so that neither is waited for at the hand-over
-      const int u_next = unit_index(r + 1);
-      UmmaUnit w_next = w;
-      if (u_next < n_units) {
-        w_next = umma_unit(p, u_next);
-        if (row < R) {
-          const T* qn = static_cast<const T*>(p.q) + (rows_of(w_next) + row) * D;
-          prefetch_l2(qn);
-          if (D * sizeof(T) > 128) prefetch_l2(qn + 64);
-        }
-      }
       const long long row_base = rows_of(w);
       float m_used = -INFINITY, l_run = 0.f;               // per-row softmax state
       int lim = w.len - 1;                                 // last visible key of this row
@@ -1332,6 +1372,11 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
         mbar_arrive(smem_u32(&ctrl->p_ready));
       }
       if (!ok) break;
+      // the next unit (published by the producer when it issued this unit's last copy, its Q rows already on their
+      // way into L2): its Q goes to tensor memory before this unit's rows are written out
+      const int u_next = unit_at(r + 1);
+      if (u_next < 0) { ok = false; break; }
+      const UmmaUnit w_next = u_next < n_units ? umma_unit(p, u_next) : w;
       write_q(u_next, w_next);
       // ---------------- the unit's rows leave tensor memory ----------------
       if (w.ntiles > 0) {
@@ -1401,7 +1446,9 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
         owed_round = r;
         ++merges;
       }
+      unit_done(r);
       w = w_next;
+      u = u_next;
     }
     if (ok) draw_owed_ticket();
     if (!ok) {
@@ -1459,8 +1506,9 @@ __global__ void __launch_bounds__(192, 2) decode_umma_kernel(const __grid_consta
     // reached, are unknown.  They are filled with NaN (and their tickets are not drawn, so nobody merges over them):
     // the failure shows in the output as well as in the error word.
     const OutT nan_t = ElemTraits<OutT>::from_float(__int_as_float(0x7fc00000));
-    for (int r = ctrl->abort_round; r != 0x7fffffff; ++r) {
-      const int u = unit_index(r);
+    // (the slots of units the softmax warps have not finished cannot have been reused by the producer)
+    for (int r = ctrl->abort_round; r < ctrl->published; ++r) {
+      const int u = ctrl->unit_ring[r % kUmmaUnitRing];
       if (u >= n_units) break;
       const UmmaUnit w = umma_unit(p, u);
       OutT* out = static_cast<OutT*>(p.out) +
