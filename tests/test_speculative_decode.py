@@ -14,7 +14,8 @@ PAGE_SIZE = 16
 M_VALUES = [2, 3, 4, 6, 8, 10, 12, 16]
 
 
-def run_spec(layout, qs, ks, vs, causal, *, index_dtype=torch.int32, permute=None, poison=None, pad=0):
+def run_spec(layout, qs, ks, vs, causal, *, index_dtype=torch.int32, permute=None, poison=None, pad=0,
+             page_size=PAGE_SIZE):
     from kernels.speculative_decode import speculative_decode_attention
 
     B = len(qs)
@@ -33,12 +34,12 @@ def run_spec(layout, qs, ks, vs, causal, *, index_dtype=torch.int32, permute=Non
         k, indptr = sdpa_ref.pack_ragged(ks, index_dtype)
         v, _ = sdpa_ref.pack_ragged(vs, index_dtype)
         return speculative_decode_attention(q, k, v, kv_indptr=indptr, causal=causal)
-    kc, kt, lens_t = sdpa_ref.pack_paged(ks, PAGE_SIZE, permute_seed=permute, extra_pages=2 if permute is not None else 0,
+    kc, kt, lens_t = sdpa_ref.pack_paged(ks, page_size, permute_seed=permute, extra_pages=2 if permute is not None else 0,
                                          pad_value=pad, poison=poison)
-    vc, vt, _ = sdpa_ref.pack_paged(vs, PAGE_SIZE, permute_seed=None if permute is None else permute + 1,
+    vc, vt, _ = sdpa_ref.pack_paged(vs, page_size, permute_seed=None if permute is None else permute + 1,
                                     extra_pages=2 if permute is not None else 0, pad_value=pad, poison=poison)
     return speculative_decode_attention(q, kc, vc, kv_indptr=lens_t.to(index_dtype), k_block_table=kt, v_block_table=vt,
-                                        kv_page_size=PAGE_SIZE, causal=causal)
+                                        kv_page_size=page_size, causal=causal)
 
 
 def with_drafts(rng, gen, B, QH, KVH, M, D, dtype, layout, causal):
@@ -152,3 +153,22 @@ def test_spec_several_units_per_cta(qh, kvh, m, layout):
     # the same call again on the same workspace: tickets and the ready count were left clean
     out2 = run_spec(layout, qs, ks, vs, True, permute=11, pad=-1, poison=float("nan"))
     assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("page", [1, 8, 24, 64, 256])
+@pytest.mark.parametrize("qh,kvh,m", [(64, 8, 5), (8, 2, 3)], ids=["tcgen05-40rows", "warp-kernel-12rows"])
+def test_spec_page_sizes(page, qh, kvh, m):
+    """Page sizes other than 16 under both tensor-core kernels: one key per page (more boxes per tile than lanes, no
+    table read-ahead), a non-power-of-two size, pages larger than a tile; sequences long enough for several tiles and
+    a split."""
+    dtype = torch.bfloat16
+    rng, gen = make_rngs("spec-page", page, qh, kvh, m)
+    lens = [rng.randint(1, 700) for _ in range(5)] + [2300]
+    qs = [torch.randn((qh, m, 64), generator=gen).to(dtype).to(DEVICE) for _ in lens]
+    ks = [torch.randn((n + m, kvh, 64), generator=gen).to(dtype).to(DEVICE) for n in lens]
+    vs = [torch.randn((n + m, kvh, 64), generator=gen).to(dtype).to(DEVICE) for n in lens]
+    refs = sdpa_ref.spec_decode_reference(qs, ks, vs, qh, kvh, True)
+    out = run_spec("paged", qs, ks, vs, True, permute=13, pad=-1, poison=float("nan"), page_size=page)
+    assert torch.isfinite(out.float()).all()
+    for b in range(len(lens)):
+        assert_close_both(out[b], refs[b], dtype, lens[b] + m, f"page {page} seq {b}")
