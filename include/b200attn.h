@@ -120,7 +120,9 @@ typedef struct b200attn_prefill_args_t {
  * runs on fp32 operands (kernels/speculative_decode.py:153,175), but fp16's
  * range: magnitudes beyond 65504 become infinite.  The workspace holds those
  * copies (2 bytes per element of q, k and v as passed: a paged cache is copied
- * whole).  b200attn_decode_static has no room for them and keeps fp32 FMAs.
+ * whole; when k and v together would need more than 8 GiB of copies the call
+ * keeps fp32 FMAs instead).  b200attn_decode_static has no room for them and
+ * keeps fp32 FMAs.
  */
 typedef struct b200attn_decode_args_t {
   const void* q;

@@ -220,3 +220,23 @@ def test_planner_chunk_matches_the_mirror(qh, kvh, m, lens):
     assert header[0] == 0
     assert header[1] == decode_chunk_tokens(plan, lens)
     assert header[2] == sum(decode_items(plan, lens))
+
+
+@pytest.mark.gpu
+def test_fp32_copies_are_capped_by_scratch_size():
+    """fp32 speculative decode asks for room for fp16 copies of q, k, v - unless the cache is so large that the copies
+    would pass 8 GiB, where the call stays on the fp32 kernel and the scratch need does not grow with the cache."""
+    import ctypes as C
+
+    from kernels import _native
+
+    def need(total_kv):
+        a = _native.DecodeArgs()
+        a.batch, a.q_heads, a.kv_heads, a.q_len, a.head_dim = 8, 64, 8, 5, 128
+        a.dtype, a.layout, a.device = _native.F32, _native.PAGED, torch.cuda.current_device()
+        a.page_size, a.total_kv, a.table_stride = 16, total_kv, 64
+        return _native.lib().b200attn_decode_workspace_bytes(C.byref(a))
+
+    small, large = need(100_000), need(10_000_000)
+    assert small >= 2 * 2 * 100_000 * 8 * 128            # fp16 copies of k and v
+    assert large < small                                 # 41 GB of fp32 cache: no copies, fp32 kernel

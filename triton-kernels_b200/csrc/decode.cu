@@ -1679,7 +1679,13 @@ DecodeWsLayout decode_ws_layout(const b200attn_decode_args_t& a, int sm_count, b
   // (kernels/speculative_decode.py:153,175); one fp32 FMA warp per q row re-reads K/V once per row and is one to two
   // orders of magnitude slower there.  Plain decode (one q row per head), which the reference computes in fp32 FMAs
   // (kernels/decode.py:146-160), stays on the fp32 kernel.
-  const bool cast16 = allow_cast && a.dtype == B200ATTN_F32 && (rows > 16 || a.q_len > 1);
+  // (not when the copies would be huge - a paged cache is copied whole - : beyond kCastLimitBytes the call stays on
+  // the fp32 kernel rather than ask the caller for that much scratch)
+  constexpr size_t kCastLimitBytes = size_t(8) << 30;
+  const size_t kv_rows_all = a.layout == B200ATTN_DENSE ? static_cast<size_t>(a.batch) * a.kv_heads * a.max_kv
+                                                        : static_cast<size_t>(a.total_kv > 0 ? a.total_kv : 0) * a.kv_heads;
+  const bool cast16 = allow_cast && a.dtype == B200ATTN_F32 && (rows > 16 || a.q_len > 1) &&
+                      kv_rows_all * a.head_dim * 4 <= kCastLimitBytes;
   const bool f32_kernel = a.dtype == B200ATTN_F32 && !cast16;
   // Six (item, kv head) CTAs per SM: two or three waves of the tensor-core kernels (3 or 2 resident CTAs per SM).
   // Fewer, longer CTAs amortise start-up and merge; the planner keeps the item count at or below this, so the grid

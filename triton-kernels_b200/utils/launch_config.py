@@ -65,7 +65,7 @@ def decode_plan(sm_count: int, batch: int, q_heads: int, kv_heads: int, q_len: i
     group = decode_pass_group(q_heads // kv_heads, q_len)
     rows = group * q_len
     # fp32 inputs of a speculative-decode call (several q rows per head) run the tensor-core kernels on fp16 copies
-    # and are planned like 16-bit inputs
+    # and are planned like 16-bit inputs (unless k and v would need more than 8 GiB of copies: csrc/decode.cu)
     fp32 = fp32 and rows <= 16 and q_len <= 1
     # six (item, kv head) CTAs per SM for the tensor-core kernels (a whole number of waves at 2 or 3 resident CTAs
     # per SM), eight for the fp32 kernel
